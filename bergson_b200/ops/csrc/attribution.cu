@@ -1,0 +1,280 @@
+// Per-example projected Linear gradients on tcgen05 tensor cores.
+//
+// The stored quantity for one Linear and one example n is  P_out (G_n^T A_n) P_in^T  in
+// R^{p x p} (p = 16), computed as (G_n P_out^T)^T (A_n P_in^T): two skinny GEMMs with N = 16
+// that are bound by streaming A and G once from HBM, and a 16 x S x 16 contraction over the
+// example's tokens.  Optimizer (Adafactor) row/column scales are folded into P_out / P_in by
+// the caller, so they cost nothing here.
+//
+//   bgn_proj_right      : A' = A P_in^T                       (forward hook)
+//   bgn_proj_left_outer : acc[n] += (G_n P_out^T)^T A'_n      (backward hook; G' never
+//                         leaves the SM: TMEM -> registers -> shared memory -> 16x16 sum)
+//   bgn_finalize_rows   : clamp / unit-norm / cast the fp32 accumulator rows into the store
+//                         dtype, scattering by dataset index.
+#include "kernels.h"
+#include "tn_gemm.cuh"
+
+#include <mutex>
+
+namespace bgn {
+
+// ---- tensor-map construction ------------------------------------------------------------
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) ==
+            cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess) {
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    }
+  });
+  return fn;
+}
+
+// Row-major 16-bit tensor viewed as (K contiguous, rows, batch); box = 64 x box_rows x 1.
+static bool make_tmap_3d(CUtensorMap* map, const void* base, int fmt, uint64_t K, uint64_t rows,
+                         uint64_t batch, uint32_t box_rows) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (!enc) return false;
+  cuuint64_t dims[3] = {K, rows, batch};
+  cuuint64_t strides[2] = {K * 2, K * rows * 2};
+  cuuint32_t box[3] = {uint32_t(kBlockK), box_rows, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUtensorMapDataType dt = fmt == 1 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  return enc(map, dt, 3, const_cast<void*>(base), dims, strides, box, estr,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+static bool make_tmap_2d(CUtensorMap* map, const void* base, int fmt, uint64_t K, uint64_t rows,
+                         uint32_t box_rows) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (!enc) return false;
+  cuuint64_t dims[2] = {K, rows};
+  cuuint64_t strides[1] = {K * 2};
+  cuuint32_t box[2] = {uint32_t(kBlockK), box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUtensorMapDataType dt = fmt == 1 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  return enc(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// ---- epilogues --------------------------------------------------------------------------
+
+// Plain fp32 store: thread `row` owns one output row and writes 16 contiguous floats.
+struct StoreF32Epilogue {
+  float* out;
+  long ld;
+  int rows;
+  int n_total;
+  int block_n;
+
+  __device__ __forceinline__ void operator()(int row, int c, const float (&acc)[16], int tile_m,
+                                             int tile_n, int batch, void*) const {
+    const long r = long(tile_m) * kBlockM + row;
+    if (r >= rows) return;
+    const int col = tile_n * block_n + c;
+    float* dst = out + (long(batch) * rows + r) * ld + col;
+    if (col + 16 <= n_total && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+#pragma unroll
+      for (int i = 0; i < 16; i += 4)
+        *reinterpret_cast<float4*>(dst + i) = make_float4(acc[i], acc[i + 1], acc[i + 2], acc[i + 3]);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 16; ++i)
+        if (col + i < n_total) dst[i] = acc[i];
+    }
+  }
+  __device__ __forceinline__ void finish(int, int, int, int, void*, bool) const {}
+};
+
+// G' tile (128 tokens x 16) meets A' (128 tokens x 16): out[i][j] = sum_t G'[t][i] A'[t][j],
+// added atomically to the example's fp32 accumulator row.
+struct OuterEpilogue {
+  const float* a_proj;  // [N*S, 16]
+  float* acc;           // [N, ld]
+  long ld;
+  long col_off;
+  int S;
+
+  static constexpr int kGStride = 17;  // padded to keep column reads conflict-free
+  static constexpr int kSmemBytes = (kBlockM * kGStride + kBlockM * 16) * 4;
+
+  __device__ __forceinline__ void operator()(int row, int c, const float (&v)[16], int tile_m, int,
+                                             int batch, void* smem) const {
+    float* gs = reinterpret_cast<float*>(smem);
+    float* as = gs + kBlockM * kGStride;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) gs[row * kGStride + i] = v[i];
+    const int s = tile_m * kBlockM + row;
+    float4 a0 = make_float4(0.f, 0.f, 0.f, 0.f), a1 = a0, a2 = a0, a3 = a0;
+    if (s < S) {
+      const float4* src = reinterpret_cast<const float4*>(a_proj + (long(batch) * S + s) * 16);
+      a0 = __ldg(src);
+      a1 = __ldg(src + 1);
+      a2 = __ldg(src + 2);
+      a3 = __ldg(src + 3);
+    }
+    float4* dst = reinterpret_cast<float4*>(as + row * 16);
+    dst[0] = a0;
+    dst[1] = a1;
+    dst[2] = a2;
+    dst[3] = a3;
+    (void)c;
+  }
+
+  __device__ __forceinline__ void finish(int e, int, int, int batch, void* smem, bool ok) const {
+    named_barrier_sync(1, 128);
+    if (!ok) return;
+    const float* gs = reinterpret_cast<const float*>(smem);
+    const float* as = gs + kBlockM * kGStride;
+    const int i = e >> 3, j = e & 7;
+    float s0 = 0.f, s1 = 0.f;
+#pragma unroll 8
+    for (int t = 0; t < kBlockM; ++t) {
+      const float g = gs[t * kGStride + i];
+      s0 = fmaf(g, as[t * 16 + j], s0);
+      s1 = fmaf(g, as[t * 16 + j + 8], s1);
+    }
+    float* dst = acc + long(batch) * ld + col_off + i * 16;
+    atomicAdd(dst + j, s0);
+    atomicAdd(dst + j + 8, s1);
+  }
+};
+
+template <int BLOCK_N, int FMT, class Epi>
+static cudaError_t launch_tn(const CUtensorMap& ta, const CUtensorMap& tb, TnGemmShape shape,
+                             dim3 grid, Epi epi, int epi_smem, int* status, cudaStream_t stream) {
+  using S = TnGemmSmem<BLOCK_N>;
+  const int stages = S::stages(epi_smem);
+  const int smem = stages * S::kStageBytes + 1024 + 256 + epi_smem;
+  auto kern = tn_gemm_kernel<BLOCK_N, FMT, Epi>;
+  static bool attr_set = false;  // one flag per template instantiation
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (e != cudaSuccess) return e;
+    attr_set = true;
+  }
+  kern<<<grid, kGemmThreads, smem, stream>>>(ta, tb, shape, stages, epi, status);
+  return cudaGetLastError();
+}
+
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+}  // namespace bgn
+
+using namespace bgn;
+
+extern "C" int bgn_proj_right(const void* a, const void* p, float* out, long T, int K, int fmt,
+                              int* status, cudaStream_t stream) {
+  if (K % 8 != 0 || !aligned16(a) || !aligned16(p) || T <= 0) return cudaErrorInvalidValue;
+  CUtensorMap ta, tb;
+  if (!make_tmap_3d(&ta, a, fmt, K, T, 1, kBlockM)) return cudaErrorInvalidValue;
+  if (!make_tmap_2d(&tb, p, fmt, K, 16, 16)) return cudaErrorInvalidValue;
+  TnGemmShape shape{int(T), K, 16};
+  StoreF32Epilogue epi{out, 16, int(T), 16, 16};
+  dim3 grid((T + kBlockM - 1) / kBlockM, 1, 1);
+  cudaError_t e = fmt == 1 ? launch_tn<16, 1>(ta, tb, shape, grid, epi, 0, status, stream)
+                           : launch_tn<16, 0>(ta, tb, shape, grid, epi, 0, status, stream);
+  return int(e);
+}
+
+extern "C" int bgn_proj_left_outer(const void* g, const void* p, const float* a_proj, float* acc,
+                                   int N, int S, int K, long ld, long col_off, int fmt, int* status,
+                                   cudaStream_t stream) {
+  if (K % 8 != 0 || !aligned16(g) || !aligned16(p) || !aligned16(a_proj) || N <= 0 || S <= 0)
+    return cudaErrorInvalidValue;
+  CUtensorMap ta, tb;
+  if (!make_tmap_3d(&ta, g, fmt, K, S, N, kBlockM)) return cudaErrorInvalidValue;
+  if (!make_tmap_2d(&tb, p, fmt, K, 16, 16)) return cudaErrorInvalidValue;
+  TnGemmShape shape{S, K, 16};
+  OuterEpilogue epi{a_proj, acc, ld, col_off, S};
+  dim3 grid((S + kBlockM - 1) / kBlockM, 1, N);
+  cudaError_t e =
+      fmt == 1 ? launch_tn<16, 1>(ta, tb, shape, grid, epi, OuterEpilogue::kSmemBytes, status, stream)
+               : launch_tn<16, 0>(ta, tb, shape, grid, epi, OuterEpilogue::kSmemBytes, status, stream);
+  return int(e);
+}
+
+extern "C" int bgn_tn_gemm(const void* a, const void* b, float* c, long M, int N, int K, long ldc,
+                           int fmt, int* status, cudaStream_t stream) {
+  if (K % 8 != 0 || !aligned16(a) || !aligned16(b) || M <= 0 || N <= 0) return cudaErrorInvalidValue;
+  constexpr int BN = 128;
+  CUtensorMap ta, tb;
+  if (!make_tmap_3d(&ta, a, fmt, K, M, 1, kBlockM)) return cudaErrorInvalidValue;
+  if (!make_tmap_2d(&tb, b, fmt, K, N, BN)) return cudaErrorInvalidValue;
+  TnGemmShape shape{int(M), K, N};
+  StoreF32Epilogue epi{c, ldc, int(M), N, BN};
+  dim3 grid((M + kBlockM - 1) / kBlockM, (N + BN - 1) / BN, 1);
+  cudaError_t e = fmt == 1 ? launch_tn<BN, 1>(ta, tb, shape, grid, epi, 0, status, stream)
+                           : launch_tn<BN, 0>(ta, tb, shape, grid, epi, 0, status, stream);
+  return int(e);
+}
+
+// ---- row finalisation ---------------------------------------------------------------------
+
+namespace bgn {
+
+template <typename T>
+__global__ void finalize_rows_kernel(const float* __restrict__ acc, T* __restrict__ out,
+                                     const long* __restrict__ row_index, long D, long out_ld, float lo,
+                                     float hi, int unit_norm) {
+  const long r = blockIdx.x;
+  const float* src = acc + r * D;
+  T* dst = out + (row_index ? row_index[r] : r) * out_ld;
+  float scale = 1.f;
+  if (unit_norm) {
+    float ss = 0.f;
+    for (long i = threadIdx.x; i < D; i += blockDim.x) {
+      const float v = to_float<T>(from_float<T>(fminf(fmaxf(src[i], lo), hi)));
+      ss = fmaf(v, v, ss);
+    }
+    __shared__ float red[32];
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+      float v = threadIdx.x < (blockDim.x >> 5) ? red[threadIdx.x] : 0.f;
+      v = warp_sum(v);
+      if (threadIdx.x == 0) red[0] = v;
+    }
+    __syncthreads();
+    // rsqrt(max(sum of squares, eps_fp32^2))
+    scale = rsqrtf(fmaxf(red[0], 1.4210854715202004e-14f));
+  }
+  for (long i = threadIdx.x; i < D; i += blockDim.x) {
+    float v = fminf(fmaxf(src[i], lo), hi);
+    if (unit_norm) v = to_float<T>(from_float<T>(v)) * scale;
+    dst[i] = from_float<T>(v);
+  }
+}
+
+}  // namespace bgn
+
+extern "C" int bgn_finalize_rows(const float* acc, void* out, const long* row_index, int N, long D,
+                                 long out_ld, float lo, float hi, int unit_norm, int out_type,
+                                 cudaStream_t stream) {
+  if (N <= 0) return 0;
+  const int threads = 256;
+  switch (out_type) {
+    case 0:
+      finalize_rows_kernel<__half><<<N, threads, 0, stream>>>(acc, (__half*)out, row_index, D, out_ld, lo, hi, unit_norm);
+      break;
+    case 1:
+      finalize_rows_kernel<__nv_bfloat16><<<N, threads, 0, stream>>>(acc, (__nv_bfloat16*)out, row_index, D, out_ld, lo, hi, unit_norm);
+      break;
+    default:
+      finalize_rows_kernel<float><<<N, threads, 0, stream>>>(acc, (float*)out, row_index, D, out_ld, lo, hi, unit_norm);
+  }
+  return int(cudaGetLastError());
+}

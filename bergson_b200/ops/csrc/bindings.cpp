@@ -1,0 +1,285 @@
+// Python bindings: tensor checks, output allocation, current-stream lookup; the kernels
+// themselves are behind the C interface in kernels.h.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/extension.h>
+
+#include <map>
+#include <mutex>
+
+#include "kernels.h"
+
+namespace {
+
+int type_code(const at::Tensor& t) {
+  switch (t.scalar_type()) {
+    case at::kHalf: return 0;
+    case at::kBFloat16: return 1;
+    case at::kFloat: return 2;
+    default: TORCH_CHECK(false, "bergson_b200: unsupported dtype ", t.scalar_type());
+  }
+}
+
+int fmt16(const at::Tensor& t) {
+  TORCH_CHECK(t.scalar_type() == at::kHalf || t.scalar_type() == at::kBFloat16,
+              "bergson_b200: tensor-core kernels take fp16 or bf16 inputs, got ", t.scalar_type());
+  return t.scalar_type() == at::kBFloat16 ? 1 : 0;
+}
+
+void check(int err, const char* what) {
+  TORCH_CHECK(err == 0, "bergson_b200: ", what, " failed: ",
+              cudaGetErrorString(static_cast<cudaError_t>(err)));
+}
+
+cudaStream_t stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+
+#define CHECK_CUDA_CONTIG(x) TORCH_CHECK((x).is_cuda() && (x).is_contiguous(), #x " must be a contiguous CUDA tensor")
+
+// One status word per device, written by kernels whose bounded waits run out.
+at::Tensor status_tensor(int device) {
+  static std::mutex mu;
+  static std::map<int, at::Tensor> words;
+  std::lock_guard<std::mutex> lock(mu);
+  auto it = words.find(device);
+  if (it == words.end()) {
+    it = words.emplace(device, at::zeros({1}, at::TensorOptions().dtype(at::kInt).device(at::kCUDA, device))).first;
+  }
+  return it->second;
+}
+
+int* status_ptr(const at::Tensor& like) { return status_tensor(like.get_device()).data_ptr<int>(); }
+
+}  // namespace
+
+std::vector<at::Tensor> rmsnorm_fwd(at::Tensor x, at::Tensor w, double eps) {
+  CHECK_CUDA_CONTIG(x); CHECK_CUDA_CONTIG(w);
+  c10::cuda::CUDAGuard guard(x.device());
+  auto y = at::empty_like(x);
+  auto rstd = at::empty({x.size(0)}, x.options().dtype(at::kFloat));
+  auto wc = w.scalar_type() == x.scalar_type() ? w : w.to(x.scalar_type());
+  check(bgn_rmsnorm_fwd(x.data_ptr(), wc.data_ptr(), y.data_ptr(), rstd.data_ptr<float>(), x.size(0),
+                        (int)x.size(1), (float)eps, type_code(x), stream()), "rmsnorm_fwd");
+  return {y, rstd};
+}
+
+std::vector<at::Tensor> rmsnorm_bwd(at::Tensor dy, at::Tensor x, at::Tensor w, at::Tensor rstd, bool need_dw) {
+  CHECK_CUDA_CONTIG(dy); CHECK_CUDA_CONTIG(x);
+  c10::cuda::CUDAGuard guard(x.device());
+  auto dx = at::empty_like(x);
+  auto wc = w.scalar_type() == x.scalar_type() ? w : w.to(x.scalar_type());
+  at::Tensor partial, dw;
+  int n_partial = 0;
+  if (need_dw) {
+    n_partial = (int)std::min<int64_t>(x.size(0), 148 * 2);
+    partial = at::empty({n_partial, x.size(1)}, x.options().dtype(at::kFloat));
+  }
+  check(bgn_rmsnorm_bwd(dy.data_ptr(), x.data_ptr(), wc.data_ptr(), rstd.data_ptr<float>(), dx.data_ptr(),
+                        need_dw ? partial.data_ptr<float>() : nullptr, n_partial, x.size(0), (int)x.size(1),
+                        type_code(x), stream()), "rmsnorm_bwd");
+  if (need_dw) dw = partial.sum(0).to(w.scalar_type());
+  return {dx, dw};
+}
+
+std::vector<at::Tensor> layernorm_fwd(at::Tensor x, at::Tensor w, c10::optional<at::Tensor> b, double eps) {
+  CHECK_CUDA_CONTIG(x);
+  c10::cuda::CUDAGuard guard(x.device());
+  auto y = at::empty_like(x);
+  auto mean = at::empty({x.size(0)}, x.options().dtype(at::kFloat));
+  auto rstd = at::empty_like(mean);
+  auto wc = w.to(x.scalar_type()).contiguous();
+  at::Tensor bc;
+  if (b.has_value()) bc = b->to(x.scalar_type()).contiguous();
+  check(bgn_layernorm_fwd(x.data_ptr(), wc.data_ptr(), b.has_value() ? bc.data_ptr() : nullptr, y.data_ptr(),
+                          mean.data_ptr<float>(), rstd.data_ptr<float>(), x.size(0), (int)x.size(1), (float)eps,
+                          type_code(x), stream()), "layernorm_fwd");
+  return {y, mean, rstd};
+}
+
+std::vector<at::Tensor> layernorm_bwd(at::Tensor dy, at::Tensor x, at::Tensor w, at::Tensor mean, at::Tensor rstd,
+                                      bool need_dw) {
+  CHECK_CUDA_CONTIG(dy); CHECK_CUDA_CONTIG(x);
+  c10::cuda::CUDAGuard guard(x.device());
+  auto dx = at::empty_like(x);
+  auto wc = w.to(x.scalar_type()).contiguous();
+  at::Tensor pw, pb, dw, db;
+  int n_partial = 0;
+  if (need_dw) {
+    n_partial = (int)std::min<int64_t>(x.size(0), 148 * 2);
+    pw = at::empty({n_partial, x.size(1)}, x.options().dtype(at::kFloat));
+    pb = at::empty_like(pw);
+  }
+  check(bgn_layernorm_bwd(dy.data_ptr(), x.data_ptr(), wc.data_ptr(), mean.data_ptr<float>(), rstd.data_ptr<float>(),
+                          dx.data_ptr(), need_dw ? pw.data_ptr<float>() : nullptr,
+                          need_dw ? pb.data_ptr<float>() : nullptr, n_partial, x.size(0), (int)x.size(1),
+                          type_code(x), stream()), "layernorm_bwd");
+  if (need_dw) {
+    dw = pw.sum(0).to(w.scalar_type());
+    db = pb.sum(0).to(w.scalar_type());
+  }
+  return {dx, dw, db};
+}
+
+at::Tensor rotary(at::Tensor x, at::Tensor cos, at::Tensor sin, int64_t rot, bool inverse) {
+  CHECK_CUDA_CONTIG(x);
+  TORCH_CHECK(x.dim() == 4, "rotary expects [B, S, H, D]");
+  c10::cuda::CUDAGuard guard(x.device());
+  auto y = at::empty_like(x);
+  auto c = cos.to(at::kFloat).contiguous(), s = sin.to(at::kFloat).contiguous();
+  TORCH_CHECK(c.size(0) >= x.size(1) && c.size(1) == rot / 2, "rotary table shape mismatch");
+  check(bgn_rotary(x.data_ptr(), c.data_ptr<float>(), s.data_ptr<float>(), y.data_ptr(), x.size(0), (int)x.size(1),
+                   (int)x.size(2), (int)x.size(3), (int)rot, inverse ? 1 : 0, type_code(x), stream()), "rotary");
+  return y;
+}
+
+at::Tensor swiglu_fwd(at::Tensor g, at::Tensor u) {
+  CHECK_CUDA_CONTIG(g); CHECK_CUDA_CONTIG(u);
+  c10::cuda::CUDAGuard guard(g.device());
+  auto y = at::empty_like(g);
+  check(bgn_swiglu_fwd(g.data_ptr(), u.data_ptr(), y.data_ptr(), g.numel(), type_code(g), stream()), "swiglu_fwd");
+  return y;
+}
+
+std::vector<at::Tensor> swiglu_bwd(at::Tensor dy, at::Tensor g, at::Tensor u) {
+  CHECK_CUDA_CONTIG(dy); CHECK_CUDA_CONTIG(g); CHECK_CUDA_CONTIG(u);
+  c10::cuda::CUDAGuard guard(g.device());
+  auto dg = at::empty_like(g), du = at::empty_like(u);
+  check(bgn_swiglu_bwd(dy.data_ptr(), g.data_ptr(), u.data_ptr(), dg.data_ptr(), du.data_ptr(), g.numel(),
+                       type_code(g), stream()), "swiglu_bwd");
+  return {dg, du};
+}
+
+at::Tensor gelu_fwd(at::Tensor x, bool tanh_approx) {
+  CHECK_CUDA_CONTIG(x);
+  c10::cuda::CUDAGuard guard(x.device());
+  auto y = at::empty_like(x);
+  check(bgn_gelu_fwd(x.data_ptr(), y.data_ptr(), x.numel(), tanh_approx, type_code(x), stream()), "gelu_fwd");
+  return y;
+}
+
+at::Tensor gelu_bwd(at::Tensor dy, at::Tensor x, bool tanh_approx) {
+  CHECK_CUDA_CONTIG(dy); CHECK_CUDA_CONTIG(x);
+  c10::cuda::CUDAGuard guard(x.device());
+  auto dx = at::empty_like(x);
+  check(bgn_gelu_bwd(dy.data_ptr(), x.data_ptr(), dx.data_ptr(), x.numel(), tanh_approx, type_code(x), stream()),
+        "gelu_bwd");
+  return dx;
+}
+
+std::vector<at::Tensor> ce_fwd(at::Tensor logits, at::Tensor targets, int64_t ignore_index) {
+  CHECK_CUDA_CONTIG(logits); CHECK_CUDA_CONTIG(targets);
+  TORCH_CHECK(logits.dim() == 2 && targets.scalar_type() == at::kLong);
+  c10::cuda::CUDAGuard guard(logits.device());
+  auto loss = at::empty({logits.size(0)}, logits.options().dtype(at::kFloat));
+  auto lse = at::empty_like(loss);
+  if (logits.size(0) > 0)
+    check(bgn_ce_fwd(logits.data_ptr(), targets.data_ptr<int64_t>(), loss.data_ptr<float>(), lse.data_ptr<float>(),
+                     logits.size(0), (int)logits.size(1), ignore_index, type_code(logits), stream()), "ce_fwd");
+  return {loss, lse};
+}
+
+at::Tensor ce_bwd(at::Tensor logits, at::Tensor targets, at::Tensor lse, at::Tensor dloss, int64_t ignore_index) {
+  CHECK_CUDA_CONTIG(logits); CHECK_CUDA_CONTIG(dloss);
+  c10::cuda::CUDAGuard guard(logits.device());
+  auto dlogits = at::empty_like(logits);
+  if (logits.size(0) > 0)
+    check(bgn_ce_bwd(logits.data_ptr(), targets.data_ptr<int64_t>(), lse.data_ptr<float>(), dloss.data_ptr<float>(),
+                     dlogits.data_ptr(), logits.size(0), (int)logits.size(1), ignore_index, type_code(logits),
+                     stream()), "ce_bwd");
+  return dlogits;
+}
+
+at::Tensor proj_right(at::Tensor a, at::Tensor p) {
+  CHECK_CUDA_CONTIG(a); CHECK_CUDA_CONTIG(p);
+  TORCH_CHECK(a.dim() == 2 && p.dim() == 2 && p.size(0) == 16 && p.size(1) == a.size(1) &&
+              p.scalar_type() == a.scalar_type(), "proj_right: a [T, K], p [16, K] of the same 16-bit dtype");
+  c10::cuda::CUDAGuard guard(a.device());
+  auto out = at::empty({a.size(0), 16}, a.options().dtype(at::kFloat));
+  check(bgn_proj_right(a.data_ptr(), p.data_ptr(), out.data_ptr<float>(), a.size(0), (int)a.size(1), fmt16(a),
+                       status_ptr(a), stream()), "proj_right");
+  return out;
+}
+
+void proj_left_outer(at::Tensor g, at::Tensor p, at::Tensor a_proj, at::Tensor acc, int64_t col_off) {
+  CHECK_CUDA_CONTIG(g); CHECK_CUDA_CONTIG(p); CHECK_CUDA_CONTIG(a_proj);
+  TORCH_CHECK(g.dim() == 3 && p.size(0) == 16 && p.size(1) == g.size(2) && p.scalar_type() == g.scalar_type());
+  TORCH_CHECK(a_proj.scalar_type() == at::kFloat && a_proj.numel() == g.size(0) * g.size(1) * 16);
+  TORCH_CHECK(acc.scalar_type() == at::kFloat && acc.dim() == 2 && acc.size(0) == g.size(0) && acc.stride(1) == 1 &&
+              col_off + 256 <= acc.size(1));
+  c10::cuda::CUDAGuard guard(g.device());
+  check(bgn_proj_left_outer(g.data_ptr(), p.data_ptr(), a_proj.data_ptr<float>(), acc.data_ptr<float>(),
+                            (int)g.size(0), (int)g.size(1), (int)g.size(2), acc.stride(0), col_off, fmt16(g),
+                            status_ptr(g), stream()), "proj_left_outer");
+}
+
+at::Tensor tn_gemm(at::Tensor a, at::Tensor b) {
+  CHECK_CUDA_CONTIG(a); CHECK_CUDA_CONTIG(b);
+  TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && a.size(1) == b.size(1) && a.scalar_type() == b.scalar_type());
+  c10::cuda::CUDAGuard guard(a.device());
+  auto c = at::empty({a.size(0), b.size(0)}, a.options().dtype(at::kFloat));
+  check(bgn_tn_gemm(a.data_ptr(), b.data_ptr(), c.data_ptr<float>(), a.size(0), (int)b.size(0), (int)a.size(1),
+                    c.stride(0), fmt16(a), status_ptr(a), stream()), "tn_gemm");
+  return c;
+}
+
+void finalize_rows(at::Tensor acc, at::Tensor out, c10::optional<at::Tensor> row_index, double lo, double hi,
+                   bool unit_norm) {
+  TORCH_CHECK(acc.is_cuda() && acc.is_contiguous() && acc.scalar_type() == at::kFloat && acc.dim() == 2);
+  TORCH_CHECK(out.dim() == 2 && out.stride(1) == 1 && out.size(1) >= acc.size(1));
+  // `out` may be device memory or page-locked host memory mapped into the device address space.
+  c10::cuda::CUDAGuard guard(acc.device());
+  const long* idx = nullptr;
+  if (row_index.has_value()) {
+    TORCH_CHECK(row_index->is_cuda() && row_index->scalar_type() == at::kLong && row_index->numel() == acc.size(0));
+    idx = row_index->data_ptr<int64_t>();
+  }
+  check(bgn_finalize_rows(acc.data_ptr<float>(), out.data_ptr(), idx, (int)acc.size(0), acc.size(1), out.stride(0),
+                          (float)lo, (float)hi, unit_norm, type_code(out), stream()), "finalize_rows");
+}
+
+void adamw_step(at::Tensor p, at::Tensor m, at::Tensor v, at::Tensor g, c10::optional<at::Tensor> p_model, double lr,
+                double b1, double b2, double eps, double eps_root, double wd, int64_t step, double grad_scale) {
+  CHECK_CUDA_CONTIG(p); CHECK_CUDA_CONTIG(m); CHECK_CUDA_CONTIG(v); CHECK_CUDA_CONTIG(g);
+  TORCH_CHECK(p.scalar_type() == at::kFloat && m.scalar_type() == at::kFloat && v.scalar_type() == at::kFloat);
+  c10::cuda::CUDAGuard guard(p.device());
+  const float bc1 = 1.f - (float)std::pow(b1, (double)step), bc2 = 1.f - (float)std::pow(b2, (double)step);
+  void* pm = nullptr;
+  int mt = 2;
+  if (p_model.has_value()) {
+    pm = p_model->data_ptr();
+    mt = type_code(*p_model);
+  }
+  check(bgn_adamw_step(p.data_ptr<float>(), m.data_ptr<float>(), v.data_ptr<float>(), g.data_ptr(), pm, p.numel(),
+                       (float)lr, (float)b1, (float)b2, (float)eps, (float)eps_root, (float)wd, bc1, bc2,
+                       (float)grad_scale, type_code(g), mt, stream()), "adamw_step");
+}
+
+void row_sumsq(at::Tensor x, at::Tensor out) {
+  TORCH_CHECK(x.is_cuda() && x.dim() == 2 && x.stride(1) == 1 && out.scalar_type() == at::kFloat &&
+              out.numel() == x.size(0));
+  c10::cuda::CUDAGuard guard(x.device());
+  check(bgn_row_sumsq(x.data_ptr(), out.data_ptr<float>(), x.size(0), x.size(1), x.stride(0), type_code(x), stream()),
+        "row_sumsq");
+}
+
+at::Tensor kernel_status(int64_t device) { return status_tensor((int)device); }
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.def("rmsnorm_fwd", &rmsnorm_fwd);
+  m.def("rmsnorm_bwd", &rmsnorm_bwd);
+  m.def("layernorm_fwd", &layernorm_fwd);
+  m.def("layernorm_bwd", &layernorm_bwd);
+  m.def("rotary", &rotary);
+  m.def("swiglu_fwd", &swiglu_fwd);
+  m.def("swiglu_bwd", &swiglu_bwd);
+  m.def("gelu_fwd", &gelu_fwd);
+  m.def("gelu_bwd", &gelu_bwd);
+  m.def("ce_fwd", &ce_fwd);
+  m.def("ce_bwd", &ce_bwd);
+  m.def("proj_right", &proj_right);
+  m.def("proj_left_outer", &proj_left_outer);
+  m.def("tn_gemm", &tn_gemm);
+  m.def("finalize_rows", &finalize_rows);
+  m.def("adamw_step", &adamw_step);
+  m.def("row_sumsq", &row_sumsq);
+  m.def("kernel_status", &kernel_status);
+}

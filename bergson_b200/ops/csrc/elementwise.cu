@@ -1,0 +1,606 @@
+// Bandwidth-bound model-side kernels: RMSNorm / LayerNorm (fwd, bwd), rotary embedding,
+// SwiGLU / GELU (fwd, bwd), per-token cross entropy (fwd, bwd), fused AdamW, row sum of
+// squares.  16-bit inputs are read with 16-byte vector loads, statistics are kept in fp32.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace bgn {
+
+template <typename T>
+struct Vec {  // 16-byte packet
+  static constexpr int N = 16 / sizeof(T);
+  T v[N];
+};
+
+template <typename T>
+__device__ __forceinline__ Vec<T> load_vec(const T* p) {
+  Vec<T> r;
+  *reinterpret_cast<uint4*>(r.v) = *reinterpret_cast<const uint4*>(p);
+  return r;
+}
+template <typename T>
+__device__ __forceinline__ void store_vec(T* p, const Vec<T>& r) {
+  *reinterpret_cast<uint4*>(p) = *reinterpret_cast<const uint4*>(r.v);
+}
+
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  v = warp_sum(v);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  __syncthreads();
+  if (l == 0) red[w] = v;
+  __syncthreads();
+  float t = l < (blockDim.x >> 5) ? red[l] : 0.f;
+  t = warp_sum(t);
+  return t;
+}
+
+__device__ __forceinline__ float block_max(float v, float* red) {
+  v = warp_max(v);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
+  __syncthreads();
+  if (l == 0) red[w] = v;
+  __syncthreads();
+  float t = l < (blockDim.x >> 5) ? red[l] : -INFINITY;
+  t = warp_max(t);
+  return t;
+}
+
+// ---- RMSNorm --------------------------------------------------------------------------
+// y = T(T(x * rstd) * w): the normalised value is rounded to the activation dtype before the
+// weight multiply, as the eager implementation of the model families does.
+
+template <typename T>
+__global__ void rmsnorm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ w, T* __restrict__ y,
+                                   float* __restrict__ rstd_out, int d, float eps) {
+  __shared__ float red[32];
+  const long r = blockIdx.x;
+  const T* xr = x + r * d;
+  T* yr = y + r * d;
+  constexpr int V = Vec<T>::N;
+  float ss = 0.f;
+  for (int i = threadIdx.x * V; i < d; i += blockDim.x * V) {
+    Vec<T> xv = load_vec(xr + i);
+#pragma unroll
+    for (int k = 0; k < V; ++k) {
+      const float f = to_float<T>(xv.v[k]);
+      ss = fmaf(f, f, ss);
+    }
+  }
+  ss = block_sum(ss, red);
+  const float rstd = rsqrtf(ss / d + eps);
+  if (threadIdx.x == 0) rstd_out[r] = rstd;
+  for (int i = threadIdx.x * V; i < d; i += blockDim.x * V) {
+    Vec<T> xv = load_vec(xr + i), wv = load_vec(w + i), o;
+#pragma unroll
+    for (int k = 0; k < V; ++k) {
+      const float n = to_float<T>(from_float<T>(to_float<T>(xv.v[k]) * rstd));
+      o.v[k] = from_float<T>(n * to_float<T>(wv.v[k]));
+    }
+    store_vec(yr + i, o);
+  }
+}
+
+// dx = rstd * (dy*w - xhat * mean(dy*w*xhat));  dw partials: block b accumulates rows
+// b, b+gridDim, ... into dw_partial[b, :] (summed by the caller).
+template <typename T>
+__global__ void rmsnorm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x,
+                                   const T* __restrict__ w, const float* __restrict__ rstd,
+                                   T* __restrict__ dx, float* __restrict__ dw_partial, long rows,
+                                   int d) {
+  __shared__ float red[32];
+  constexpr int V = Vec<T>::N;
+  constexpr int kMaxPer = 4;  // supports d <= blockDim * V * 4
+  float dw_acc[kMaxPer][V];
+#pragma unroll
+  for (int a = 0; a < kMaxPer; ++a)
+#pragma unroll
+    for (int k = 0; k < V; ++k) dw_acc[a][k] = 0.f;
+
+  for (long r = blockIdx.x; r < rows; r += gridDim.x) {
+    const T* xr = x + r * d;
+    const T* gr = dy + r * d;
+    T* dr = dx + r * d;
+    const float rs = rstd[r];
+    float dot = 0.f;
+    for (int i = threadIdx.x * V; i < d; i += blockDim.x * V) {
+      Vec<T> xv = load_vec(xr + i), gv = load_vec(gr + i), wv = load_vec(w + i);
+#pragma unroll
+      for (int k = 0; k < V; ++k)
+        dot = fmaf(to_float<T>(gv.v[k]) * to_float<T>(wv.v[k]), to_float<T>(xv.v[k]) * rs, dot);
+    }
+    dot = block_sum(dot, red) / d;
+    int a = 0;
+    for (int i = threadIdx.x * V; i < d; i += blockDim.x * V, ++a) {
+      Vec<T> xv = load_vec(xr + i), gv = load_vec(gr + i), wv = load_vec(w + i), o;
+#pragma unroll
+      for (int k = 0; k < V; ++k) {
+        const float xh = to_float<T>(xv.v[k]) * rs;
+        const float g = to_float<T>(gv.v[k]);
+        o.v[k] = from_float<T>(rs * (g * to_float<T>(wv.v[k]) - xh * dot));
+        if (dw_partial && a < kMaxPer) dw_acc[a][k] = fmaf(g, xh, dw_acc[a][k]);
+      }
+      store_vec(dr + i, o);
+    }
+  }
+  if (dw_partial) {
+    int a = 0;
+    for (int i = threadIdx.x * V; i < d && a < kMaxPer; i += blockDim.x * V, ++a)
+#pragma unroll
+      for (int k = 0; k < V; ++k) dw_partial[long(blockIdx.x) * d + i + k] = dw_acc[a][k];
+  }
+}
+
+// ---- LayerNorm ------------------------------------------------------------------------
+
+template <typename T>
+__global__ void layernorm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ w,
+                                     const T* __restrict__ b, T* __restrict__ y,
+                                     float* __restrict__ mean_out, float* __restrict__ rstd_out,
+                                     int d, float eps) {
+  __shared__ float red[32];
+  const long r = blockIdx.x;
+  const T* xr = x + r * d;
+  T* yr = y + r * d;
+  constexpr int V = Vec<T>::N;
+  float s = 0.f;
+  for (int i = threadIdx.x * V; i < d; i += blockDim.x * V) {
+    Vec<T> xv = load_vec(xr + i);
+#pragma unroll
+    for (int k = 0; k < V; ++k) s += to_float<T>(xv.v[k]);
+  }
+  const float mean = block_sum(s, red) / d;
+  float ss = 0.f;
+  for (int i = threadIdx.x * V; i < d; i += blockDim.x * V) {
+    Vec<T> xv = load_vec(xr + i);
+#pragma unroll
+    for (int k = 0; k < V; ++k) {
+      const float c = to_float<T>(xv.v[k]) - mean;
+      ss = fmaf(c, c, ss);
+    }
+  }
+  const float rstd = rsqrtf(block_sum(ss, red) / d + eps);
+  if (threadIdx.x == 0) {
+    mean_out[r] = mean;
+    rstd_out[r] = rstd;
+  }
+  for (int i = threadIdx.x * V; i < d; i += blockDim.x * V) {
+    Vec<T> xv = load_vec(xr + i), wv = load_vec(w + i), o;
+    Vec<T> bv;
+    if (b) bv = load_vec(b + i);
+#pragma unroll
+    for (int k = 0; k < V; ++k) {
+      float v = (to_float<T>(xv.v[k]) - mean) * rstd * to_float<T>(wv.v[k]);
+      if (b) v += to_float<T>(bv.v[k]);
+      o.v[k] = from_float<T>(v);
+    }
+    store_vec(yr + i, o);
+  }
+}
+
+// dx = rstd * (g - mean(g) - xhat * mean(g * xhat)), g = dy * w.
+template <typename T>
+__global__ void layernorm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x,
+                                     const T* __restrict__ w, const float* __restrict__ mean,
+                                     const float* __restrict__ rstd, T* __restrict__ dx,
+                                     float* __restrict__ dw_partial, float* __restrict__ db_partial,
+                                     long rows, int d) {
+  __shared__ float red[32];
+  constexpr int V = Vec<T>::N;
+  constexpr int kMaxPer = 4;
+  float dw_acc[kMaxPer][V], db_acc[kMaxPer][V];
+#pragma unroll
+  for (int a = 0; a < kMaxPer; ++a)
+#pragma unroll
+    for (int k = 0; k < V; ++k) dw_acc[a][k] = db_acc[a][k] = 0.f;
+
+  for (long r = blockIdx.x; r < rows; r += gridDim.x) {
+    const T* xr = x + r * d;
+    const T* gr = dy + r * d;
+    T* dr = dx + r * d;
+    const float mu = mean[r], rs = rstd[r];
+    float s1 = 0.f, s2 = 0.f;
+    for (int i = threadIdx.x * V; i < d; i += blockDim.x * V) {
+      Vec<T> xv = load_vec(xr + i), gv = load_vec(gr + i), wv = load_vec(w + i);
+#pragma unroll
+      for (int k = 0; k < V; ++k) {
+        const float g = to_float<T>(gv.v[k]) * to_float<T>(wv.v[k]);
+        s1 += g;
+        s2 = fmaf(g, (to_float<T>(xv.v[k]) - mu) * rs, s2);
+      }
+    }
+    s1 = block_sum(s1, red) / d;
+    s2 = block_sum(s2, red) / d;
+    int a = 0;
+    for (int i = threadIdx.x * V; i < d; i += blockDim.x * V, ++a) {
+      Vec<T> xv = load_vec(xr + i), gv = load_vec(gr + i), wv = load_vec(w + i), o;
+#pragma unroll
+      for (int k = 0; k < V; ++k) {
+        const float xh = (to_float<T>(xv.v[k]) - mu) * rs;
+        const float gy = to_float<T>(gv.v[k]);
+        const float g = gy * to_float<T>(wv.v[k]);
+        o.v[k] = from_float<T>(rs * (g - s1 - xh * s2));
+        if (dw_partial && a < kMaxPer) {
+          dw_acc[a][k] = fmaf(gy, xh, dw_acc[a][k]);
+          db_acc[a][k] += gy;
+        }
+      }
+      store_vec(dr + i, o);
+    }
+  }
+  if (dw_partial) {
+    int a = 0;
+    for (int i = threadIdx.x * V; i < d && a < kMaxPer; i += blockDim.x * V, ++a)
+#pragma unroll
+      for (int k = 0; k < V; ++k) {
+        dw_partial[long(blockIdx.x) * d + i + k] = dw_acc[a][k];
+        db_partial[long(blockIdx.x) * d + i + k] = db_acc[a][k];
+      }
+  }
+}
+
+// ---- rotary ---------------------------------------------------------------------------
+
+template <typename T>
+__global__ void rotary_kernel(const T* __restrict__ x, const float* __restrict__ cosT,
+                              const float* __restrict__ sinT, T* __restrict__ y, long total_pairs,
+                              int S, int H, int D, int rot, float sign) {
+  // One thread per (b, s, h, i) with i in [0, D/2): handles features i and i + D/2 when inside
+  // the rotated prefix (pairs are (i, i + rot/2) for i < rot/2); copies the rest.
+  const int half = rot >> 1;
+  const long per_head = D - half;  // threads per head: rot/2 pairs + (D - rot) pass-through
+  for (long idx = blockIdx.x * long(blockDim.x) + threadIdx.x; idx < total_pairs;
+       idx += long(gridDim.x) * blockDim.x) {
+    const long head = idx / per_head;
+    const int i = int(idx - head * per_head);
+    const int s = int((head / H) % S);
+    const T* xp = x + head * D;
+    T* yp = y + head * D;
+    if (i < half) {
+      const float c = cosT[long(s) * half + i], sn = sinT[long(s) * half + i] * sign;
+      const float a = to_float<T>(xp[i]), b = to_float<T>(xp[i + half]);
+      yp[i] = from_float<T>(a * c - b * sn);
+      yp[i + half] = from_float<T>(b * c + a * sn);
+    } else {
+      yp[i + half] = xp[i + half];
+    }
+  }
+}
+
+// ---- activations ----------------------------------------------------------------------
+
+__device__ __forceinline__ float sigmoidf_(float x) { return 1.f / (1.f + __expf(-x)); }
+
+template <typename T>
+__global__ void swiglu_fwd_kernel(const T* __restrict__ g, const T* __restrict__ u, T* __restrict__ y,
+                                  long n) {
+  constexpr int V = Vec<T>::N;
+  for (long i = (blockIdx.x * long(blockDim.x) + threadIdx.x) * V; i < n;
+       i += long(gridDim.x) * blockDim.x * V) {
+    Vec<T> gv = load_vec(g + i), uv = load_vec(u + i), o;
+#pragma unroll
+    for (int k = 0; k < V; ++k) {
+      const float a = to_float<T>(gv.v[k]);
+      // silu rounded to the activation dtype before the product, as an eager silu(g) * u is.
+      const float s = to_float<T>(from_float<T>(a * sigmoidf_(a)));
+      o.v[k] = from_float<T>(s * to_float<T>(uv.v[k]));
+    }
+    store_vec(y + i, o);
+  }
+}
+
+template <typename T>
+__global__ void swiglu_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ g,
+                                  const T* __restrict__ u, T* __restrict__ dg, T* __restrict__ du,
+                                  long n) {
+  constexpr int V = Vec<T>::N;
+  for (long i = (blockIdx.x * long(blockDim.x) + threadIdx.x) * V; i < n;
+       i += long(gridDim.x) * blockDim.x * V) {
+    Vec<T> yv = load_vec(dy + i), gv = load_vec(g + i), uv = load_vec(u + i), og, ou;
+#pragma unroll
+    for (int k = 0; k < V; ++k) {
+      const float a = to_float<T>(gv.v[k]), d = to_float<T>(yv.v[k]), b = to_float<T>(uv.v[k]);
+      const float sg = sigmoidf_(a);
+      ou.v[k] = from_float<T>(d * a * sg);
+      og.v[k] = from_float<T>(d * b * sg * (1.f + a * (1.f - sg)));
+    }
+    store_vec(dg + i, og);
+    store_vec(du + i, ou);
+  }
+}
+
+__device__ __forceinline__ float gelu_f(float x, bool tanh_approx) {
+  if (tanh_approx) {
+    const float k = 0.7978845608028654f;
+    return 0.5f * x * (1.f + tanhf(k * (x + 0.044715f * x * x * x)));
+  }
+  return 0.5f * x * (1.f + erff(x * 0.7071067811865476f));
+}
+
+__device__ __forceinline__ float gelu_grad_f(float x, bool tanh_approx) {
+  if (tanh_approx) {
+    const float k = 0.7978845608028654f;
+    const float t = tanhf(k * (x + 0.044715f * x * x * x));
+    return 0.5f * (1.f + t) + 0.5f * x * (1.f - t * t) * k * (1.f + 3.f * 0.044715f * x * x);
+  }
+  const float cdf = 0.5f * (1.f + erff(x * 0.7071067811865476f));
+  return cdf + x * 0.3989422804014327f * __expf(-0.5f * x * x);
+}
+
+template <typename T>
+__global__ void gelu_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, long n, int tanh_approx) {
+  constexpr int V = Vec<T>::N;
+  for (long i = (blockIdx.x * long(blockDim.x) + threadIdx.x) * V; i < n;
+       i += long(gridDim.x) * blockDim.x * V) {
+    Vec<T> xv = load_vec(x + i), o;
+#pragma unroll
+    for (int k = 0; k < V; ++k) o.v[k] = from_float<T>(gelu_f(to_float<T>(xv.v[k]), tanh_approx));
+    store_vec(y + i, o);
+  }
+}
+
+template <typename T>
+__global__ void gelu_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x, T* __restrict__ dx,
+                                long n, int tanh_approx) {
+  constexpr int V = Vec<T>::N;
+  for (long i = (blockIdx.x * long(blockDim.x) + threadIdx.x) * V; i < n;
+       i += long(gridDim.x) * blockDim.x * V) {
+    Vec<T> xv = load_vec(x + i), gv = load_vec(dy + i), o;
+#pragma unroll
+    for (int k = 0; k < V; ++k)
+      o.v[k] = from_float<T>(to_float<T>(gv.v[k]) * gelu_grad_f(to_float<T>(xv.v[k]), tanh_approx));
+    store_vec(dx + i, o);
+  }
+}
+
+// ---- cross entropy --------------------------------------------------------------------
+
+template <typename T>
+__global__ void ce_fwd_kernel(const T* __restrict__ logits, const long* __restrict__ targets,
+                              float* __restrict__ loss, float* __restrict__ lse_out, int V_,
+                              long ignore_index) {
+  __shared__ float red[32];
+  const long r = blockIdx.x;
+  const T* z = logits + r * V_;
+  constexpr int V = Vec<T>::N;
+  const bool vec_ok = (V_ % V) == 0;
+  float m = -INFINITY, s = 0.f;  // online softmax statistics
+  auto push = [&](float f) {
+    if (f > m) {
+      s = s * __expf(m - f) + 1.f;
+      m = f;
+    } else {
+      s += __expf(f - m);
+    }
+  };
+  if (vec_ok) {
+    for (int i = threadIdx.x * V; i < V_; i += blockDim.x * V) {
+      Vec<T> zv = load_vec(z + i);
+#pragma unroll
+      for (int k = 0; k < V; ++k) push(to_float<T>(zv.v[k]));
+    }
+  } else {
+    for (int i = threadIdx.x; i < V_; i += blockDim.x) push(to_float<T>(z[i]));
+  }
+  const float gm = block_max(m, red);
+  const float contrib = (m == -INFINITY) ? 0.f : s * __expf(m - gm);
+  const float gs = block_sum(contrib, red);
+  if (threadIdx.x == 0) {
+    const float lse = gm + logf(gs);
+    lse_out[r] = lse;
+    const long t = targets[r];
+    loss[r] = (t == ignore_index) ? 0.f : lse - to_float<T>(z[t]);
+  }
+}
+
+template <typename T>
+__global__ void ce_bwd_kernel(const T* __restrict__ logits, const long* __restrict__ targets,
+                              const float* __restrict__ lse, const float* __restrict__ dloss,
+                              T* __restrict__ dlogits, int V_, long ignore_index) {
+  const long r = blockIdx.x;
+  const T* z = logits + r * V_;
+  T* dz = dlogits + r * V_;
+  const long t = targets[r];
+  const float g = (t == ignore_index) ? 0.f : dloss[r];
+  const float l = lse[r];
+  constexpr int V = Vec<T>::N;
+  if ((V_ % V) == 0) {
+    for (int i = threadIdx.x * V; i < V_; i += blockDim.x * V) {
+      Vec<T> zv = load_vec(z + i), o;
+#pragma unroll
+      for (int k = 0; k < V; ++k) {
+        float p = __expf(to_float<T>(zv.v[k]) - l);
+        if (i + k == t) p -= 1.f;
+        o.v[k] = from_float<T>(p * g);
+      }
+      store_vec(dz + i, o);
+    }
+  } else {
+    for (int i = threadIdx.x; i < V_; i += blockDim.x) {
+      float p = __expf(to_float<T>(z[i]) - l);
+      if (i == t) p -= 1.f;
+      dz[i] = from_float<T>(p * g);
+    }
+  }
+}
+
+// ---- AdamW ----------------------------------------------------------------------------
+
+template <typename G, typename M>
+__global__ void adamw_kernel(float* __restrict__ p, float* __restrict__ m, float* __restrict__ v,
+                             const G* __restrict__ g, M* __restrict__ pm, long n, float lr, float b1,
+                             float b2, float eps, float eps_root, float wd, float bc1, float bc2,
+                             float gscale) {
+  for (long i = blockIdx.x * long(blockDim.x) + threadIdx.x; i < n;
+       i += long(gridDim.x) * blockDim.x) {
+    const float gi = to_float<G>(g[i]) * gscale;
+    const float mi = b1 * m[i] + (1.f - b1) * gi;
+    const float vi = b2 * v[i] + (1.f - b2) * gi * gi;
+    m[i] = mi;
+    v[i] = vi;
+    const float upd = (mi / bc1) / (sqrtf(vi / bc2 + eps_root) + eps) + wd * p[i];
+    const float pi = p[i] - lr * upd;
+    p[i] = pi;
+    if (pm) pm[i] = from_float<M>(pi);
+  }
+}
+
+template <typename T>
+__global__ void row_sumsq_kernel(const T* __restrict__ x, float* __restrict__ out, long d, long ldx) {
+  __shared__ float red[32];
+  const long r = blockIdx.x;
+  const T* xr = x + r * ldx;
+  float ss = 0.f;
+  for (long i = threadIdx.x; i < d; i += blockDim.x) {
+    const float f = to_float<T>(xr[i]);
+    ss = fmaf(f, f, ss);
+  }
+  ss = block_sum(ss, red);
+  if (threadIdx.x == 0) out[r] += ss;
+}
+
+static inline int grid_for(long n, int per_block) {
+  long b = (n + per_block - 1) / per_block;
+  const long cap = 148L * 16;
+  return int(b < 1 ? 1 : (b > cap ? cap : b));
+}
+
+}  // namespace bgn
+
+using namespace bgn;
+
+#define BGN_DISPATCH(type, ...)                         \
+  switch (type) {                                       \
+    case 0: { using T = __half; __VA_ARGS__; break; }   \
+    case 1: { using T = __nv_bfloat16; __VA_ARGS__; break; } \
+    case 2: { using T = float; __VA_ARGS__; break; }    \
+    default: return int(cudaErrorInvalidValue);         \
+  }
+
+static inline int vec_threads(int d, int vec) {
+  int t = (d / vec + 31) / 32 * 32;
+  return t < 32 ? 32 : (t > 512 ? 512 : t);
+}
+
+extern "C" int bgn_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, long rows, int d,
+                               float eps, int type, cudaStream_t st) {
+  BGN_DISPATCH(type, {
+    if (d % Vec<T>::N) return int(cudaErrorInvalidValue);
+    rmsnorm_fwd_kernel<T><<<rows, vec_threads(d, Vec<T>::N), 0, st>>>((const T*)x, (const T*)w, (T*)y, rstd, d, eps);
+  });
+  return int(cudaGetLastError());
+}
+
+extern "C" int bgn_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd,
+                               void* dx, float* dw_partial, int n_partial, long rows, int d, int type,
+                               cudaStream_t st) {
+  BGN_DISPATCH(type, {
+    const int threads = vec_threads(d, Vec<T>::N);
+    if (d % Vec<T>::N || (dw_partial && d > threads * Vec<T>::N * 4)) return int(cudaErrorInvalidValue);
+    const int grid = dw_partial ? n_partial : int(rows < 148L * 8 ? rows : 148L * 8);
+    rmsnorm_bwd_kernel<T><<<grid, threads, 0, st>>>((const T*)dy, (const T*)x, (const T*)w, rstd, (T*)dx, dw_partial, rows, d);
+  });
+  return int(cudaGetLastError());
+}
+
+extern "C" int bgn_layernorm_fwd(const void* x, const void* w, const void* b, void* y, float* mean,
+                                 float* rstd, long rows, int d, float eps, int type, cudaStream_t st) {
+  BGN_DISPATCH(type, {
+    if (d % Vec<T>::N) return int(cudaErrorInvalidValue);
+    layernorm_fwd_kernel<T><<<rows, vec_threads(d, Vec<T>::N), 0, st>>>((const T*)x, (const T*)w, (const T*)b, (T*)y, mean, rstd, d, eps);
+  });
+  return int(cudaGetLastError());
+}
+
+extern "C" int bgn_layernorm_bwd(const void* dy, const void* x, const void* w, const float* mean,
+                                 const float* rstd, void* dx, float* dw_partial, float* db_partial,
+                                 int n_partial, long rows, int d, int type, cudaStream_t st) {
+  BGN_DISPATCH(type, {
+    const int threads = vec_threads(d, Vec<T>::N);
+    if (d % Vec<T>::N || (dw_partial && d > threads * Vec<T>::N * 4)) return int(cudaErrorInvalidValue);
+    const int grid = dw_partial ? n_partial : int(rows < 148L * 8 ? rows : 148L * 8);
+    layernorm_bwd_kernel<T><<<grid, threads, 0, st>>>((const T*)dy, (const T*)x, (const T*)w, mean, rstd, (T*)dx, dw_partial, db_partial, rows, d);
+  });
+  return int(cudaGetLastError());
+}
+
+extern "C" int bgn_rotary(const void* x, const float* cosT, const float* sinT, void* y, long B, int S,
+                          int H, int D, int rot, int inverse, int type, cudaStream_t st) {
+  const long heads = B * S * H;
+  const long total = heads * (D - rot / 2);
+  BGN_DISPATCH(type, {
+    rotary_kernel<T><<<grid_for(total, 256), 256, 0, st>>>((const T*)x, cosT, sinT, (T*)y, total, S, H, D, rot, inverse ? -1.f : 1.f);
+  });
+  return int(cudaGetLastError());
+}
+
+extern "C" int bgn_swiglu_fwd(const void* g, const void* u, void* y, long n, int type, cudaStream_t st) {
+  BGN_DISPATCH(type, {
+    if (n % Vec<T>::N) return int(cudaErrorInvalidValue);
+    swiglu_fwd_kernel<T><<<grid_for(n, 256 * Vec<T>::N), 256, 0, st>>>((const T*)g, (const T*)u, (T*)y, n);
+  });
+  return int(cudaGetLastError());
+}
+
+extern "C" int bgn_swiglu_bwd(const void* dy, const void* g, const void* u, void* dg, void* du, long n,
+                              int type, cudaStream_t st) {
+  BGN_DISPATCH(type, {
+    if (n % Vec<T>::N) return int(cudaErrorInvalidValue);
+    swiglu_bwd_kernel<T><<<grid_for(n, 256 * Vec<T>::N), 256, 0, st>>>((const T*)dy, (const T*)g, (const T*)u, (T*)dg, (T*)du, n);
+  });
+  return int(cudaGetLastError());
+}
+
+extern "C" int bgn_gelu_fwd(const void* x, void* y, long n, int tanh_approx, int type, cudaStream_t st) {
+  BGN_DISPATCH(type, {
+    if (n % Vec<T>::N) return int(cudaErrorInvalidValue);
+    gelu_fwd_kernel<T><<<grid_for(n, 256 * Vec<T>::N), 256, 0, st>>>((const T*)x, (T*)y, n, tanh_approx);
+  });
+  return int(cudaGetLastError());
+}
+
+extern "C" int bgn_gelu_bwd(const void* dy, const void* x, void* dx, long n, int tanh_approx, int type,
+                            cudaStream_t st) {
+  BGN_DISPATCH(type, {
+    if (n % Vec<T>::N) return int(cudaErrorInvalidValue);
+    gelu_bwd_kernel<T><<<grid_for(n, 256 * Vec<T>::N), 256, 0, st>>>((const T*)dy, (const T*)x, (T*)dx, n, tanh_approx);
+  });
+  return int(cudaGetLastError());
+}
+
+extern "C" int bgn_ce_fwd(const void* logits, const long* targets, float* loss, float* lse, long T_,
+                          int V, long ignore_index, int type, cudaStream_t st) {
+  BGN_DISPATCH(type, {
+    ce_fwd_kernel<T><<<T_, 512, 0, st>>>((const T*)logits, targets, loss, lse, V, ignore_index);
+  });
+  return int(cudaGetLastError());
+}
+
+extern "C" int bgn_ce_bwd(const void* logits, const long* targets, const float* lse, const float* dloss,
+                          void* dlogits, long T_, int V, long ignore_index, int type, cudaStream_t st) {
+  BGN_DISPATCH(type, {
+    ce_bwd_kernel<T><<<T_, 512, 0, st>>>((const T*)logits, targets, lse, dloss, (T*)dlogits, V, ignore_index);
+  });
+  return int(cudaGetLastError());
+}
+
+extern "C" int bgn_adamw_step(float* p, float* m, float* v, const void* g, void* pm, long n, float lr,
+                              float b1, float b2, float eps, float eps_root, float wd, float bc1,
+                              float bc2, float gscale, int g_type, int model_type, cudaStream_t st) {
+  const int grid = grid_for(n, 256);
+#define ADAM_LAUNCH(G, M) \
+  adamw_kernel<G, M><<<grid, 256, 0, st>>>(p, m, v, (const G*)g, (M*)pm, n, lr, b1, b2, eps, eps_root, wd, bc1, bc2, gscale)
+  if (g_type == 1 && model_type == 1) ADAM_LAUNCH(__nv_bfloat16, __nv_bfloat16);
+  else if (g_type == 2 && model_type == 1) ADAM_LAUNCH(float, __nv_bfloat16);
+  else if (g_type == 2 && model_type == 2) ADAM_LAUNCH(float, float);
+  else if (g_type == 0 && model_type == 0) ADAM_LAUNCH(__half, __half);
+  else if (g_type == 2 && model_type == 0) ADAM_LAUNCH(float, __half);
+  else return int(cudaErrorInvalidValue);
+#undef ADAM_LAUNCH
+  return int(cudaGetLastError());
+}
+
+extern "C" int bgn_row_sumsq(const void* x, float* out, long rows, long d, long ldx, int type,
+                             cudaStream_t st) {
+  BGN_DISPATCH(type, { row_sumsq_kernel<T><<<rows, 256, 0, st>>>((const T*)x, out, d, ldx); });
+  return int(cudaGetLastError());
+}

@@ -1,0 +1,70 @@
+// C launch interface of the sm_100a kernels.  Every launcher enqueues on `stream`, never
+// synchronises, and returns a cudaError_t (as int).  `fmt` selects the 16-bit input type:
+// 0 = fp16, 1 = bf16; element type codes for the elementwise kernels: 0 = fp16, 1 = bf16,
+// 2 = fp32.  `status` points at a device int that kernels set to a non-zero KernelStatus
+// when one of their bounded waits runs out.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+extern "C" {
+
+// ---- attribution (tcgen05 + TMA) ------------------------------------------------------
+
+// out[T, 16] (fp32) = a[T, K] * p[16, K]^T.          (K multiple of 8, a/p 16-byte aligned)
+int bgn_proj_right(const void* a, const void* p, float* out, long T, int K, int fmt, int* status,
+                   cudaStream_t stream);
+
+// acc[n, col_off + i*16 + j] += sum_s (g[n, s, :] . p[i, :]) * a_proj[n*S + s, j]
+// g: [N, S, K] 16-bit, p: [16, K], a_proj: [N*S, 16] fp32, acc: [N, ld] fp32 (pre-zeroed by
+// the caller at the start of a batch; this kernel only adds).
+int bgn_proj_left_outer(const void* g, const void* p, const float* a_proj, float* acc, int N, int S,
+                        int K, long ld, long col_off, int fmt, int* status, cudaStream_t stream);
+
+// c[M, N] (fp32, row stride ldc) = a[M, K] * b[N, K]^T; optional row_sumsq[M] += sum_k a^2 is
+// not computed here (see bgn_row_sumsq).
+int bgn_tn_gemm(const void* a, const void* b, float* c, long M, int N, int K, long ldc, int fmt,
+                int* status, cudaStream_t stream);
+
+// acc fp32 [N, D] -> out rows (type code `out_type`) with clamp to [lo, hi]; if unit_norm,
+// every row is divided by max(||row||, eps) computed on the rounded values.  Row r goes to
+// out + row_index[r] * out_ld (row_index == nullptr means r).
+int bgn_finalize_rows(const float* acc, void* out, const long* row_index, int N, long D, long out_ld,
+                      float lo, float hi, int unit_norm, int out_type, cudaStream_t stream);
+
+// ---- model-side elementwise -----------------------------------------------------------
+
+int bgn_rmsnorm_fwd(const void* x, const void* w, void* y, float* rstd, long rows, int d, float eps,
+                    int type, cudaStream_t stream);
+int bgn_rmsnorm_bwd(const void* dy, const void* x, const void* w, const float* rstd, void* dx,
+                    float* dw_partial, int n_partial, long rows, int d, int type,
+                    cudaStream_t stream);
+int bgn_layernorm_fwd(const void* x, const void* w, const void* b, void* y, float* mean, float* rstd,
+                      long rows, int d, float eps, int type, cudaStream_t stream);
+int bgn_layernorm_bwd(const void* dy, const void* x, const void* w, const float* mean,
+                      const float* rstd, void* dx, float* dw_partial, float* db_partial,
+                      int n_partial, long rows, int d, int type, cudaStream_t stream);
+// x: [B, S, H, D]; cos/sin: [S, rot/2] fp32; rotate-half on the first `rot` features.
+int bgn_rotary(const void* x, const float* cos, const float* sin, void* y, long B, int S, int H,
+               int D, int rot, int inverse, int type, cudaStream_t stream);
+int bgn_swiglu_fwd(const void* gate, const void* up, void* y, long n, int type, cudaStream_t stream);
+int bgn_swiglu_bwd(const void* dy, const void* gate, const void* up, void* dgate, void* dup, long n,
+                   int type, cudaStream_t stream);
+int bgn_gelu_fwd(const void* x, void* y, long n, int tanh_approx, int type, cudaStream_t stream);
+int bgn_gelu_bwd(const void* dy, const void* x, void* dx, long n, int tanh_approx, int type,
+                 cudaStream_t stream);
+// logits [T, V]; loss[T], lse[T] fp32; targets int64 (ignore_index -> loss 0).
+int bgn_ce_fwd(const void* logits, const long* targets, float* loss, float* lse, long T, int V,
+               long ignore_index, int type, cudaStream_t stream);
+int bgn_ce_bwd(const void* logits, const long* targets, const float* lse, const float* dloss,
+               void* dlogits, long T, int V, long ignore_index, int type, cudaStream_t stream);
+// Fused AdamW on flat fp32 master state; writes the 16-bit/32-bit model copy as well.
+int bgn_adamw_step(float* p, float* m, float* v, const void* g, void* p_model, long n, float lr,
+                   float b1, float b2, float eps, float eps_root, float wd, float bc1, float bc2,
+                   float grad_scale, int g_type, int model_type, cudaStream_t stream);
+// out[r] += sum_k x[r, k]^2  (x 16-bit or fp32).
+int bgn_row_sumsq(const void* x, float* out, long rows, long d, long ldx, int type,
+                  cudaStream_t stream);
+
+}  // extern "C"

@@ -1,0 +1,299 @@
+"""Model-side ops with two execution paths.
+
+* **fused** (default on CUDA): each op is one hand-written sm_100a kernel for the
+  forward and one for the backward, wrapped in an ``autograd.Function``.  The
+  backward kernels are not themselves differentiable.
+* **composable**: the op is written with differentiable torch primitives so that
+  ``create_graph=True`` works to any order.  This is the CPU path and the path the
+  twice-differentiable trainer selects with ``ops.composable()``.
+
+The numerics of both paths are the same formulas; GPU tests compare each kernel
+against the composable expression evaluated in fp32.
+"""
+
+from __future__ import annotations
+
+import contextlib
+import math
+import threading
+
+import torch
+import torch.nn.functional as F
+from torch import Tensor
+
+_state = threading.local()
+
+
+def _composable() -> bool:
+    return getattr(_state, "composable", False)
+
+
+@contextlib.contextmanager
+def composable(enabled: bool = True):
+    """Force the any-order-differentiable torch path inside the block."""
+    prev = _composable()
+    _state.composable = enabled
+    try:
+        yield
+    finally:
+        _state.composable = prev
+
+
+def use_fused(*tensors: Tensor) -> bool:
+    """True when the fused CUDA kernels should run for these operands."""
+    if _composable():
+        return False
+    if not all(t.is_cuda for t in tensors if t is not None):
+        return False
+    from . import native
+
+    return native.available()
+
+
+# --------------------------------------------------------------------------- #
+# normalisation
+# --------------------------------------------------------------------------- #
+
+
+def rms_norm_ref(x: Tensor, weight: Tensor, eps: float) -> Tensor:
+    xf = x.float()
+    y = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)
+    return (y.to(x.dtype)) * weight
+
+
+class _RMSNormFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, eps):
+        from . import native
+
+        x2 = x.reshape(-1, x.shape[-1]).contiguous()
+        y, rstd = native.rmsnorm_fwd(x2, weight, eps)
+        ctx.save_for_backward(x2, weight, rstd)
+        ctx.shape = x.shape
+        return y.view(x.shape)
+
+    @staticmethod
+    def backward(ctx, dy):
+        from . import native
+
+        x2, weight, rstd = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1]).contiguous()
+        dx, dw = native.rmsnorm_bwd(dy2, x2, weight, rstd, ctx.needs_input_grad[1])
+        return dx.view(ctx.shape), dw, None
+
+
+def rms_norm(x: Tensor, weight: Tensor, eps: float) -> Tensor:
+    if use_fused(x, weight) and x.dtype in (torch.bfloat16, torch.float16, torch.float32):
+        return _RMSNormFn.apply(x, weight, eps)
+    return rms_norm_ref(x, weight, eps)
+
+
+def layer_norm_ref(x: Tensor, weight: Tensor, bias: Tensor | None, eps: float) -> Tensor:
+    return F.layer_norm(x, (x.shape[-1],), weight, bias, eps)
+
+
+class _LayerNormFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, bias, eps):
+        from . import native
+
+        x2 = x.reshape(-1, x.shape[-1]).contiguous()
+        y, mean, rstd = native.layernorm_fwd(x2, weight, bias, eps)
+        ctx.save_for_backward(x2, weight, mean, rstd)
+        ctx.shape = x.shape
+        ctx.has_bias = bias is not None
+        return y.view(x.shape)
+
+    @staticmethod
+    def backward(ctx, dy):
+        from . import native
+
+        x2, weight, mean, rstd = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1]).contiguous()
+        need_w = ctx.needs_input_grad[1] or (ctx.has_bias and ctx.needs_input_grad[2])
+        dx, dw, db = native.layernorm_bwd(dy2, x2, weight, mean, rstd, need_w)
+        return dx.view(ctx.shape), dw, (db if ctx.has_bias else None), None
+
+
+def layer_norm(x: Tensor, weight: Tensor, bias: Tensor | None, eps: float) -> Tensor:
+    if use_fused(x, weight) and x.dtype in (torch.bfloat16, torch.float16, torch.float32):
+        return _LayerNormFn.apply(x, weight, bias, eps)
+    return layer_norm_ref(x, weight, bias, eps)
+
+
+# --------------------------------------------------------------------------- #
+# rotary embedding (rotate-half convention, optional partial rotation)
+# --------------------------------------------------------------------------- #
+
+
+def rotary_tables(seq_len: int, rot_dim: int, theta: float, device, dtype=torch.float32):
+    inv = 1.0 / (theta ** (torch.arange(0, rot_dim, 2, device=device, dtype=torch.float32) / rot_dim))
+    ang = torch.outer(torch.arange(seq_len, device=device, dtype=torch.float32), inv)
+    return ang.cos().to(dtype), ang.sin().to(dtype)  # [S, rot_dim/2]
+
+
+def rotary_ref(x: Tensor, cos: Tensor, sin: Tensor, rot_dim: int) -> Tensor:
+    """x: [B, S, H, D]; rotate the first ``rot_dim`` features of each head."""
+    half = rot_dim // 2
+    c = cos[None, : x.shape[1], None, :].to(x.dtype)
+    s = sin[None, : x.shape[1], None, :].to(x.dtype)
+    x1, x2, rest = x[..., :half], x[..., half:rot_dim], x[..., rot_dim:]
+    return torch.cat([x1 * c - x2 * s, x2 * c + x1 * s, rest], dim=-1)
+
+
+class _RotaryFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, cos, sin, rot_dim):
+        from . import native
+
+        ctx.save_for_backward(cos, sin)
+        ctx.rot_dim = rot_dim
+        return native.rotary(x.contiguous(), cos, sin, rot_dim, False)
+
+    @staticmethod
+    def backward(ctx, dy):
+        from . import native
+
+        cos, sin = ctx.saved_tensors
+        return native.rotary(dy.contiguous(), cos, sin, ctx.rot_dim, True), None, None, None
+
+
+def rotary(x: Tensor, cos: Tensor, sin: Tensor, rot_dim: int) -> Tensor:
+    if use_fused(x) and x.dtype in (torch.bfloat16, torch.float16, torch.float32):
+        return _RotaryFn.apply(x, cos, sin, rot_dim)
+    return rotary_ref(x, cos, sin, rot_dim)
+
+
+# --------------------------------------------------------------------------- #
+# MLP activations
+# --------------------------------------------------------------------------- #
+
+
+def swiglu_ref(gate: Tensor, up: Tensor) -> Tensor:
+    return F.silu(gate) * up
+
+
+class _SwiGLUFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, gate, up):
+        from . import native
+
+        ctx.save_for_backward(gate, up)
+        return native.swiglu_fwd(gate.contiguous(), up.contiguous())
+
+    @staticmethod
+    def backward(ctx, dy):
+        from . import native
+
+        gate, up = ctx.saved_tensors
+        return native.swiglu_bwd(dy.contiguous(), gate.contiguous(), up.contiguous())
+
+
+def swiglu(gate: Tensor, up: Tensor) -> Tensor:
+    if use_fused(gate, up) and gate.dtype in (torch.bfloat16, torch.float16, torch.float32):
+        return _SwiGLUFn.apply(gate, up)
+    return swiglu_ref(gate, up)
+
+
+def gelu_ref(x: Tensor, approximate: str = "none") -> Tensor:
+    return F.gelu(x, approximate=approximate)
+
+
+class _GELUFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, tanh_approx):
+        from . import native
+
+        ctx.save_for_backward(x)
+        ctx.tanh_approx = tanh_approx
+        return native.gelu_fwd(x.contiguous(), tanh_approx)
+
+    @staticmethod
+    def backward(ctx, dy):
+        from . import native
+
+        (x,) = ctx.saved_tensors
+        return native.gelu_bwd(dy.contiguous(), x.contiguous(), ctx.tanh_approx), None
+
+
+def gelu(x: Tensor, approximate: str = "none") -> Tensor:
+    if use_fused(x) and x.dtype in (torch.bfloat16, torch.float16, torch.float32):
+        return _GELUFn.apply(x, approximate == "tanh")
+    return gelu_ref(x, approximate)
+
+
+# --------------------------------------------------------------------------- #
+# attention
+# --------------------------------------------------------------------------- #
+
+
+def causal_attention(q: Tensor, k: Tensor, v: Tensor, scale: float | None = None) -> Tensor:
+    """q: [B, Hq, S, D]; k, v: [B, Hkv, S, D] (Hq a multiple of Hkv). Causal."""
+    B, Hq, S, D = q.shape
+    Hkv = k.shape[1]
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    if _composable() or not q.is_cuda:
+        # Explicit softmax(QK^T)V: differentiable to any order on every backend.
+        if Hkv != Hq:
+            rep = Hq // Hkv
+            k = k.repeat_interleave(rep, dim=1)
+            v = v.repeat_interleave(rep, dim=1)
+        att = torch.matmul(q, k.transpose(-1, -2)) * scale
+        mask = torch.ones(S, S, dtype=torch.bool, device=q.device).tril()
+        att = att.masked_fill(~mask, float("-inf"))
+        att = torch.softmax(att.float(), dim=-1).to(q.dtype)
+        return torch.matmul(att, v)
+    return F.scaled_dot_product_attention(
+        q, k, v, is_causal=True, scale=scale, enable_gqa=(Hkv != Hq)
+    )
+
+
+# --------------------------------------------------------------------------- #
+# cross entropy on logits (per-token losses)
+# --------------------------------------------------------------------------- #
+
+
+def token_cross_entropy_ref(
+    logits: Tensor, targets: Tensor, ignore_index: int = -100, label_smoothing: float = 0.0
+) -> Tensor:
+    z = logits if logits.dtype == torch.float64 else logits.float()
+    return F.cross_entropy(
+        z, targets, reduction="none", ignore_index=ignore_index, label_smoothing=label_smoothing
+    )
+
+
+class _TokenCEFn(torch.autograd.Function):
+    """Per-row CE over ``[T, V]`` logits: one pass computes loss and log-sum-exp;
+    the backward rewrites ``(softmax - onehot) * dloss`` in one pass, in the logits'
+    own dtype, without an fp32 ``[T, V]`` intermediate."""
+
+    @staticmethod
+    def forward(ctx, logits, targets, ignore_index):
+        from . import native
+
+        logits = logits.contiguous()
+        loss, lse = native.ce_fwd(logits, targets, ignore_index)
+        ctx.save_for_backward(logits, targets, lse)
+        ctx.ignore_index = ignore_index
+        return loss
+
+    @staticmethod
+    def backward(ctx, dloss):
+        from . import native
+
+        logits, targets, lse = ctx.saved_tensors
+        dlogits = native.ce_bwd(logits, targets, lse, dloss.contiguous().float(), ctx.ignore_index)
+        return dlogits, None, None
+
+
+def token_cross_entropy(
+    logits: Tensor, targets: Tensor, ignore_index: int = -100, label_smoothing: float = 0.0
+) -> Tensor:
+    """``[T, V]`` logits, ``[T]`` targets -> ``[T]`` fp32 losses (0 where ignored)."""
+    if (
+        label_smoothing == 0.0
+        and use_fused(logits)
+        and logits.dtype in (torch.bfloat16, torch.float16, torch.float32)
+    ):
+        return _TokenCEFn.apply(logits, targets, ignore_index)
+    return token_cross_entropy_ref(logits, targets, ignore_index, label_smoothing)

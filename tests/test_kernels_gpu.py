@@ -1,0 +1,174 @@
+"""Each sm_100a kernel against a plain PyTorch fp32 expression of the same op."""
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def native():
+    from bergson_b200.ops import native as n
+
+    assert n.available()
+    return n
+
+
+def _status_ok(native):
+    torch.cuda.synchronize()
+    assert int(native.kernel_status(0).item()) == 0
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("T,K", [(128, 64), (300, 136), (1024, 768), (4099, 4096)])
+def test_proj_right(native, dtype, T, K):
+    torch.manual_seed(0)
+    a = torch.randn(T, K, device="cuda", dtype=dtype)
+    p = (torch.randn(16, K, device="cuda") / 4).to(dtype)
+    out = native.proj_right(a, p)
+    ref = a.float() @ p.float().T
+    _status_ok(native)
+    torch.testing.assert_close(out, ref, atol=2e-2 * (K / 64) ** 0.5, rtol=1e-2)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("N,S,K", [(1, 128, 64), (3, 77, 72), (2, 300, 512), (4, 1024, 3072)])
+def test_proj_left_outer(native, dtype, N, S, K):
+    torch.manual_seed(1)
+    g = torch.randn(N, S, K, device="cuda", dtype=dtype)
+    p = (torch.randn(16, K, device="cuda") / 4).to(dtype)
+    a_proj = torch.randn(N * S, 16, device="cuda")
+    acc = torch.zeros(N, 3 * 256, device="cuda")
+    native.proj_left_outer(g, p, a_proj, acc, 256)
+    gp = g.float() @ p.float().T  # [N, S, 16]
+    ref = torch.einsum("nsi,nsj->nij", gp, a_proj.view(N, S, 16)).reshape(N, 256)
+    _status_ok(native)
+    scale = ref.abs().max().item()
+    torch.testing.assert_close(acc[:, 256:512], ref, atol=2e-3 * scale, rtol=1e-2)
+    assert acc[:, :256].abs().max().item() == 0 and acc[:, 512:].abs().max().item() == 0
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (200, 72, 264), (1000, 1024, 4096)])
+def test_tn_gemm(native, M, N, K):
+    torch.manual_seed(2)
+    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    b = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
+    c = native.tn_gemm(a, b)
+    ref = a.float() @ b.float().T
+    _status_ok(native)
+    torch.testing.assert_close(c, ref, atol=1e-3 * K**0.5 + 1e-2, rtol=1e-2)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_rmsnorm(native, dtype):
+    from bergson_b200.ops import functional as F
+
+    torch.manual_seed(3)
+    x = torch.randn(37, 512, device="cuda", dtype=dtype, requires_grad=True)
+    w = (1 + 0.1 * torch.randn(512, device="cuda")).to(dtype).requires_grad_()
+    y = F.rms_norm(x, w, 1e-5)
+    gy = torch.randn_like(y)
+    y.backward(gy)
+    x2 = x.detach().float().requires_grad_()
+    w2 = w.detach().float().requires_grad_()
+    y2 = F.rms_norm_ref(x2, w2, 1e-5)
+    y2.backward(gy.float())
+    tol = dict(atol=3e-2, rtol=3e-2) if dtype == torch.bfloat16 else dict(atol=1e-5, rtol=1e-4)
+    torch.testing.assert_close(y.float(), y2, **tol)
+    torch.testing.assert_close(x.grad.float(), x2.grad, **tol)
+    torch.testing.assert_close(w.grad.float(), w2.grad, atol=tol["atol"] * 10, rtol=tol["rtol"])
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+def test_layernorm(native, dtype):
+    from bergson_b200.ops import functional as F
+
+    torch.manual_seed(4)
+    x = torch.randn(29, 768, device="cuda", dtype=dtype, requires_grad=True)
+    w = (1 + 0.1 * torch.randn(768, device="cuda")).to(dtype).requires_grad_()
+    b = (0.1 * torch.randn(768, device="cuda")).to(dtype).requires_grad_()
+    y = F.layer_norm(x, w, b, 1e-5)
+    gy = torch.randn_like(y)
+    y.backward(gy)
+    x2, w2, b2 = (t.detach().float().requires_grad_() for t in (x, w, b))
+    y2 = F.layer_norm_ref(x2, w2, b2, 1e-5)
+    y2.backward(gy.float())
+    tol = dict(atol=3e-2, rtol=3e-2) if dtype == torch.bfloat16 else dict(atol=1e-5, rtol=1e-4)
+    torch.testing.assert_close(y.float(), y2, **tol)
+    torch.testing.assert_close(x.grad.float(), x2.grad, **tol)
+    torch.testing.assert_close(w.grad.float(), w2.grad, atol=tol["atol"] * 10, rtol=tol["rtol"])
+    torch.testing.assert_close(b.grad.float(), b2.grad, atol=tol["atol"] * 10, rtol=tol["rtol"])
+
+
+@pytest.mark.parametrize("rot", [8, 32])
+def test_rotary(native, rot):
+    from bergson_b200.ops import functional as F
+
+    x = torch.randn(2, 19, 4, 32, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    cos, sin = F.rotary_tables(19, rot, 10000.0, x.device)
+    y = F.rotary(x, cos, sin, rot)
+    gy = torch.randn_like(y)
+    y.backward(gy)
+    x2 = x.detach().float().requires_grad_()
+    y2 = F.rotary_ref(x2, cos, sin, rot)
+    y2.backward(gy.float())
+    torch.testing.assert_close(y.float(), y2, atol=2e-2, rtol=2e-2)
+    torch.testing.assert_close(x.grad.float(), x2.grad, atol=2e-2, rtol=2e-2)
+
+
+def test_swiglu_gelu(native):
+    from bergson_b200.ops import functional as F
+
+    g = torch.randn(64, 256, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    u = torch.randn(64, 256, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    y = F.swiglu(g, u)
+    gy = torch.randn_like(y)
+    y.backward(gy)
+    g2, u2 = g.detach().float().requires_grad_(), u.detach().float().requires_grad_()
+    y2 = F.swiglu_ref(g2, u2)
+    y2.backward(gy.float())
+    torch.testing.assert_close(y.float(), y2, atol=3e-2, rtol=3e-2)
+    torch.testing.assert_close(g.grad.float(), g2.grad, atol=3e-2, rtol=3e-2)
+    torch.testing.assert_close(u.grad.float(), u2.grad, atol=3e-2, rtol=3e-2)
+    for approx in ("none", "tanh"):
+        x = torch.randn(64, 256, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+        y = F.gelu(x, approx)
+        y.backward(gy)
+        x2 = x.detach().float().requires_grad_()
+        y2 = F.gelu_ref(x2, approx)
+        y2.backward(gy.float())
+        torch.testing.assert_close(y.float(), y2, atol=3e-2, rtol=3e-2)
+        torch.testing.assert_close(x.grad.float(), x2.grad, atol=3e-2, rtol=3e-2)
+
+
+@pytest.mark.parametrize("V", [1000, 50304])
+def test_cross_entropy(native, V):
+    from bergson_b200.ops import functional as F
+
+    torch.manual_seed(5)
+    z = (3 * torch.randn(33, V, device="cuda")).to(torch.bfloat16).requires_grad_()
+    t = torch.randint(0, V, (33,), device="cuda")
+    t[5] = -100
+    loss = F.token_cross_entropy(z, t)
+    w = torch.rand(33, device="cuda")
+    (loss * w).sum().backward()
+    z2 = z.detach().float().requires_grad_()
+    loss2 = F.token_cross_entropy_ref(z2, t)
+    (loss2 * w).sum().backward()
+    torch.testing.assert_close(loss, loss2, atol=1e-3, rtol=1e-3)
+    torch.testing.assert_close(z.grad.float(), z2.grad, atol=5e-3, rtol=2e-2)
+
+
+def test_finalize_rows(native):
+    acc = torch.randn(5, 512, device="cuda") * 1e5
+    out = torch.zeros(9, 512, device="cuda", dtype=torch.float16)
+    idx = torch.tensor([8, 0, 3, 4, 6], device="cuda")
+    native.finalize_rows(acc, out, idx, -65504.0, 65504.0, False)
+    ref = acc.clamp(-65504.0, 65504.0).half()
+    torch.testing.assert_close(out[idx], ref)
+    assert out[1].abs().max() == 0
+    out2 = torch.zeros(5, 512, device="cuda", dtype=torch.float16)
+    native.finalize_rows(acc / 1e5, out2, None, -65504.0, 65504.0, True)
+    r = (acc / 1e5).half().float()
+    ref2 = (r / r.norm(dim=1, keepdim=True)).half()
+    torch.testing.assert_close(out2, ref2, atol=1e-3, rtol=1e-2)
