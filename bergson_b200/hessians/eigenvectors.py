@@ -1,0 +1,192 @@
+"""Eigendecomposition of Kronecker factors and EK-FAC eigenvalue correction
+(reference ``bergson/hessians/eigenvectors.py``).
+
+Directory layout produced (all row-sharded with ``shard_bounds``):
+``eigen_activation_sharded/``, ``eigen_gradient_sharded/`` (rows of the eigenvector
+matrix, columns = eigenvectors, ascending eigenvalues), ``eigenvalue_sharded/``
+(``outer(l_G, l_A) * total_processed``), ``factor_eig_a/`` (full ``l_A * sqrt(T)``
+replicated), ``factor_eig_g/`` (``l_G * sqrt(T)`` shard), and
+``eigenvalue_correction_sharded/`` (``sum_n (Q_G^T G_n Q_A)^2``, un-normalised).
+"""
+
+from __future__ import annotations
+
+import gc
+import os
+from dataclasses import dataclass
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+from safetensors import safe_open
+from safetensors.torch import load_file, save_file
+from torch import Tensor
+
+from ..collector.collector import HookCollectorBase
+from ..utils.logger import get_logger
+from ..utils.utils import assert_type, get_device
+from .sharded_computation import ShardedMul, shard_bounds
+
+
+def fair_distribute_by_cost(key_dimensions: dict[str, int], world_size: int) -> list[list[str]]:
+    """Deal keys to ranks in snake order of decreasing ``d^3`` cost."""
+    order = sorted(key_dimensions, key=lambda k: key_dimensions[k] ** 3, reverse=True)
+    out: list[list[str]] = [[] for _ in range(world_size)]
+    for i, key in enumerate(order):
+        rnd, pos = divmod(i, world_size)
+        out[pos if rnd % 2 == 0 else world_size - 1 - pos].append(key)
+    return out
+
+
+@dataclass(kw_only=True)
+class LambdaCollector(HookCollectorBase):
+    """EK-FAC corrected eigenvalues ``L*[o, i] = sum_n (Q_G^T G_n Q_A)^2[o, i]`` with
+    per-document gradients ``G_n``.  The eigenvector shards are gathered into local
+    memory once in ``setup`` and reused by every batch; accumulation stays on the device."""
+
+    path: str
+    eigen_path: str | None = None
+    output_subdir: str = "eigenvalue_correction_sharded"
+    dtype: torch.dtype = torch.float32
+
+    def setup(self) -> None:
+        self.shard_computer = sc = ShardedMul()
+        self.device = get_device(self.rank)
+        src = self.eigen_path or self.path
+
+        def load(sub: str) -> dict[str, Tensor]:
+            shard = load_file(os.path.join(src, f"{sub}/shard_{self.rank}.safetensors"), device=self.device)
+            return {k: sc.gather_rows(v.to(self.dtype), v.shape[1]) for k, v in shard.items()}
+
+        self.eigen_a = load("eigen_activation_sharded")
+        self.eigen_g = load("eigen_gradient_sharded")
+        self.eigenvalue_corrections: dict[str, Tensor] = {}
+        self.transformed_a_cache: dict[str, Tensor] = {}
+
+    def forward_hook(self, module: nn.Module, a: Tensor) -> None:
+        name = assert_type(str, module._name)
+        if module._collect_bias:
+            a = torch.cat([a, a.new_ones(*a.shape[:-1], 1)], dim=-1)
+        self.transformed_a_cache[name] = a.to(self.dtype) @ self.eigen_a[name]
+
+    def backward_hook(self, module: nn.Module, g: Tensor) -> None:
+        name = assert_type(str, module._name)
+        tg = g.to(self.dtype) @ self.eigen_g[name]  # [N, S, O]
+        ta = self.transformed_a_cache.pop(name)  # [N, S, I]
+        per_doc = tg.mT @ ta  # [N, O, I]
+        upd = per_doc.square_().sum(dim=0)
+        if name in self.eigenvalue_corrections:
+            self.eigenvalue_corrections[name].add_(upd)
+        else:
+            self.eigenvalue_corrections[name] = upd
+
+    def process_batch(self, indices: list[int], **kwargs) -> None:
+        pass
+
+    def teardown(self) -> None:
+        sc = self.shard_computer
+        out = {}
+        for name, full in self.eigenvalue_corrections.items():
+            if sc.dist:
+                dist.all_reduce(full, op=dist.ReduceOp.SUM)
+            lo, hi = sc.shard_bounds(full.shape[0])
+            out[name] = full[lo:hi].contiguous().cpu()
+        d = os.path.join(self.path, self.output_subdir)
+        os.makedirs(d, exist_ok=True)
+        save_file(out, os.path.join(d, f"shard_{self.rank}.safetensors"))
+
+
+def _compute_full_matrix(name: str, shard_path, rank: int, world_size: int) -> Tensor:
+    """Concatenate ``name`` from every shard file (row order = rank order)."""
+    files = [f for f in os.listdir(shard_path) if f.endswith(".safetensors")]
+    assert len(files) == world_size, f"Expected {world_size} shards, found {len(files)} in {shard_path}"
+    device = get_device(rank)
+    parts = []
+    for r in range(world_size):
+        with safe_open(os.path.join(shard_path, f"shard_{r}.safetensors"), framework="pt", device=device) as f:
+            parts.append(f.get_tensor(name))
+    return parts[0] if world_size == 1 else torch.cat(parts, dim=0)
+
+
+def _gather_and_shard_along_dim_0(input_dict, full_shape_per_key, dtype, rank, world_size, device):
+    """Every key lives on exactly one rank; sum-reduce (others contribute zeros) and keep
+    this rank's rows."""
+    if world_size == 1:
+        return input_dict
+    out = {}
+    for key, shape in full_shape_per_key.items():
+        t = input_dict[key].to(device=device, dtype=dtype) if key in input_dict else torch.zeros(shape, device=device, dtype=dtype)
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        lo, hi = shard_bounds(shape[0], rank, world_size)
+        out[key] = t[lo:hi].contiguous().cpu()
+    return out
+
+
+def compute_eigendecomposition(covariance_path: str, total_processed) -> dict[str, Tensor]:
+    """``eigh`` (fp64) of every factor in ``covariance_path`` divided by
+    ``total_processed`` and symmetrised; writes ``eigen_<basename>/shard_<rank>`` and
+    returns this rank's eigenvalue shards."""
+    rank = dist.get_rank() if dist.is_initialized() else 0
+    world = dist.get_world_size() if dist.is_initialized() else 1
+    device = get_device(rank)
+    total = torch.as_tensor(total_processed).to(device)
+
+    with safe_open(os.path.join(covariance_path, "shard_0.safetensors"), framework="pt") as f:
+        keys = list(f.keys())
+        out_dtype = f.get_tensor(keys[0]).dtype
+        dims = {k: f.get_slice(k).get_shape()[-1] for k in keys}
+
+    vecs: dict[str, Tensor] = {}
+    vals: dict[str, Tensor] = {}
+    for key in fair_distribute_by_cost(dims, world)[rank]:
+        m = _compute_full_matrix(key, covariance_path, rank, world).to(torch.float64) / total
+        m = (m + m.T) / 2
+        if not torch.isfinite(m).all():
+            raise ValueError(f"Covariance matrix for {key} contains NaNs or Infs. Consider using fp32.")
+        try:
+            w, q = torch.linalg.eigh(m)
+        except Exception as e:
+            raise RuntimeError(f"Eigendecomposition failed for {key}") from e
+        vecs[key] = q.to(out_dtype).cpu().contiguous()
+        vals[key] = w.to(out_dtype).cpu().contiguous()
+
+    vecs = _gather_and_shard_along_dim_0(vecs, {k: (m, m) for k, m in dims.items()}, out_dtype, rank, world, device)
+    vals = _gather_and_shard_along_dim_0(vals, {k: (m,) for k, m in dims.items()}, out_dtype, rank, world, device)
+
+    out_dir = os.path.join(os.path.dirname(covariance_path), "eigen_" + os.path.basename(covariance_path))
+    os.makedirs(out_dir, exist_ok=True)
+    save_file(vecs, os.path.join(out_dir, f"shard_{rank}.safetensors"))
+    gc.collect()
+    get_logger().info(f"Saved eigenvectors to {out_dir}")
+    return vals
+
+
+def save_uncorrected_eigenvalues(partial_run_path, eigenvalues_a, eigenvalues_g, total_processed, rank: int,
+                                 world_size: int) -> None:
+    """``eigenvalue_sharded`` = ``outer(l_G shard, l_A full) * T`` and the per-factor
+    eigenvalues scaled by ``sqrt(T)`` (their product equals the grid)."""
+    root = str(partial_run_path)
+    dirs = {k: os.path.join(root, k) for k in ("eigenvalue_sharded", "factor_eig_a", "factor_eig_g")}
+    for d in dirs.values():
+        os.makedirs(d, exist_ok=True)
+    device = get_device(rank)
+    total = torch.as_tensor(total_processed).to(device)
+    sc = ShardedMul()
+    grid, fa, fg = {}, {}, {}
+    for key, g_shard in eigenvalues_g.items():
+        g_shard = g_shard.to(device)
+        a_shard = eigenvalues_a[key].to(device)
+        if world_size > 1:
+            m = torch.tensor(a_shard.shape[0], device=device)
+            dist.all_reduce(m, op=dist.ReduceOp.SUM)
+            a_full = sc.gather_rows(a_shard, int(m.item()))
+        else:
+            a_full = a_shard
+        grid[key] = (torch.outer(g_shard, a_full) * total).cpu().contiguous()
+        scale = total.to(a_full.dtype).sqrt()
+        fa[key] = (a_full * scale).cpu().contiguous()
+        fg[key] = (g_shard * scale).cpu().contiguous()
+    save_file(grid, os.path.join(dirs["eigenvalue_sharded"], f"shard_{rank}.safetensors"))
+    save_file(fa, os.path.join(dirs["factor_eig_a"], f"shard_{rank}.safetensors"))
+    save_file(fg, os.path.join(dirs["factor_eig_g"], f"shard_{rank}.safetensors"))
+    get_logger().info(f"Saved uncorrected eigenvalues to {dirs['eigenvalue_sharded']}")

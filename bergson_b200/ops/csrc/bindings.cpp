@@ -8,6 +8,7 @@
 #include <mutex>
 
 #include "kernels.h"
+#include "kernels_cov.h"
 
 namespace {
 
@@ -261,6 +262,29 @@ void row_sumsq(at::Tensor x, at::Tensor out) {
         "row_sumsq");
 }
 
+void cov_syrk(at::Tensor x, std::vector<int64_t> dst_ptrs, std::vector<int64_t> row_start,
+              c10::optional<at::Tensor> local) {
+  // x: [T, D] 16-bit; dst_ptrs: device addresses (this GPU's or peer-mapped) of every rank's
+  // fp32 row shard; row_start: world + 1 row boundaries.
+  TORCH_CHECK(x.is_cuda() && x.dim() == 2 && x.is_contiguous());
+  const int world = (int)dst_ptrs.size();
+  TORCH_CHECK(world >= 1 && world <= 8 && (int)row_start.size() == world + 1);
+  c10::cuda::CUDAGuard guard(x.device());
+  float* dst[8];
+  int rs[9];
+  for (int r = 0; r < world; ++r) dst[r] = reinterpret_cast<float*>(dst_ptrs[r]);
+  for (int r = 0; r <= world; ++r) rs[r] = (int)row_start[r];
+  const float* loc = nullptr;
+  if (local.has_value()) {
+    TORCH_CHECK(local->is_cuda() && local->is_contiguous() && local->scalar_type() == at::kFloat &&
+                local->size(0) == x.size(1) && local->size(1) == x.size(1));
+    loc = local->data_ptr<float>();
+  }
+  const int sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
+  check(bgn_cov_syrk(x.data_ptr(), x.size(0), (int)x.size(1), fmt16(x), dst, rs, world, loc, sms, status_ptr(x),
+                     stream()), "cov_syrk");
+}
+
 at::Tensor kernel_status(int64_t device) { return status_tensor((int)device); }
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
@@ -281,5 +305,6 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("finalize_rows", &finalize_rows);
   m.def("adamw_step", &adamw_step);
   m.def("row_sumsq", &row_sumsq);
+  m.def("cov_syrk", &cov_syrk);
   m.def("kernel_status", &kernel_status);
 }

@@ -186,7 +186,8 @@ class _SwiGLUFn(torch.autograd.Function):
         from . import native
 
         gate, up = ctx.saved_tensors
-        return native.swiglu_bwd(dy.contiguous(), gate.contiguous(), up.contiguous())
+        dg, du = native.swiglu_bwd(dy.contiguous(), gate.contiguous(), up.contiguous())
+        return dg, du
 
 
 def swiglu(gate: Tensor, up: Tensor) -> Tensor:

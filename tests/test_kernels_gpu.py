@@ -172,3 +172,36 @@ def test_finalize_rows(native):
     r = (acc / 1e5).half().float()
     ref2 = (r / r.norm(dim=1, keepdim=True)).half()
     torch.testing.assert_close(out2, ref2, atol=1e-3, rtol=1e-2)
+
+
+@pytest.mark.parametrize("T,D", [(64, 128), (1000, 200), (4096, 768), (5000, 1032)])
+def test_cov_syrk(native, T, D):
+    torch.manual_seed(6)
+    x = torch.randn(T, D, device="cuda", dtype=torch.bfloat16)
+    c = torch.zeros(D, D, device="cuda")
+    native.cov_syrk(x, [c.data_ptr()], [0, D], None)
+    native.cov_syrk(x, [c.data_ptr()], [0, D], None)  # accumulates
+    _status_ok(native)
+    full = torch.triu(c) + torch.triu(c, 1).T
+    ref = 2 * (x.float().T @ x.float())
+    torch.testing.assert_close(full, ref, atol=1e-3 * T**0.5 + 1e-2, rtol=1e-3)
+
+
+def test_cov_syrk_row_shards_and_fold(native):
+    """Two "ranks" emulated on one GPU as two destination buffers; the fold step adds a
+    local accumulator into the same adds."""
+    torch.manual_seed(7)
+    T, D = 2048, 392
+    x = torch.randn(T, D, device="cuda", dtype=torch.bfloat16)
+    local = torch.randn(D, D, device="cuda")
+    r0, r1 = torch.zeros(200, D, device="cuda"), torch.zeros(D - 200, D, device="cuda")
+    native.cov_syrk(x, [r0.data_ptr(), r1.data_ptr()], [0, 200, D], local)
+    _status_ok(native)
+    got = torch.cat([r0, r1])
+    ref = x.float().T @ x.float() + local
+    # only the block-upper triangle (128-wide tiles) is produced
+    mask = torch.zeros(D, D, dtype=torch.bool, device="cuda")
+    for i in range(0, D, 128):
+        mask[i : i + 128, i:] = True
+    torch.testing.assert_close(got[mask], ref[mask], atol=0.2, rtol=1e-3)
+    assert got[~mask].abs().max() == 0
