@@ -286,6 +286,11 @@ class HookCollectorBase(ContextDecorator, ABC):
         return self
 
     def __enter__(self):
+        # Re-entrant: the collection loop holds the hooks for the whole run while each
+        # batch enters again through ``with_batch``.
+        self._depth = getattr(self, "_depth", 0) + 1
+        if self._depth > 1:
+            return self
         for name in self.target_info:
             layer = self.model.get_submodule(name)
             layer._name = name  # type: ignore[attr-defined]
@@ -310,8 +315,11 @@ class HookCollectorBase(ContextDecorator, ABC):
         return None
 
     def __exit__(self, exc_type, exc, tb):
+        self._depth -= 1
+        if self._depth > 0:
+            return False
         for layer in self.model.modules():
-            for attr in ("_inputs", "_name", "_collect_bias"):
+            for attr in ("_inputs", "_name", "_collect_bias", "_fused"):
                 if hasattr(layer, attr):
                     delattr(layer, attr)
         for h in self._fwd_hooks:

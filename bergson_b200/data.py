@@ -86,10 +86,27 @@ def synthetic_dataset(spec: str) -> Dataset:
     return Dataset.from_dict({"input_ids": ids, "length": [len(x) for x in ids]})
 
 
+def _slice_rows(ds: Dataset, split: str) -> Dataset:
+    """Apply a ``name[a:b]`` row slice (absolute indices or percentages) to ``ds``."""
+    m = re.fullmatch(r"[^\[]*\[\s*(-?\d+%?)?\s*:\s*(-?\d+%?)?\s*\]", split.strip())
+    if not m:
+        return ds
+    n = len(ds)
+
+    def pos(tok, default):
+        if tok is None:
+            return default
+        v = int(tok.rstrip("%"))
+        v = v * n // 100 if tok.endswith("%") else v
+        return max(0, min(n, v + n if v < 0 else v))
+
+    return ds.select(range(pos(m.group(1), 0), pos(m.group(2), n)))
+
+
 def load_data_string(data_str: str, split: str = "train", subset: str | None = None, data_kwargs: str = "") -> Dataset:
     """Resolve a dataset string to a ``datasets.Dataset``."""
     if data_str.startswith("synthetic:"):
-        return synthetic_dataset(data_str)
+        return _slice_rows(synthetic_dataset(data_str), split)
     p = Path(data_str)
     if data_str.endswith(".csv"):
         ds = load_dataset("csv", data_files=data_str, split=split)
@@ -97,6 +114,9 @@ def load_data_string(data_str: str, split: str = "train", subset: str | None = N
         ds = load_dataset("json", data_files=data_str, split=split)
     elif p.is_dir() and ((p / "dataset_info.json").exists() or (p / "dataset_dict.json").exists() or (p / "state.json").exists()):
         ds = load_from_disk(data_str, keep_in_memory=False)
+        if isinstance(ds, DatasetDict):
+            ds = ds[split.split("[")[0]]
+        return _slice_rows(assert_type(Dataset, ds), split)
     else:
         try:
             ds = load_dataset(data_str, subset, split=split, **simple_parse_kwargs_string(data_kwargs))

@@ -70,6 +70,18 @@ class CausalLMOutput:
     hidden_states: Tensor | None = None
 
 
+class Backbone(nn.Module):
+    """Base of the ``base_model`` sub-modules; mirrors HF's ``device`` / ``dtype``."""
+
+    @property
+    def device(self) -> torch.device:
+        return next(self.parameters()).device
+
+    @property
+    def dtype(self) -> torch.dtype:
+        return next(self.parameters()).dtype
+
+
 class NativeCausalLM(nn.Module):
     """Base class: HF-like surface (``config``, ``base_model``, ``device``, ``dtype``,
     ``get_input_embeddings``, ``loss_function``, ``forward(...).logits``)."""

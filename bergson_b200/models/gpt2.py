@@ -8,7 +8,7 @@ import torch.nn as nn
 from torch import Tensor
 
 from .. import ops
-from .common import Conv1D, ModelArgs, NativeCausalLM, maybe_checkpoint
+from .common import Backbone, Conv1D, ModelArgs, NativeCausalLM, maybe_checkpoint
 
 
 class _LN(nn.LayerNorm):
@@ -57,7 +57,7 @@ class GPT2Block(nn.Module):
         return x + self.mlp(self.ln_2(x))
 
 
-class GPT2Model(nn.Module):
+class GPT2Model(Backbone):
     def __init__(self, cfg: ModelArgs):
         super().__init__()
         self.wte = nn.Embedding(cfg.vocab_size, cfg.hidden_size)

@@ -8,7 +8,7 @@ import torch.nn as nn
 from torch import Tensor
 
 from .. import ops
-from .common import ModelArgs, NativeCausalLM, maybe_checkpoint
+from .common import Backbone, ModelArgs, NativeCausalLM, maybe_checkpoint
 
 
 class _LN(nn.LayerNorm):
@@ -64,7 +64,7 @@ class NeoXLayer(nn.Module):
         return x + self.mlp(self.post_attention_layernorm(x))
 
 
-class NeoXModel(nn.Module):
+class NeoXModel(Backbone):
     def __init__(self, cfg: ModelArgs):
         super().__init__()
         self.embed_in = nn.Embedding(cfg.vocab_size, cfg.hidden_size)

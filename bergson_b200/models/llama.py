@@ -7,7 +7,7 @@ import torch.nn as nn
 from torch import Tensor
 
 from .. import ops
-from .common import ModelArgs, NativeCausalLM, maybe_checkpoint
+from .common import Backbone, ModelArgs, NativeCausalLM, maybe_checkpoint
 
 
 class LlamaRMSNorm(nn.Module):
@@ -66,7 +66,7 @@ class LlamaDecoderLayer(nn.Module):
         return x + self.mlp(self.post_attention_layernorm(x))
 
 
-class LlamaModel(nn.Module):
+class LlamaModel(Backbone):
     def __init__(self, cfg: ModelArgs):
         super().__init__()
         self.embed_tokens = nn.Embedding(cfg.vocab_size, cfg.hidden_size)
