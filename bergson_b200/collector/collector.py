@@ -558,19 +558,30 @@ class CollectorComputer:
             with_modules=True,
         )
 
-    def step(self, indices: list[int]) -> Tensor:
-        """One batch: stage inputs, forward/backward under the hooks, hand off rows."""
+    def stage(self, indices: list[int]):
+        """Host side of a batch: fetch rows, pad, copy to the device through pinned memory
+        (asynchronously).  Returns ``(x, y, collection_mask, batch)``."""
         batch = self.data[indices]
         x, y, _, mask = pad_and_tensor(
             batch["input_ids"], labels=batch.get("labels"), device=self.device,
             sync_max_len=False, pinned=self.device.type == "cuda",
         )
+        return x, y, mask, batch
+
+    def run_staged(self, indices: list[int], x: Tensor, y: Tensor, mask: Tensor, batch: dict) -> Tensor:
+        """Device side of a batch: forward/backward under the hooks, hand off rows."""
+        if not hasattr(self, "_total_processed"):
+            self._total_processed = torch.zeros((), dtype=torch.long, device=self.device)
         self._total_processed += mask.sum()
         self.collector.begin_fused_batch(len(indices), self.device)
         with self.collector.with_batch(mask):
             losses = self.forward_backward(self.model, x, y, batch)
         self.collector.process_batch(indices, losses=losses)
         return losses
+
+    def step(self, indices: list[int]) -> Tensor:
+        """One batch end to end; returns the per-document losses (on the device)."""
+        return self.run_staged(indices, *self.stage(indices))
 
     def run_with_collector_hooks(self, desc: Optional[str] = None):
         self._total_processed = torch.zeros((), dtype=torch.long, device=self.device)

@@ -96,6 +96,7 @@ def parse_native_spec(spec: str) -> tuple[ModelArgs, int]:
     name, _, query = body.partition("?")
     opts = {k: _convert(v) for k, v in parse_qsl(query)}
     seed = int(opts.pop("seed", 0))
+    opts.pop("init", None)
     if name in PRESETS:
         base = dict(PRESETS[name])
     elif name in FAMILIES:
@@ -106,10 +107,23 @@ def parse_native_spec(spec: str) -> tuple[ModelArgs, int]:
     return args_from_dict(base), seed
 
 
-def build_model(args: ModelArgs, *, dtype=torch.float32, device="cpu", seed: int = 0) -> NativeCausalLM:
-    """Random-init model; initialisation is drawn on CPU in fp32 from ``seed`` so the
-    weights do not depend on the target device or dtype."""
+def build_model(args: ModelArgs, *, dtype=torch.float32, device="cpu", seed: int = 0,
+                init_on_device: bool = False) -> NativeCausalLM:
+    """Random-init model.  By default initialisation is drawn on CPU in fp32 from ``seed``
+    so the weights do not depend on the target device or dtype; ``init_on_device`` draws
+    them directly on ``device`` in ``dtype`` (fast for multi-billion-parameter models,
+    reproducible per device type)."""
     cls = FAMILIES[args.model_type]
+    if init_on_device and torch.device(device).type == "cuda":
+        prev = torch.get_default_dtype()
+        torch.set_default_dtype(dtype)
+        try:
+            with torch.device(device), torch.random.fork_rng(devices=[torch.device(device)]):
+                torch.manual_seed(seed)
+                model = cls(args)
+        finally:
+            torch.set_default_dtype(prev)
+        return model
     with torch.random.fork_rng(devices=[]):
         torch.manual_seed(seed)
         model = cls(args)
@@ -120,7 +134,7 @@ def load_model(name: str, *, dtype=torch.float32, device="cpu", revision=None, *
     """Resolve a model string (see module docstring)."""
     if name.startswith("native:"):
         args, seed = parse_native_spec(name)
-        return build_model(args, dtype=dtype, device=device, seed=seed)
+        return build_model(args, dtype=dtype, device=device, seed=seed, init_on_device="init=device" in name)
     path = Path(name)
     if (path / "config.json").exists():
         with open(path / "config.json") as f:

@@ -70,6 +70,33 @@ def ext():
     return mod
 
 
+_launches = 0
+# Number of kernel launches behind one call of each extension function (helpers such as the
+# reduction of per-block partial sums are torch ops and are not counted).
+_KERNELS_PER_CALL = {"kernel_status": 0}
+
+
+def launch_count() -> int:
+    """Kernel launches issued through this module since the last ``reset_launch_count``."""
+    return _launches
+
+
+def reset_launch_count() -> None:
+    global _launches
+    _launches = 0
+
+
 def __getattr__(name: str):
-    # ``native.rmsnorm_fwd(...)`` forwards to the extension's function of that name.
-    return getattr(ext(), name)
+    # ``native.rmsnorm_fwd(...)`` forwards to the extension's function of that name and
+    # counts the launch.
+    fn = getattr(ext(), name)
+    per_call = _KERNELS_PER_CALL.get(name, 1)
+
+    def counted(*args, **kwargs):
+        global _launches
+        _launches += per_call
+        return fn(*args, **kwargs)
+
+    counted.__name__ = name
+    globals()[name] = counted
+    return counted
