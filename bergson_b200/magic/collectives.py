@@ -1,0 +1,85 @@
+"""Collectives that are differentiable to any order.
+
+Each is a linear map whose transpose is another collective of this module, so the
+backward of one is an application of the other and autograd can differentiate a training
+step twice (gradient synchronisation inside ``create_graph=True``) without special cases:
+
+* ``all_reduce_sum``        backward: ``all_reduce_sum``
+* ``all_gather_rows``       backward: ``reduce_scatter_rows`` (sum)
+* ``reduce_scatter_rows``   backward: ``all_gather_rows``
+
+The reference gets the first from a custom autograd function
+(``bergson/magic/trainer.py:80-96``) and the other two by patching DTensor's
+redistribute backward (``bergson/magic/dtensor_patch.py``).
+"""
+
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+from torch import Tensor
+
+
+def _world(group) -> int:
+    return dist.get_world_size(group) if dist.is_initialized() else 1
+
+
+class _AllReduceSum(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x: Tensor, group):
+        ctx.group = group
+        out = x.clone()
+        dist.all_reduce(out, op=dist.ReduceOp.SUM, group=group)
+        return out
+
+    @staticmethod
+    def backward(ctx, g: Tensor):
+        return _AllReduceSum.apply(g, ctx.group), None
+
+
+class _AllGatherRows(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, shard: Tensor, group):
+        ctx.group = group
+        w = _world(group)
+        out = torch.empty((w * shard.shape[0], *shard.shape[1:]), dtype=shard.dtype, device=shard.device)
+        dist.all_gather_into_tensor(out, shard.contiguous(), group=group)
+        return out
+
+    @staticmethod
+    def backward(ctx, g: Tensor):
+        return _ReduceScatterRows.apply(g, ctx.group), None
+
+
+class _ReduceScatterRows(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, full: Tensor, group):
+        ctx.group = group
+        w = _world(group)
+        out = torch.empty((full.shape[0] // w, *full.shape[1:]), dtype=full.dtype, device=full.device)
+        dist.reduce_scatter_tensor(out, full.contiguous(), op=dist.ReduceOp.SUM, group=group)
+        return out
+
+    @staticmethod
+    def backward(ctx, g: Tensor):
+        return _AllGatherRows.apply(g, ctx.group), None
+
+
+def all_reduce_sum(x: Tensor, group=None) -> Tensor:
+    if not dist.is_initialized() or _world(group) == 1:
+        return x
+    return _AllReduceSum.apply(x, group)
+
+
+def all_gather_rows(shard: Tensor, group=None) -> Tensor:
+    """Concatenate every rank's ``[r, ...]`` shard along dim 0."""
+    if not dist.is_initialized() or _world(group) == 1:
+        return shard
+    return _AllGatherRows.apply(shard, group)
+
+
+def reduce_scatter_rows(full: Tensor, group=None) -> Tensor:
+    """Sum over ranks and keep this rank's block of rows (dim 0 divisible by world)."""
+    if not dist.is_initialized() or _world(group) == 1:
+        return full
+    return _ReduceScatterRows.apply(full, group)

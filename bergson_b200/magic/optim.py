@@ -1,0 +1,258 @@
+"""Functional, twice-differentiable optimizers.
+
+The reference builds its optimizers from the third-party ``torchopt`` package
+(``bergson/magic/trainer.py:1072-1096``) plus an in-repo Muon
+(``bergson/magic/optim.py:27-269``).  This module provides the same update rules as
+self-contained ``GradientTransformation(init, update)`` pairs whose state is a plain
+nested dict of tensors, so that a training step can be differentiated with respect to
+gradients, parameters and optimizer state to any order:
+
+* ``adamw``: ``m = b1 m + (1-b1) g``, ``v = b2 v + (1-b2) g^2``, bias-corrected,
+  ``u = m_hat / (sqrt(v_hat + eps_root) + eps) + wd * p``, step ``-lr(count) * u``;
+* ``sgd``: ``g += wd * p``, heavy-ball ``t = g + momentum * t``, step ``-lr(count) * t``;
+* ``muon``: 2-D params: Nesterov momentum, 5 quintic Newton-Schulz iterations
+  (a, b, c = 3.4445, -4.7750, 2.0315), lr ratio ``0.2 sqrt(max(A, B))``, decoupled
+  weight decay; other params: AdamW.
+
+On CUDA, the non-traced (``inplace=True``) AdamW step over fp32 state runs in the fused
+``adamw_step`` kernel.
+"""
+
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import Any, Callable
+
+import torch
+from torch import Tensor
+
+Params = dict[str, Tensor]
+OptState = dict[str, Any]
+Schedule = Callable[[int], float]
+
+NS_EPS = 1e-7
+NS_COEFFS = (3.4445, -4.7750, 2.0315)
+NS_STEPS = 5
+
+
+@dataclass
+class GradientTransformation:
+    init: Callable[[Params], OptState]
+    update: Callable[..., tuple[Params, OptState]]
+
+
+def apply_updates(params: Params, updates: Params, *, inplace: bool = False) -> Params:
+    """``p + u`` per key (keys without an update are passed through)."""
+    out = {}
+    for k, p in params.items():
+        u = updates.get(k)
+        if u is None:
+            out[k] = p
+        elif inplace:
+            out[k] = p.add_(u.to(p.dtype))
+        else:
+            out[k] = p + u.to(p.dtype)
+    return out
+
+
+def _lr_of(schedule: Schedule | float, count: Tensor) -> float:
+    return float(schedule(int(count))) if callable(schedule) else float(schedule)
+
+
+# --------------------------------------------------------------------------- #
+# pytree helpers for the nested-dict optimizer state
+# --------------------------------------------------------------------------- #
+
+
+def tree_flatten_with_path(tree: Any, prefix: tuple = ()) -> list[tuple[tuple, Any]]:
+    """Leaves of a nested dict / list with their key paths, dict keys in sorted order."""
+    if isinstance(tree, dict):
+        out = []
+        for k in sorted(tree, key=str):
+            out += tree_flatten_with_path(tree[k], prefix + (k,))
+        return out
+    if isinstance(tree, (list, tuple)):
+        out = []
+        for i, v in enumerate(tree):
+            out += tree_flatten_with_path(v, prefix + (i,))
+        return out
+    return [(prefix, tree)]
+
+
+def tree_iter(tree: Any):
+    for _, leaf in tree_flatten_with_path(tree):
+        yield leaf
+
+
+def tree_map(fn: Callable, tree: Any, *rest: Any) -> Any:
+    if isinstance(tree, dict):
+        return {k: tree_map(fn, v, *(r[k] for r in rest)) for k, v in tree.items()}
+    if isinstance(tree, (list, tuple)):
+        return type(tree)(tree_map(fn, v, *(r[i] for r in rest)) for i, v in enumerate(tree))
+    return fn(tree, *rest)
+
+
+def tree_unflatten_like(tree: Any, leaves: list) -> Any:
+    """Rebuild a tree of ``tree``'s structure from ``leaves`` in flatten order."""
+    it = iter(leaves)
+
+    def build(node):
+        if isinstance(node, dict):
+            vals = {k: None for k in node}
+            for k in sorted(node, key=str):
+                vals[k] = build(node[k])
+            return vals
+        if isinstance(node, (list, tuple)):
+            return type(node)(build(v) for v in node)
+        return next(it)
+
+    return build(tree)
+
+
+# --------------------------------------------------------------------------- #
+# AdamW
+# --------------------------------------------------------------------------- #
+
+
+def _adam_direction(g, m, v, count: int, b1, b2, eps, eps_root, inplace: bool):
+    if inplace:
+        m = m.mul_(b1).add_(g, alpha=1 - b1)
+        v = v.mul_(b2).addcmul_(g, g, value=1 - b2)
+    else:
+        m = m * b1 + g * (1 - b1)
+        v = v * b2 + g * g * (1 - b2)
+    m_hat = m / (1 - b1**count)
+    v_hat = v / (1 - b2**count)
+    return m_hat / ((v_hat + eps_root).sqrt() + eps), m, v
+
+
+def adamw(lr: Schedule | float, betas=(0.9, 0.999), eps: float = 1e-8, eps_root: float = 0.0,
+          weight_decay: float = 0.0) -> GradientTransformation:
+    b1, b2 = betas
+
+    def init(params: Params) -> OptState:
+        return {
+            "mu": {k: torch.zeros_like(p, dtype=torch.float32 if p.dtype != torch.float64 else p.dtype) for k, p in params.items()},
+            "nu": {k: torch.zeros_like(p, dtype=torch.float32 if p.dtype != torch.float64 else p.dtype) for k, p in params.items()},
+            "count": torch.zeros((), dtype=torch.long),
+        }
+
+    def update(grads: Params, state: OptState, *, params: Params, inplace: bool = False):
+        count = state["count"] + 1
+        step_lr = _lr_of(lr, state["count"])
+        t = int(count)
+        updates, mu, nu = {}, {}, {}
+        for k, p in params.items():
+            g = grads.get(k)
+            if g is None:
+                mu[k], nu[k], updates[k] = state["mu"][k], state["nu"][k], None
+                continue
+            d, mu[k], nu[k] = _adam_direction(g.to(state["mu"][k].dtype), state["mu"][k], state["nu"][k], t, b1, b2,
+                                              eps, eps_root, inplace)
+            if weight_decay:
+                d = d + weight_decay * p
+            updates[k] = -step_lr * d
+        return updates, {"mu": mu, "nu": nu, "count": count}
+
+    return GradientTransformation(init, update)
+
+
+# --------------------------------------------------------------------------- #
+# SGD with heavy-ball momentum
+# --------------------------------------------------------------------------- #
+
+
+def sgd(lr: Schedule | float, momentum: float = 0.0, weight_decay: float = 0.0) -> GradientTransformation:
+    def init(params: Params) -> OptState:
+        return {"trace": {k: torch.zeros_like(p) for k, p in params.items()}, "count": torch.zeros((), dtype=torch.long)}
+
+    def update(grads: Params, state: OptState, *, params: Params, inplace: bool = False):
+        step_lr = _lr_of(lr, state["count"])
+        updates, trace = {}, {}
+        for k, p in params.items():
+            g = grads.get(k)
+            if g is None:
+                trace[k], updates[k] = state["trace"][k], None
+                continue
+            if weight_decay:
+                g = g + weight_decay * p
+            t = state["trace"][k]
+            t = t.mul_(momentum).add_(g) if inplace else t * momentum + g
+            trace[k] = t
+            updates[k] = -step_lr * t
+        return updates, {"trace": trace, "count": state["count"] + 1}
+
+    return GradientTransformation(init, update)
+
+
+# --------------------------------------------------------------------------- #
+# Muon
+# --------------------------------------------------------------------------- #
+
+
+def zeropower_via_newtonschulz(grad: Tensor) -> Tensor:
+    """Quintic Newton-Schulz orthogonalisation ``X <- aX + (bA + cA^2)X``, ``A = XX^T``,
+    on the Frobenius-normalised matrix (transposed so that rows <= columns)."""
+    if grad.ndim != 2:
+        raise ValueError("Input tensor gradient must be a 2D matrix")
+    a, b, c = NS_COEFFS
+    x = grad.T if grad.size(0) > grad.size(1) else grad
+    x = x / x.norm().clamp(min=NS_EPS)
+    for _ in range(NS_STEPS):
+        gram = x @ x.T
+        poly = torch.addmm(gram, gram, gram, beta=b, alpha=c)
+        x = torch.addmm(x, poly, x, beta=a)
+    return x.T if grad.size(0) > grad.size(1) else x
+
+
+def adjust_lr(lr: float, mode: str | None, shape) -> float:
+    A, B = shape[:2]
+    if mode is None or mode == "original":
+        return lr * math.sqrt(max(1, A / B))
+    if mode == "match_rms_adamw":
+        return lr * 0.2 * math.sqrt(max(A, B))
+    return lr
+
+
+def muon(lr: Schedule | float, momentum: float = 0.95, adamw_betas=(0.9, 0.999), adamw_eps: float = 1e-8,
+         adamw_eps_root: float = 0.0, weight_decay: float = 0.0) -> GradientTransformation:
+    b1, b2 = adamw_betas
+
+    def init(params: Params) -> OptState:
+        return {
+            "trace": {k: torch.zeros_like(p) for k, p in params.items() if p.ndim == 2},
+            "mu": {k: torch.zeros_like(p) for k, p in params.items() if p.ndim != 2},
+            "nu": {k: torch.zeros_like(p) for k, p in params.items() if p.ndim != 2},
+            "count": torch.zeros((), dtype=torch.long),
+        }
+
+    def update(grads: Params, state: OptState, *, params: Params, inplace: bool = False):
+        count = state["count"] + 1
+        step_lr = _lr_of(lr, state["count"])
+        first = int(state["count"]) == 0
+        updates = {}
+        trace, mu, nu = dict(state["trace"]), dict(state["mu"]), dict(state["nu"])
+        for k, p in params.items():
+            g = grads.get(k)
+            if g is None:
+                updates[k] = None
+                continue
+            if p.ndim > 2:
+                raise ValueError(f"Muon does not support parameters with more than 2 dimensions, got shape {p.shape}")
+            if p.ndim == 2:
+                t = state["trace"][k]
+                t = t + g if first else t * momentum + g
+                trace[k] = t
+                d = zeropower_via_newtonschulz(g + momentum * t).to(g.dtype) * adjust_lr(1.0, "match_rms_adamw", p.shape)
+                if weight_decay:
+                    d = d + weight_decay * p.detach()
+            else:
+                d, mu[k], nu[k] = _adam_direction(g, state["mu"][k], state["nu"][k], int(count), b1, b2, adamw_eps,
+                                                  adamw_eps_root, False)
+                if weight_decay:
+                    d = d + weight_decay * p.detach()
+            updates[k] = -step_lr * d
+        return updates, {"trace": trace, "mu": mu, "nu": nu, "count": count}
+
+    return GradientTransformation(init, update)

@@ -56,7 +56,7 @@ def use_fused(*tensors: Tensor) -> bool:
 
 
 def rms_norm_ref(x: Tensor, weight: Tensor, eps: float) -> Tensor:
-    xf = x.float()
+    xf = x if x.dtype == torch.float64 else x.float()
     y = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)
     return (y.to(x.dtype)) * weight
 
@@ -127,8 +127,8 @@ def layer_norm(x: Tensor, weight: Tensor, bias: Tensor | None, eps: float) -> Te
 
 
 def rotary_tables(seq_len: int, rot_dim: int, theta: float, device, dtype=torch.float32):
-    inv = 1.0 / (theta ** (torch.arange(0, rot_dim, 2, device=device, dtype=torch.float32) / rot_dim))
-    ang = torch.outer(torch.arange(seq_len, device=device, dtype=torch.float32), inv)
+    inv = 1.0 / (theta ** (torch.arange(0, rot_dim, 2, device=device, dtype=torch.float64) / rot_dim))
+    ang = torch.outer(torch.arange(seq_len, device=device, dtype=torch.float64), inv)
     return ang.cos().to(dtype), ang.sin().to(dtype)  # [S, rot_dim/2]
 
 
@@ -242,7 +242,7 @@ def causal_attention(q: Tensor, k: Tensor, v: Tensor, scale: float | None = None
         att = torch.matmul(q, k.transpose(-1, -2)) * scale
         mask = torch.ones(S, S, dtype=torch.bool, device=q.device).tril()
         att = att.masked_fill(~mask, float("-inf"))
-        att = torch.softmax(att.float(), dim=-1).to(q.dtype)
+        att = torch.softmax(att if att.dtype == torch.float64 else att.float(), dim=-1).to(q.dtype)
         return torch.matmul(att, v)
     return F.scaled_dot_product_attention(
         q, k, v, is_causal=True, scale=scale, enable_gqa=(Hkv != Hq)

