@@ -1,0 +1,146 @@
+"""Micro-benchmarks of the attribution kernels against their rooflines.
+
+    python -m bergson_b200.ops.bench_kernels [--kernel NAME] [--small] [--iters N]
+
+Each kernel is timed with CUDA events after warm-up, on inputs larger than L2, and
+reported as achieved bandwidth / throughput and as a fraction of the measured peaks in
+``MEASURED_PEAKS.json`` at the repository root (copy bandwidth and cuBLAS bf16 GEMM).
+The torch composition of the same op (cuBLAS / ATen) is timed alongside.  ``--small``
+selects shapes of a few hundred MB for profiler captures.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+from pathlib import Path
+
+import torch
+
+
+def _peaks() -> dict:
+    p = Path(__file__).resolve().parents[2] / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return {"hbm_gbs": d["hbm_gbs"], "tflops": d["bf16_tflops"], "src": "measured"}
+    return {"hbm_gbs": 6650.0, "tflops": 1590.0, "src": "fallback"}
+
+
+def _time(fn, iters: int, warmup: int = 3) -> float:
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for _ in range(iters):
+        fn()
+    t1.record()
+    torch.cuda.synchronize()
+    return t0.elapsed_time(t1) / iters
+
+
+def bench_proj_right(small: bool, iters: int):
+    from . import native
+
+    T, K = (16384, 4096) if small else (65536, 4096)
+    a = torch.randn(T, K, device="cuda", dtype=torch.bfloat16)
+    p = (torch.randn(16, K, device="cuda") / 4).to(torch.bfloat16)
+    ms = _time(lambda: native.proj_right(a, p), iters)
+    ref = _time(lambda: a @ p.T, iters)
+    return dict(kernel="proj_right", shape=[T, K], ms=ms, torch_ms=ref, bytes=T * K * 2 + T * 64, flops=2 * T * K * 16)
+
+
+def bench_proj_left_outer(small: bool, iters: int):
+    from . import native
+
+    N, S, K = (8, 2048, 4096) if small else (32, 2048, 4096)
+    g = torch.randn(N, S, K, device="cuda", dtype=torch.bfloat16)
+    p = (torch.randn(16, K, device="cuda") / 4).to(torch.bfloat16)
+    ap = torch.randn(N * S, 16, device="cuda")
+    acc = torch.zeros(N, 256, device="cuda")
+    ms = _time(lambda: native.proj_left_outer(g, p, ap, acc, 0), iters)
+    apb = ap.view(N, S, 16).to(torch.bfloat16)
+    ref = _time(lambda: (g @ p.T).mT @ apb, iters)
+    return dict(kernel="proj_left_outer", shape=[N, S, K], ms=ms, torch_ms=ref,
+                bytes=N * S * K * 2 + N * S * 64, flops=2 * N * S * K * 16 + 2 * N * S * 256)
+
+
+def bench_cov_syrk(small: bool, iters: int):
+    from . import native
+
+    T, D = (16384, 3072) if small else (65536, 4096)
+    x = torch.randn(T, D, device="cuda", dtype=torch.bfloat16)
+    c = torch.zeros(D, D, device="cuda")
+    ms = _time(lambda: native.cov_syrk(x, [c.data_ptr()], [0, D], None), iters)
+    xf = None
+    ref = _time(lambda: torch.addmm(c, x.T, x.to(torch.bfloat16), out=None) if False else x.T @ x, iters)
+    del xf
+    # only tiles on or above the block diagonal are computed
+    nt = -(-D // 128)
+    frac = (nt * (nt + 1) / 2) / (nt * nt)
+    return dict(kernel="cov_syrk", shape=[T, D], ms=ms, torch_ms=ref, bytes=T * D * 2 + D * D * 4,
+                flops=2 * T * D * D * frac, note="flops count the computed (upper) tiles; torch_ms is the full bf16 GEMM")
+
+
+def bench_tn_gemm(small: bool, iters: int):
+    from . import native
+
+    M, N, K = (8192, 1024, 8192) if small else (32768, 1024, 57344)
+    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    b = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
+    ms = _time(lambda: native.tn_gemm(a, b), iters)
+    ref = _time(lambda: a @ b.T, iters)
+    return dict(kernel="tn_gemm(score)", shape=[M, N, K], ms=ms, torch_ms=ref, bytes=(M + N) * K * 2 + M * N * 4,
+                flops=2 * M * N * K)
+
+
+def bench_ce(small: bool, iters: int):
+    from . import native
+
+    T, V = (4096, 128256) if small else (16384, 128256)
+    z = torch.randn(T, V, device="cuda", dtype=torch.bfloat16)
+    t = torch.randint(0, V, (T,), device="cuda")
+    ms = _time(lambda: native.ce_fwd(z, t, -100), iters)
+    ref = _time(lambda: torch.nn.functional.cross_entropy(z, t, reduction="none"), iters)
+    return dict(kernel="ce_fwd", shape=[T, V], ms=ms, torch_ms=ref, bytes=T * V * 2, flops=0)
+
+
+def bench_rmsnorm(small: bool, iters: int):
+    from . import native
+
+    T, D = (32768, 4096) if small else (131072, 4096)
+    x = torch.randn(T, D, device="cuda", dtype=torch.bfloat16)
+    w = torch.ones(D, device="cuda", dtype=torch.bfloat16)
+    ms = _time(lambda: native.rmsnorm_fwd(x, w, 1e-5), iters)
+    from .functional import rms_norm_ref
+
+    ref = _time(lambda: rms_norm_ref(x, w, 1e-5), iters)
+    return dict(kernel="rmsnorm_fwd", shape=[T, D], ms=ms, torch_ms=ref, bytes=2 * T * D * 2, flops=0)
+
+
+BENCHES = {"proj_right": bench_proj_right, "proj_left_outer": bench_proj_left_outer, "cov_syrk": bench_cov_syrk,
+           "tn_gemm": bench_tn_gemm, "ce_fwd": bench_ce, "rmsnorm_fwd": bench_rmsnorm}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--kernel", choices=sorted(BENCHES), default=None)
+    ap.add_argument("--small", action="store_true")
+    ap.add_argument("--iters", type=int, default=20)
+    args = ap.parse_args()
+    peaks = _peaks()
+    for name, fn in BENCHES.items():
+        if args.kernel and name != args.kernel:
+            continue
+        r = fn(args.small, args.iters)
+        gbs = r["bytes"] / r["ms"] / 1e6
+        tf = r["flops"] / r["ms"] / 1e9
+        r.update(gbs=round(gbs, 1), tflops=round(tf, 1), frac_hbm=round(gbs / peaks["hbm_gbs"], 3),
+                 frac_tc=round(tf / peaks["tflops"], 3), speedup_vs_torch=round(r["torch_ms"] / r["ms"], 2),
+                 peaks=peaks["src"])
+        print(json.dumps(r))
+        torch.cuda.empty_cache()
+
+
+if __name__ == "__main__":
+    main()
