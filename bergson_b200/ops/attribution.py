@@ -99,8 +99,8 @@ def gram_fused_ok(x: Tensor) -> bool:
 
 
 def gram_accumulate(acc: Tensor, x: Tensor) -> None:
-    """``acc [D, D] (fp32) += x^T x`` on the tcgen05 SYRK kernel.  Only 128-wide tiles on
-    or above the block diagonal are written; call ``gram_finalize`` before reading."""
+    """``acc [D, D] (fp32) += x^T x`` on the tcgen05 SYRK kernel.  Only 128 x 256 tiles that
+    touch the upper triangle are written; call ``gram_finalize`` before reading."""
     native.cov_syrk(x.contiguous(), [acc.data_ptr()], [0, acc.shape[0]], None)
     _UPPER_ONLY.add(acc.data_ptr())
 

@@ -209,7 +209,7 @@ extern "C" int bgn_proj_left_outer(const void* g, const void* p, const float* a_
 extern "C" int bgn_tn_gemm(const void* a, const void* b, float* c, long M, int N, int K, long ldc,
                            int fmt, int* status, cudaStream_t stream) {
   if (K % 8 != 0 || !aligned16(a) || !aligned16(b) || M <= 0 || N <= 0) return cudaErrorInvalidValue;
-  constexpr int BN = 128;
+  constexpr int BN = 256;
   CUtensorMap ta, tb;
   if (!make_tmap_3d(&ta, a, fmt, K, M, 1, kBlockM)) return cudaErrorInvalidValue;
   if (!make_tmap_2d(&tb, b, fmt, K, N, BN)) return cudaErrorInvalidValue;

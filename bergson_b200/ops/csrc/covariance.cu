@@ -2,8 +2,8 @@
 //
 // Both MMA operands are the same matrix read "MN-major" (the D axis is contiguous, the
 // reduction runs over the token rows), so a TMA box of 64 columns x 64 rows with the
-// 128-byte swizzle is directly a canonical MN-major UMMA tile.  Only tiles on or above the
-// block diagonal are computed (the caller mirrors them).  The token range is split over
+// 128-byte swizzle is directly a canonical MN-major UMMA tile.  Output tiles are 128 rows x 256
+// columns; only tiles that touch the upper triangle are computed (the caller mirrors them).  The token range is split over
 // gridDim.y CTAs per tile and partial tiles are added to the fp32 output with vector
 // reductions, so one launch fills the machine even for D = 768.
 //
@@ -17,12 +17,15 @@
 
 namespace bgn {
 
-constexpr int kCovBlock = 128;   // output tile edge
-constexpr int kCovBlockK = 64;   // token rows per stage
-constexpr int kCovBoxBytes = 64 * kCovBlockK * 2;  // one 64-column box
-constexpr int kCovOperandBytes = 2 * kCovBoxBytes; // 128 columns
-constexpr int kCovStageBytes = 2 * kCovOperandBytes;
-constexpr int kCovStages = 6;
+constexpr int kCovBlock = 128;    // output tile rows (MMA M)
+constexpr int kCovBlockN = 256;   // output tile columns (MMA N): halves the shared-memory
+                                  // bytes read per flop relative to a 128 x 128 tile
+constexpr int kCovBlockK = 64;    // token rows per stage
+constexpr int kCovBoxBytes = 64 * kCovBlockK * 2;       // one 64-column box
+constexpr int kCovABytes = (kCovBlock / 64) * kCovBoxBytes;
+constexpr int kCovBBytes = (kCovBlockN / 64) * kCovBoxBytes;
+constexpr int kCovStageBytes = kCovABytes + kCovBBytes;
+constexpr int kCovStages = 4;
 constexpr int kCovThreads = 192;
 constexpr int kCovSmemBytes = kCovStages * kCovStageBytes + 1024 + 256;
 
@@ -33,7 +36,8 @@ struct CovParams {
   int world;
   int D;
   long T;
-  int tiles_n;         // tiles per edge
+  int tiles_m;         // 128-row tile rows
+  int tiles_n;         // 256-column tile columns
 };
 
 __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
@@ -55,14 +59,16 @@ cov_syrk_kernel(const __grid_constant__ CUtensorMap tmap, CovParams p, int* stat
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-  // blockIdx.x enumerates upper-triangular tiles row by row.
-  int tm = 0, rem = blockIdx.x, width = p.tiles_n;
-  while (rem >= width) {
+  // blockIdx.x enumerates, row by row, the tiles that touch the upper triangle: tile row tm
+  // starts at tile column tm / 2 (a 256-wide column block covers two 128-high row blocks).
+  int tm = 0, rem = blockIdx.x;
+  while (true) {
+    const int width = p.tiles_n - tm / 2;
+    if (rem < width) break;
     rem -= width;
-    --width;
     ++tm;
   }
-  const int tn = tm + rem;
+  const int tn = tm / 2 + rem;
 
   const long kb_total = (p.T + kCovBlockK - 1) / kCovBlockK;
   const long kb_per = (kb_total + gridDim.y - 1) / gridDim.y;
@@ -83,7 +89,7 @@ cov_syrk_kernel(const __grid_constant__ CUtensorMap tmap, CovParams p, int* stat
     tma_prefetch_desc(&tmap);
   }
   if (warp == 1) {
-    tmem_alloc(tmem_slot, kCovBlock);
+    tmem_alloc(tmem_slot, kCovBlockN);
     tmem_relinquish();
   }
   tc_fence_before();
@@ -103,13 +109,15 @@ cov_syrk_kernel(const __grid_constant__ CUtensorMap tmap, CovParams p, int* stat
           break;
         }
         uint8_t* a_dst = tiles + s * kCovStageBytes;
-        uint8_t* b_dst = a_dst + kCovOperandBytes;
+        uint8_t* b_dst = a_dst + kCovABytes;
         const int row = int((kb_begin + i) * kCovBlockK);
         mbar_expect_tx(&full_bar[s], kCovStageBytes);
-        tma_load_2d(a_dst, &tmap, &full_bar[s], tm * kCovBlock, row);
-        tma_load_2d(a_dst + kCovBoxBytes, &tmap, &full_bar[s], tm * kCovBlock + 64, row);
-        tma_load_2d(b_dst, &tmap, &full_bar[s], tn * kCovBlock, row);
-        tma_load_2d(b_dst + kCovBoxBytes, &tmap, &full_bar[s], tn * kCovBlock + 64, row);
+#pragma unroll
+        for (int b = 0; b < kCovBlock / 64; ++b)
+          tma_load_2d(a_dst + b * kCovBoxBytes, &tmap, &full_bar[s], tm * kCovBlock + b * 64, row);
+#pragma unroll
+        for (int b = 0; b < kCovBlockN / 64; ++b)
+          tma_load_2d(b_dst + b * kCovBoxBytes, &tmap, &full_bar[s], tn * kCovBlockN + b * 64, row);
         issued = i + 1;
       }
       if (!ok) {
@@ -118,7 +126,7 @@ cov_syrk_kernel(const __grid_constant__ CUtensorMap tmap, CovParams p, int* stat
       }
     }
   } else if (warp == 1) {
-    constexpr uint32_t idesc = make_idesc_f16(kCovBlock, kCovBlock, FMT, 1, 1);
+    constexpr uint32_t idesc = make_idesc_f16(kCovBlock, kCovBlockN, FMT, 1, 1);
     bool ok = true;
     for (int i = 0; i < num_kb && ok; ++i) {
       const int s = i % kCovStages;
@@ -131,7 +139,7 @@ cov_syrk_kernel(const __grid_constant__ CUtensorMap tmap, CovParams p, int* stat
       tc_fence_after();
       if (lane == 0) {
         const uint32_t a_addr = smem_u32(tiles + s * kCovStageBytes);
-        const uint32_t b_addr = a_addr + kCovOperandBytes;
+        const uint32_t b_addr = a_addr + kCovABytes;
 #pragma unroll
         for (int k = 0; k < kCovBlockK / 16; ++k) {
           // 16 token rows = two 8-row swizzle groups = 2048 bytes further into each box.
@@ -162,7 +170,7 @@ cov_syrk_kernel(const __grid_constant__ CUtensorMap tmap, CovParams p, int* stat
       float* drow = nullptr;
       if (r < p.D) drow = p.dst[owner] + long(r - p.row_start[owner]) * p.D;
 #pragma unroll 1
-      for (int c = 0; c < kCovBlock; c += 16) {
+      for (int c = 0; c < kCovBlockN; c += 16) {
         float acc[16];
         if (num_kb > 0) {
           tmem_ld_32x16(tmem_base + (uint32_t(quad * 32) << 16) + c, acc);
@@ -170,7 +178,7 @@ cov_syrk_kernel(const __grid_constant__ CUtensorMap tmap, CovParams p, int* stat
 #pragma unroll
           for (int i = 0; i < 16; ++i) acc[i] = 0.f;
         }
-        const int col = tn * kCovBlock + c;
+        const int col = tn * kCovBlockN + c;
         if (drow == nullptr || col >= p.D) continue;
         if (fold_local) {
           const float* lrow = p.local + long(r) * p.D + col;
@@ -195,7 +203,7 @@ cov_syrk_kernel(const __grid_constant__ CUtensorMap tmap, CovParams p, int* stat
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, kCovBlock);
+    tmem_dealloc(tmem_base, kCovBlockN);
   }
 }
 
@@ -247,8 +255,10 @@ extern "C" int bgn_cov_syrk(const void* x, long T, int D, int fmt, float* const*
   p.world = world;
   p.D = D;
   p.T = T > 0 ? T : 0;
-  p.tiles_n = (D + kCovBlock - 1) / kCovBlock;
-  const int tiles = p.tiles_n * (p.tiles_n + 1) / 2;
+  p.tiles_m = (D + kCovBlock - 1) / kCovBlock;
+  p.tiles_n = (D + kCovBlockN - 1) / kCovBlockN;
+  int tiles = 0;
+  for (int tm = 0; tm < p.tiles_m; ++tm) tiles += p.tiles_n - tm / 2;
   const long kb_total = (p.T + kCovBlockK - 1) / kCovBlockK;
   // Split the token range so that the grid covers the SMs, keeping >= 8 k-blocks per CTA.
   long splits = (sm_count + tiles - 1) / tiles;

@@ -5,7 +5,7 @@
 
 extern "C" {
 // dst[r] + (row - row_start[r]) * D + col  receives  sum_t x[t, row] * x[t, col]  for every
-// row owned by rank r (row_start has world + 1 entries), col >= 128 * (row / 128) (block
+// row owned by rank r (row_start has world + 1 entries), col >= 256 * (row / 256) (block
 // upper triangle).  `local` ([D, D] fp32, may be null) is folded into the same adds.
 // dst pointers may be peer-mapped memory of other GPUs.
 int bgn_cov_syrk(const void* x, long T, int D, int fmt, float* const* dst, const int* row_start,

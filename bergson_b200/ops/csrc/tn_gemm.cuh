@@ -30,8 +30,11 @@ struct TnGemmSmem {
   // B tiles must keep 1024-byte alignment for the 128B swizzle pattern.
   static constexpr int kBBytesPadded = (kBBytes + 1023) / 1024 * 1024;
   static constexpr int kStageBytes = kABytes + kBBytesPadded;
+  // Skinny tiles (BLOCK_N <= 32) are bandwidth bound: two CTAs per SM with six stages each
+  // keep more loads in flight and halve the tail of the last wave.
+  static constexpr int kCtasPerSm = BLOCK_N <= 32 ? 2 : 1;
   static constexpr int stages(int extra_bytes) {
-    int avail = 227 * 1024 - 1024 /*align slack*/ - 256 /*barriers*/ - extra_bytes;
+    int avail = (227 * 1024) / kCtasPerSm - 1024 /*align slack*/ - 256 /*barriers*/ - extra_bytes;
     int s = avail / kStageBytes;
     return s > 8 ? 8 : s;
   }
@@ -43,7 +46,7 @@ struct TnGemmSmem {
 // `finish(...)` after all chunks (all 128 epilogue threads call it).
 
 template <int BLOCK_N, int FMT, class Epilogue>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+__global__ void __launch_bounds__(kGemmThreads, TnGemmSmem<BLOCK_N>::kCtasPerSm)
 tn_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                TnGemmShape shape, int stages, Epilogue epi, int* status) {
   using S = TnGemmSmem<BLOCK_N>;
