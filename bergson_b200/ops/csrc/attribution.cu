@@ -76,23 +76,20 @@ struct StoreF32Epilogue {
   float* out;
   long ld;
   int rows;
-  int n_total;
-  int block_n;
 
   __device__ __forceinline__ void operator()(int row, int c, const float (&acc)[16], int tile_m,
-                                             int tile_n, int batch, void*) const {
+                                             int out_col0, int n_valid, int batch, void*) const {
     const long r = long(tile_m) * kBlockM + row;
-    if (r >= rows) return;
-    const int col = tile_n * block_n + c;
-    float* dst = out + (long(batch) * rows + r) * ld + col;
-    if (col + 16 <= n_total && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+    if (r >= rows || c >= n_valid) return;
+    float* dst = out + (long(batch) * rows + r) * ld + out_col0 + c;
+    if (c + 16 <= n_valid && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
 #pragma unroll
       for (int i = 0; i < 16; i += 4)
         *reinterpret_cast<float4*>(dst + i) = make_float4(acc[i], acc[i + 1], acc[i + 2], acc[i + 3]);
     } else {
 #pragma unroll
       for (int i = 0; i < 16; ++i)
-        if (col + i < n_total) dst[i] = acc[i];
+        if (c + i < n_valid) dst[i] = acc[i];
     }
   }
   __device__ __forceinline__ void finish(int, int, int, int, void*, bool) const {}
@@ -111,7 +108,7 @@ struct OuterEpilogue {
   static constexpr int kSmemBytes = (kBlockM * kGStride + kBlockM * 16) * 4;
 
   __device__ __forceinline__ void operator()(int row, int c, const float (&v)[16], int tile_m, int,
-                                             int batch, void* smem) const {
+                                             int, int batch, void* smem) const {
     float* gs = reinterpret_cast<float*>(smem);
     float* as = gs + kBlockM * kGStride;
 #pragma unroll
@@ -153,7 +150,7 @@ struct OuterEpilogue {
 };
 
 template <int BLOCK_N, int FMT, class Epi>
-static cudaError_t launch_tn(const CUtensorMap& ta, const CUtensorMap& tb, TnGemmShape shape,
+static cudaError_t launch_tn(const CUtensorMap& ta, const TmapSet& tb, TnGemmShape shape,
                              dim3 grid, Epi epi, int epi_smem, int* status, cudaStream_t stream) {
   using S = TnGemmSmem<BLOCK_N>;
   const int stages = S::stages(epi_smem);
@@ -178,11 +175,12 @@ using namespace bgn;
 extern "C" int bgn_proj_right(const void* a, const void* p, float* out, long T, int K, int fmt,
                               int* status, cudaStream_t stream) {
   if (K % 8 != 0 || !aligned16(a) || !aligned16(p) || T <= 0) return cudaErrorInvalidValue;
-  CUtensorMap ta, tb;
+  CUtensorMap ta;
+  TmapSet tb;
   if (!make_tmap_3d(&ta, a, fmt, K, T, 1, kBlockM)) return cudaErrorInvalidValue;
-  if (!make_tmap_2d(&tb, p, fmt, K, 16, 16)) return cudaErrorInvalidValue;
-  TnGemmShape shape{int(T), K, 16};
-  StoreF32Epilogue epi{out, 16, int(T), 16, 16};
+  if (!make_tmap_2d(&tb.m[0], p, fmt, K, 16, 16)) return cudaErrorInvalidValue;
+  TnGemmShape shape{int(T), K, 16, 0};
+  StoreF32Epilogue epi{out, 16, int(T)};
   dim3 grid((T + kBlockM - 1) / kBlockM, 1, 1);
   cudaError_t e = fmt == 1 ? launch_tn<16, 1>(ta, tb, shape, grid, epi, 0, status, stream)
                            : launch_tn<16, 0>(ta, tb, shape, grid, epi, 0, status, stream);
@@ -194,10 +192,11 @@ extern "C" int bgn_proj_left_outer(const void* g, const void* p, const float* a_
                                    cudaStream_t stream) {
   if (K % 8 != 0 || !aligned16(g) || !aligned16(p) || !aligned16(a_proj) || N <= 0 || S <= 0)
     return cudaErrorInvalidValue;
-  CUtensorMap ta, tb;
+  CUtensorMap ta;
+  TmapSet tb;
   if (!make_tmap_3d(&ta, g, fmt, K, S, N, kBlockM)) return cudaErrorInvalidValue;
-  if (!make_tmap_2d(&tb, p, fmt, K, 16, 16)) return cudaErrorInvalidValue;
-  TnGemmShape shape{S, K, 16};
+  if (!make_tmap_2d(&tb.m[0], p, fmt, K, 16, 16)) return cudaErrorInvalidValue;
+  TnGemmShape shape{S, K, 16, 0};
   OuterEpilogue epi{a_proj, acc, ld, col_off, S};
   dim3 grid((S + kBlockM - 1) / kBlockM, 1, N);
   cudaError_t e =
@@ -210,12 +209,36 @@ extern "C" int bgn_tn_gemm(const void* a, const void* b, float* c, long M, int N
                            int fmt, int* status, cudaStream_t stream) {
   if (K % 8 != 0 || !aligned16(a) || !aligned16(b) || M <= 0 || N <= 0) return cudaErrorInvalidValue;
   constexpr int BN = 256;
-  CUtensorMap ta, tb;
+  CUtensorMap ta;
+  TmapSet tb;
   if (!make_tmap_3d(&ta, a, fmt, K, M, 1, kBlockM)) return cudaErrorInvalidValue;
-  if (!make_tmap_2d(&tb, b, fmt, K, N, BN)) return cudaErrorInvalidValue;
-  TnGemmShape shape{int(M), K, N};
-  StoreF32Epilogue epi{c, ldc, int(M), N, BN};
+  if (!make_tmap_2d(&tb.m[0], b, fmt, K, N, BN)) return cudaErrorInvalidValue;
+  TnGemmShape shape{int(M), K, N, 0};
+  StoreF32Epilogue epi{c, ldc, int(M)};
   dim3 grid((M + kBlockM - 1) / kBlockM, (N + BN - 1) / BN, 1);
+  cudaError_t e = fmt == 1 ? launch_tn<BN, 1>(ta, tb, shape, grid, epi, 0, status, stream)
+                           : launch_tn<BN, 0>(ta, tb, shape, grid, epi, 0, status, stream);
+  return int(e);
+}
+
+// c[M, world * N] = a[M, K] * [b_0; b_1; ...]^T where b_r [N, K] is rank r's buffer (this GPU's
+// or peer-mapped): the all-gather of B is fused into the operand loads -- every CTA pulls
+// the B tiles it needs straight from the owning GPU with plain TMA loads while the tensor
+// cores work on the previous stage.
+extern "C" int bgn_tn_gemm_gathered(const void* a, const void* const* b, int world, float* c, long M, int N,
+                                    int K, long ldc, int fmt, int* status, cudaStream_t stream) {
+  if (K % 8 != 0 || !aligned16(a) || M <= 0 || N <= 0 || world < 1 || world > 8) return cudaErrorInvalidValue;
+  constexpr int BN = 256;
+  CUtensorMap ta;
+  TmapSet tb;
+  if (!make_tmap_3d(&ta, a, fmt, K, M, 1, kBlockM)) return cudaErrorInvalidValue;
+  for (int r = 0; r < world; ++r) {
+    if (!aligned16(b[r]) || !make_tmap_2d(&tb.m[r], b[r], fmt, K, N, BN)) return cudaErrorInvalidValue;
+  }
+  const int tiles_per_src = (N + BN - 1) / BN;
+  TnGemmShape shape{int(M), K, N, tiles_per_src};
+  StoreF32Epilogue epi{c, ldc, int(M)};
+  dim3 grid((M + kBlockM - 1) / kBlockM, world * tiles_per_src, 1);
   cudaError_t e = fmt == 1 ? launch_tn<BN, 1>(ta, tb, shape, grid, epi, 0, status, stream)
                            : launch_tn<BN, 0>(ta, tb, shape, grid, epi, 0, status, stream);
   return int(e);

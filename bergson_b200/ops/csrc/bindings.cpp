@@ -222,6 +222,20 @@ at::Tensor tn_gemm(at::Tensor a, at::Tensor b) {
   return c;
 }
 
+at::Tensor tn_gemm_gathered(at::Tensor a, std::vector<int64_t> b_ptrs, int64_t n_per_rank) {
+  // b_ptrs: device addresses of every rank's [n_per_rank, K] block of B, same dtype as a.
+  CHECK_CUDA_CONTIG(a);
+  const int world = (int)b_ptrs.size();
+  TORCH_CHECK(a.dim() == 2 && world >= 1 && world <= 8);
+  c10::cuda::CUDAGuard guard(a.device());
+  auto c = at::empty({a.size(0), world * n_per_rank}, a.options().dtype(at::kFloat));
+  const void* b[8];
+  for (int r = 0; r < world; ++r) b[r] = reinterpret_cast<const void*>(b_ptrs[r]);
+  check(bgn_tn_gemm_gathered(a.data_ptr(), b, world, c.data_ptr<float>(), a.size(0), (int)n_per_rank, (int)a.size(1),
+                             c.stride(0), fmt16(a), status_ptr(a), stream()), "tn_gemm_gathered");
+  return c;
+}
+
 void finalize_rows(at::Tensor acc, at::Tensor out, c10::optional<at::Tensor> row_index, double lo, double hi,
                    bool unit_norm) {
   TORCH_CHECK(acc.is_cuda() && acc.is_contiguous() && acc.scalar_type() == at::kFloat && acc.dim() == 2);
@@ -263,7 +277,7 @@ void row_sumsq(at::Tensor x, at::Tensor out) {
 }
 
 void cov_syrk(at::Tensor x, std::vector<int64_t> dst_ptrs, std::vector<int64_t> row_start,
-              c10::optional<at::Tensor> local) {
+              c10::optional<at::Tensor> local, bool full, int64_t num_rows) {
   // x: [T, D] 16-bit; dst_ptrs: device addresses (this GPU's or peer-mapped) of every rank's
   // fp32 row shard; row_start: world + 1 row boundaries.
   TORCH_CHECK(x.is_cuda() && x.dim() == 2 && x.is_contiguous());
@@ -281,8 +295,10 @@ void cov_syrk(at::Tensor x, std::vector<int64_t> dst_ptrs, std::vector<int64_t> 
     loc = local->data_ptr<float>();
   }
   const int sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
-  check(bgn_cov_syrk(x.data_ptr(), x.size(0), (int)x.size(1), fmt16(x), dst, rs, world, loc, sms, status_ptr(x),
-                     stream()), "cov_syrk");
+  // num_rows < 0: use every row of x; num_rows == 0: only push `local`.
+  const long T = num_rows < 0 ? x.size(0) : std::min<int64_t>(num_rows, x.size(0));
+  check(bgn_cov_syrk(x.data_ptr(), T, (int)x.size(1), fmt16(x), dst, rs, world, loc, full ? 1 : 0, sms,
+                     status_ptr(x), stream()), "cov_syrk");
 }
 
 at::Tensor kernel_status(int64_t device) { return status_tensor((int)device); }
@@ -302,9 +318,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("proj_right", &proj_right);
   m.def("proj_left_outer", &proj_left_outer);
   m.def("tn_gemm", &tn_gemm);
+  m.def("tn_gemm_gathered", &tn_gemm_gathered);
   m.def("finalize_rows", &finalize_rows);
   m.def("adamw_step", &adamw_step);
   m.def("row_sumsq", &row_sumsq);
-  m.def("cov_syrk", &cov_syrk);
+  m.def("cov_syrk", &cov_syrk, py::arg("x"), py::arg("dst_ptrs"), py::arg("row_start"), py::arg("local"),
+        py::arg("full") = false, py::arg("num_rows") = -1);
   m.def("kernel_status", &kernel_status);
 }

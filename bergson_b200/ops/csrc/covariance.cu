@@ -38,6 +38,8 @@ struct CovParams {
   long T;
   int tiles_m;         // 128-row tile rows
   int tiles_n;         // 256-column tile columns
+  int full;            // 1: every tile is visited (used when the destination must end up
+                       // holding complete rows, e.g. the cross-rank reduce-scatter)
 };
 
 __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
@@ -63,12 +65,12 @@ cov_syrk_kernel(const __grid_constant__ CUtensorMap tmap, CovParams p, int* stat
   // starts at tile column tm / 2 (a 256-wide column block covers two 128-high row blocks).
   int tm = 0, rem = blockIdx.x;
   while (true) {
-    const int width = p.tiles_n - tm / 2;
+    const int width = p.full ? p.tiles_n : p.tiles_n - tm / 2;
     if (rem < width) break;
     rem -= width;
     ++tm;
   }
-  const int tn = tm / 2 + rem;
+  const int tn = (p.full ? 0 : tm / 2) + rem;
 
   const long kb_total = (p.T + kCovBlockK - 1) / kCovBlockK;
   const long kb_per = (kb_total + gridDim.y - 1) / gridDim.y;
@@ -230,7 +232,8 @@ static EncodeTiledFn cov_encode_fn() {
 using namespace bgn;
 
 extern "C" int bgn_cov_syrk(const void* x, long T, int D, int fmt, float* const* dst, const int* row_start,
-                            int world, const float* local, int sm_count, int* status, cudaStream_t stream) {
+                            int world, const float* local, int full, int sm_count, int* status,
+                            cudaStream_t stream) {
   if (D % 8 != 0 || (reinterpret_cast<uintptr_t>(x) & 15) || world < 1 || world > 8)
     return int(cudaErrorInvalidValue);
   if (T <= 0 && local == nullptr) return 0;
@@ -257,8 +260,9 @@ extern "C" int bgn_cov_syrk(const void* x, long T, int D, int fmt, float* const*
   p.T = T > 0 ? T : 0;
   p.tiles_m = (D + kCovBlock - 1) / kCovBlock;
   p.tiles_n = (D + kCovBlockN - 1) / kCovBlockN;
+  p.full = full ? 1 : 0;
   int tiles = 0;
-  for (int tm = 0; tm < p.tiles_m; ++tm) tiles += p.tiles_n - tm / 2;
+  for (int tm = 0; tm < p.tiles_m; ++tm) tiles += p.full ? p.tiles_n : p.tiles_n - tm / 2;
   const long kb_total = (p.T + kCovBlockK - 1) / kCovBlockK;
   // Split the token range so that the grid covers the SMs, keeping >= 8 k-blocks per CTA.
   long splits = (sm_count + tiles - 1) / tiles;

@@ -27,6 +27,11 @@ int bgn_proj_left_outer(const void* g, const void* p, const float* a_proj, float
 int bgn_tn_gemm(const void* a, const void* b, float* c, long M, int N, int K, long ldc, int fmt,
                 int* status, cudaStream_t stream);
 
+// c[M, world * N] (fp32) = a[M, K] * concat_r(b[r])^T with b[r] [N, K] in rank r's (possibly
+// peer-mapped) memory: all-gather of B fused into the GEMM's operand loads.
+int bgn_tn_gemm_gathered(const void* a, const void* const* b, int world, float* c, long M, int N, int K,
+                         long ldc, int fmt, int* status, cudaStream_t stream);
+
 // acc fp32 [N, D] -> out rows (type code `out_type`) with clamp to [lo, hi]; if unit_norm,
 // every row is divided by max(||row||, eps) computed on the rounded values.  Row r goes to
 // out + row_index[r] * out_ld (row_index == nullptr means r).

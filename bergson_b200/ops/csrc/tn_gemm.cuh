@@ -18,9 +18,16 @@ constexpr int kUmmaK = 16;
 constexpr int kGemmThreads = 192;
 
 struct TnGemmShape {
-  int rows;     // rows of A per batch item
-  int k;        // reduction length
-  int n_total;  // rows of B
+  int rows;            // rows of A per batch item
+  int k;               // reduction length
+  int n_total;         // rows of B (per source when B is gathered from several buffers)
+  int tiles_per_src;   // 0: one B buffer; else n-tiles per source buffer (gridDim.y = sources * this)
+};
+
+// B operand maps: index 0 for an ordinary GEMM; one map per rank when the rows of B are
+// spread over the ranks' buffers (plain, non-multicast TMA loads, also from peer memory).
+struct TmapSet {
+  CUtensorMap m[8];
 };
 
 template <int BLOCK_N>
@@ -40,14 +47,16 @@ struct TnGemmSmem {
   }
 };
 
-// Epilogue contract:  void operator()(int quad_row /*0..127*/, int col0, const float (&acc)[16],
-//                                     int tile_m, int tile_n, int batch, void* epi_smem)
+// Epilogue contract:  void operator()(int quad_row /*0..127*/, int c /*chunk start in tile*/,
+//                                     const float (&acc)[16], int tile_m, int out_col0 /*global
+//                                     column of the tile's first column*/, int n_valid /*valid
+//                                     columns in the tile*/, int batch, void* epi_smem)
 // called once per 16-column chunk by each of the 128 epilogue threads, followed by
 // `finish(...)` after all chunks (all 128 epilogue threads call it).
 
 template <int BLOCK_N, int FMT, class Epilogue>
 __global__ void __launch_bounds__(kGemmThreads, TnGemmSmem<BLOCK_N>::kCtasPerSm)
-tn_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+tn_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ TmapSet tmaps_b,
                TnGemmShape shape, int stages, Epilogue epi, int* status) {
   using S = TnGemmSmem<BLOCK_N>;
   extern __shared__ uint8_t smem_raw[];
@@ -67,6 +76,12 @@ tn_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   const int tile_m = blockIdx.x, tile_n = blockIdx.y, batch = blockIdx.z;
   const int num_kb = (shape.k + kBlockK - 1) / kBlockK;
   constexpr uint32_t kTmemCols = BLOCK_N < 32 ? 32 : BLOCK_N;
+  // Which B buffer this n-tile reads, the row coordinate inside it and the output column.
+  const int src = shape.tiles_per_src > 0 ? tile_n / shape.tiles_per_src : 0;
+  const int n_coord = (shape.tiles_per_src > 0 ? tile_n % shape.tiles_per_src : tile_n) * BLOCK_N;
+  const int out_col0 = src * shape.n_total + n_coord;
+  const int n_valid = shape.n_total - n_coord < BLOCK_N ? shape.n_total - n_coord : BLOCK_N;
+  const CUtensorMap* tmap_b = &tmaps_b.m[src];
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; ++s) {
@@ -76,7 +91,7 @@ tn_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     mbar_init(tmem_full_bar, 1);
     fence_barrier_init();
     tma_prefetch_desc(&tmap_a);
-    tma_prefetch_desc(&tmap_b);
+    tma_prefetch_desc(tmap_b);
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, kTmemCols);
@@ -103,7 +118,7 @@ tn_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         uint8_t* b_dst = a_dst + S::kABytes;
         mbar_expect_tx(&full_bar[s], S::kABytes + S::kBBytes);
         tma_load_3d(a_dst, &tmap_a, &full_bar[s], kb * kBlockK, tile_m * kBlockM, batch);
-        tma_load_2d(b_dst, &tmap_b, &full_bar[s], kb * kBlockK, tile_n * BLOCK_N);
+        tma_load_2d(b_dst, tmap_b, &full_bar[s], kb * kBlockK, n_coord);
         issued = kb + 1;
       }
       if (!ok) {
@@ -155,12 +170,12 @@ tn_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       for (int c = 0; c < BLOCK_N; c += 16) {
         float acc[16];
         tmem_ld_32x16(tmem_base + (uint32_t(quad * 32) << 16) + c, acc);
-        epi(row, c, acc, tile_m, tile_n, batch, epi_smem);
+        epi(row, c, acc, tile_m, out_col0, n_valid, batch, epi_smem);
       }
     }
     // finish() contains a named barrier over the 128 epilogue threads, so every one of
     // them calls it on both the normal and the give-up path.
-    epi.finish(row, tile_m, tile_n, batch, epi_smem, ok);
+    epi.finish(row, tile_m, out_col0, batch, epi_smem, ok);
   }
 
   tc_fence_before();

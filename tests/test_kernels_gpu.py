@@ -205,3 +205,32 @@ def test_cov_syrk_row_shards_and_fold(native):
         mask[i : i + 128, (i // 256) * 256 :] = True
     torch.testing.assert_close(got[mask], ref[mask], atol=0.2, rtol=1e-3)
     assert got[~mask].abs().max() == 0
+
+
+def test_tn_gemm_gathered_two_buffers(native):
+    """All-gather fused into the operand loads: two "ranks" emulated as two buffers."""
+    torch.manual_seed(8)
+    M, K, N = 300, 520, 200
+    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    b0 = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
+    b1 = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
+    c = native.tn_gemm_gathered(a, [b0.data_ptr(), b1.data_ptr()], N)
+    _status_ok(native)
+    ref = a.float() @ torch.cat([b0, b1]).float().T
+    torch.testing.assert_close(c, ref, atol=1e-3 * K**0.5 + 1e-2, rtol=1e-2)
+
+
+def test_cov_syrk_full_tiles_push(native):
+    """Pure push of a local accumulator into two row-shard destinations (T = 0)."""
+    D = 392
+    local = torch.randn(D, D, device="cuda")
+    r0, r1 = torch.zeros(196, D, device="cuda"), torch.zeros(D - 196, D, device="cuda")
+    x = torch.zeros(64, D, device="cuda", dtype=torch.bfloat16)
+    native.cov_syrk(x, [r0.data_ptr(), r1.data_ptr()], [0, 196, D], local, True, 0)
+    _status_ok(native)
+    torch.testing.assert_close(torch.cat([r0, r1]), local)
+    xs = torch.randn(1000, D, device="cuda", dtype=torch.bfloat16)
+    r0.zero_(), r1.zero_()
+    native.cov_syrk(xs, [r0.data_ptr(), r1.data_ptr()], [0, 196, D], local, True, -1)
+    _status_ok(native)
+    torch.testing.assert_close(torch.cat([r0, r1]), local + xs.float().T @ xs.float(), atol=0.2, rtol=1e-3)
