@@ -65,9 +65,27 @@ class ModelArgs:
 
 @dataclass
 class CausalLMOutput:
+    """Forward result; indexable like an HF ``ModelOutput`` (by field name, or by position
+    over the fields that are set, loss first)."""
+
     logits: Tensor | None = None
     loss: Tensor | None = None
     hidden_states: Tensor | None = None
+
+    def _present(self) -> list[tuple[str, Tensor]]:
+        order = ("loss", "logits", "hidden_states")
+        return [(k, getattr(self, k)) for k in order if getattr(self, k) is not None]
+
+    def __getitem__(self, key):
+        if isinstance(key, str):
+            return getattr(self, key)
+        return self._present()[key][1]
+
+    def keys(self):
+        return [k for k, _ in self._present()]
+
+    def __contains__(self, key) -> bool:
+        return key in self.keys()
 
 
 class Backbone(nn.Module):

@@ -234,3 +234,24 @@ def test_cov_syrk_full_tiles_push(native):
     native.cov_syrk(xs, [r0.data_ptr(), r1.data_ptr()], [0, 196, D], local, True, -1)
     _status_ok(native)
     torch.testing.assert_close(torch.cat([r0, r1]), local + xs.float().T @ xs.float(), atol=0.2, rtol=1e-3)
+
+
+def test_adamw_step_and_row_sumsq(native):
+    torch.manual_seed(9)
+    n = 10007
+    p = torch.randn(n, device="cuda")
+    m, v = torch.zeros(n, device="cuda"), torch.zeros(n, device="cuda")
+    g = torch.randn(n, device="cuda").to(torch.bfloat16)
+    pm = torch.empty(n, device="cuda", dtype=torch.bfloat16)
+    ref_p = torch.nn.Parameter(p.clone())
+    opt = torch.optim.AdamW([ref_p], lr=1e-2, betas=(0.9, 0.99), eps=1e-8, weight_decay=0.1)
+    for step in (1, 2, 3):
+        native.adamw_step(p, m, v, g, pm, 1e-2, 0.9, 0.99, 1e-8, 0.0, 0.1, step, 1.0)
+        ref_p.grad = g.float()
+        opt.step()
+    torch.testing.assert_close(p, ref_p.data, atol=1e-5, rtol=1e-4)
+    torch.testing.assert_close(pm.float(), p, atol=1e-2, rtol=1e-2)
+    x = torch.randn(33, 1000, device="cuda", dtype=torch.float16)
+    out = torch.ones(33, device="cuda")
+    native.row_sumsq(x, out)
+    torch.testing.assert_close(out, 1 + x.float().pow(2).sum(1), rtol=1e-4, atol=1e-3)
