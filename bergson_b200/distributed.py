@@ -84,6 +84,13 @@ def dist_worker(worker: Callable, rank: int, local_rank: int, world_size: int, m
                 *worker_args):
     os.environ.update(LOCAL_RANK=str(local_rank), RANK=str(rank), WORLD_SIZE=str(world_size),
                       MASTER_ADDR=master_addr, MASTER_PORT=master_port)
+    # Hang diagnosis: BERGSON_B200_DUMP_AFTER=<seconds> prints every thread's stack to stderr
+    # that long after the worker started (and keeps running).
+    if os.environ.get("BERGSON_B200_DUMP_AFTER"):
+        import faulthandler
+        import sys
+
+        faulthandler.dump_traceback_later(float(os.environ["BERGSON_B200_DUMP_AFTER"]), repeat=False, file=sys.stderr)
     try:
         with nullcontext() if rank == 0 else redirect_stdout(io.StringIO()):
             worker(rank, local_rank, world_size, *worker_args)

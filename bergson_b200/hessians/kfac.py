@@ -107,24 +107,58 @@ class _FactorCollector(HookCollectorBase):
 
     # -- flush ----------------------------------------------------------------------------
 
-    def _symmetrize(self, store: dict[str, Tensor]) -> None:
-        """The fused SYRK fills the block-upper triangle only; mirror it."""
-        for name, m in store.items():
-            if getattr(m, "_upper_only", False):
-                store[name] = torch.triu(m) + torch.triu(m, 1).T
-
     def _row_shards(self, store: dict[str, Tensor]) -> dict[str, Tensor]:
-        """Sum over ranks and keep this rank's rows."""
+        """Sum over ranks and keep this rank's rows.  On NVLink-connected GPUs the reduction
+        is done by the covariance kernel's epilogue pushing rows into their owners' peer
+        memory; otherwise (CPU, single rank, no symmetric memory) by NCCL / Gloo."""
         sc = self.shard_computer
+        names = [n for n in self.target_info if n in store]
+        if sc.dist and names and store[names[0]].is_cuda:
+            try:
+                return self._row_shards_peer(store, names)
+            except Exception as e:  # noqa: BLE001 - fall back to the library collective
+                self.logger.warning(f"peer-memory reduce-scatter unavailable ({e}); using all_reduce")
         out = {}
-        for name in self.target_info:
-            if name not in store:
-                continue
+        for name in names:
             full = store[name]
             if sc.dist:
                 dist.all_reduce(full, op=dist.ReduceOp.SUM)
             lo, hi = sc.shard_bounds(full.shape[0])
             out[name] = full[lo:hi].to(self.dtype).contiguous()
+        return out
+
+    def _row_shards_peer(self, store: dict[str, Tensor], names: list[str]) -> dict[str, Tensor]:
+        from ..parallel.peer import PeerHeap, symmetric_memory_available
+        from ..ops import native
+        from .sharded_computation import shard_bounds
+
+        if not symmetric_memory_available():
+            raise RuntimeError("symmetric memory not available")
+        world, rank = self.shard_computer.world_size, self.shard_computer.rank
+        # Same offsets on every rank: regions are sized for the largest (rank 0) shard.
+        offsets, total = {}, 0
+        for n in names:
+            d = store[n].shape[0]
+            offsets[n] = total
+            total += (shard_bounds(d, 0, world)[1]) * d
+        heap = PeerHeap(total, torch.float32)
+        heap.local.zero_()
+        heap.barrier()
+        dummy: dict[int, Tensor] = {}
+        for n in names:
+            full = store[n].contiguous()
+            d = full.shape[0]
+            bounds = [shard_bounds(d, r, world) for r in range(world)]
+            x = dummy.setdefault(d, torch.zeros(64, d, device=full.device, dtype=torch.bfloat16))
+            native.cov_syrk(x, [heap.ptr(r, offsets[n]) for r in range(world)], [b[0] for b in bounds] + [d], full,
+                            True, 0)
+        heap.barrier()
+        out = {}
+        for n in names:
+            d = store[n].shape[0]
+            lo, hi = shard_bounds(d, rank, world)
+            out[n] = heap.local[offsets[n] : offsets[n] + (hi - lo) * d].view(hi - lo, d).to(self.dtype).clone()
+        heap.barrier()
         return out
 
     def teardown(self) -> None:

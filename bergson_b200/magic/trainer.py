@@ -448,6 +448,8 @@ def _backward(self: Trainer, ckpt_dir: str, data: DataStream, bwd_state: Backwar
         t0 = time.monotonic()
         fwd_state.load(ckpt) if isinstance(ckpt, str) else fwd_state.copy_(ckpt)
         fwd_state.batch_index = idx
+        if dist.is_initialized() and isinstance(ckpt, str):
+            dist.barrier()  # every rank has read its file before rank 0 may delete the directory
         if debug and main:
             bar.write(f"Loaded checkpoint {ckpt if isinstance(ckpt, str) else idx} in {time.monotonic() - t0:.2f}s")
         if idx == expected:

@@ -1,0 +1,67 @@
+"""Two gloo ranks on CPU: same stores, factors and MAGIC scores as a single process; a rank
+that fails makes the launcher raise."""
+
+import numpy as np
+import pytest
+import torch
+
+from bergson_b200.__main__ import main
+from bergson_b200.data import load_gradients, load_scores
+from bergson_b200.hessians.preconditioner import _load_full
+
+MODEL = "native:llama-tiny?vocab_size=256"
+TRAIN = "synthetic:zipf?n=24&len=16&vocab=256&seed=0&min_len=6"
+QUERY = "synthetic:zipf?n=4&len=16&vocab=256&seed=1&min_len=8"
+
+
+def run(*args):
+    main([str(a) for a in args])
+
+
+def test_build_two_ranks_equals_one(tmp_path):
+    for n in (1, 2):
+        run("build", tmp_path / f"w{n}", "--model", MODEL, "--data.dataset", TRAIN, "--projection_dim", "4",
+            "--token_batch_size", "64", "--nproc_per_node", n)
+    a, b = np.asarray(load_gradients(tmp_path / "w1")), np.asarray(load_gradients(tmp_path / "w2"))
+    np.testing.assert_allclose(a, b, rtol=1e-4, atol=1e-6)
+    assert int(torch.load(tmp_path / "w1" / "total_processed.pt")) == int(torch.load(tmp_path / "w2" / "total_processed.pt"))
+
+
+def test_ekfac_two_ranks_equals_one(tmp_path):
+    for n in (1, 2):
+        run("ekfac", tmp_path / f"e{n}", "--model", MODEL, "--index_cfg.data.dataset", TRAIN,
+            "--hessian_pipeline_cfg.query.dataset", QUERY, "--method", "kfac", "--hessian_cfg.ev_correction", "true",
+            "--use_dataset_labels", "--token_batch_size", "64", "--nproc_per_node", n)
+    for sub in ("activation_sharded", "gradient_sharded", "eigenvalue_correction_sharded"):
+        one = _load_full(tmp_path / "e1" / "hessian" / "kfac", sub, "cpu")
+        two = _load_full(tmp_path / "e2" / "hessian" / "kfac", sub, "cpu")
+        for k in one:
+            assert (one[k] - two[k]).norm() / one[k].norm() < 1e-3, (sub, k)
+    s1, s2 = load_scores(tmp_path / "e1" / "scores")[:], load_scores(tmp_path / "e2" / "scores")[:]
+    assert np.corrcoef(s1.ravel(), s2.ravel())[0, 1] > 0.999
+
+
+def test_magic_two_ranks_equals_one(tmp_path):
+    for n in (1, 2):
+        run("magic", tmp_path / f"m{n}", "--model", MODEL, "--data.dataset", "synthetic:zipf?n=16&len=12&vocab=256",
+            "--query.dataset", "synthetic:zipf?n=4&len=12&vocab=256&seed=1", "--batch_size", "4", "--query_method", "mean",
+            "--lr", "1e-3", "--nproc_per_node", n)
+    a, b = load_scores(tmp_path / "m1" / "scores")[:], load_scores(tmp_path / "m2" / "scores")[:]
+    # equal-length rows: the per-rank token means that DDP averages equal the global mean
+    np.testing.assert_allclose(a, b, rtol=1e-3, atol=1e-4 * np.abs(a).max())
+
+
+def _boom(rank, local_rank, world):
+    from bergson_b200.distributed import init_dist
+
+    init_dist(rank, local_rank, world)
+    if rank == 1:
+        raise RuntimeError("injected failure")
+
+
+def test_failed_rank_raises_in_parent():
+    from bergson_b200.config import DistributedConfig
+    from bergson_b200.distributed import launch_distributed_run
+
+    with pytest.raises(RuntimeError, match="child exited"):
+        launch_distributed_run("boom", _boom, [], DistributedConfig(nproc_per_node=2))
