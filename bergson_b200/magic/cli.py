@@ -37,6 +37,8 @@ def compute_query_gradients(trainer: Trainer, fwd_state: TrainerState, query_str
     and ranks.  Returns ``(grads, loss)``."""
     world = dist.get_world_size() if dist.is_initialized() else 1
     main = not dist.is_initialized() or dist.get_rank() == 0
+    # Sharded parameters: the gather's backward sums gradients over ranks; replicated
+    # parameters: the all-reduce below sums them.  Either way the mean divides by world.
     denom = len(query_stream) * world
     params = {k: v.detach().requires_grad_(True) for k, v in fwd_state.params.items()}
     call = lambda p, mb: trainer.call_model(p, mb, fwd_state.buffers)  # noqa: E731

@@ -24,6 +24,35 @@ def _world(group) -> int:
     return dist.get_world_size(group) if dist.is_initialized() else 1
 
 
+def _is_gloo(group) -> bool:
+    return dist.get_backend(group) == "gloo"
+
+
+def _all_gather_raw(shard: Tensor, group) -> Tensor:
+    w = _world(group)
+    shard = shard.contiguous()
+    if _is_gloo(group):  # Gloo has no fused all-gather into one tensor
+        parts = [torch.empty_like(shard) for _ in range(w)]
+        dist.all_gather(parts, shard, group=group)
+        return torch.cat(parts, dim=0)
+    out = torch.empty((w * shard.shape[0], *shard.shape[1:]), dtype=shard.dtype, device=shard.device)
+    dist.all_gather_into_tensor(out, shard, group=group)
+    return out
+
+
+def _reduce_scatter_raw(full: Tensor, group) -> Tensor:
+    w = _world(group)
+    rows = full.shape[0] // w
+    if _is_gloo(group):  # Gloo has no reduce-scatter: all-reduce and keep this rank's rows
+        tmp = full.clone()
+        dist.all_reduce(tmp, op=dist.ReduceOp.SUM, group=group)
+        r = dist.get_rank(group)
+        return tmp[r * rows : (r + 1) * rows].clone()
+    out = torch.empty((rows, *full.shape[1:]), dtype=full.dtype, device=full.device)
+    dist.reduce_scatter_tensor(out, full.contiguous(), op=dist.ReduceOp.SUM, group=group)
+    return out
+
+
 class _AllReduceSum(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x: Tensor, group):
@@ -41,10 +70,7 @@ class _AllGatherRows(torch.autograd.Function):
     @staticmethod
     def forward(ctx, shard: Tensor, group):
         ctx.group = group
-        w = _world(group)
-        out = torch.empty((w * shard.shape[0], *shard.shape[1:]), dtype=shard.dtype, device=shard.device)
-        dist.all_gather_into_tensor(out, shard.contiguous(), group=group)
-        return out
+        return _all_gather_raw(shard, group)
 
     @staticmethod
     def backward(ctx, g: Tensor):
@@ -55,10 +81,7 @@ class _ReduceScatterRows(torch.autograd.Function):
     @staticmethod
     def forward(ctx, full: Tensor, group):
         ctx.group = group
-        w = _world(group)
-        out = torch.empty((full.shape[0] // w, *full.shape[1:]), dtype=full.dtype, device=full.device)
-        dist.reduce_scatter_tensor(out, full.contiguous(), op=dist.ReduceOp.SUM, group=group)
-        return out
+        return _reduce_scatter_raw(full, group)
 
     @staticmethod
     def backward(ctx, g: Tensor):

@@ -2,9 +2,9 @@
 
 Every trainable parameter is stored as this rank's block of rows (dim 0 padded to a
 multiple of the world size).  ``gather_params`` rebuilds the full tensors with the
-differentiable all-gather of ``collectives``; its backward is a reduce-scatter that
-averages over ranks, so parameter gradients come back sharded, and the backward of that
-is again an all-gather: the whole step stays differentiable to any order.  The reference
+differentiable all-gather of ``collectives``; its backward is a reduce-scatter, so
+parameter gradients come back sharded (summed over ranks), and the backward of that is
+again an all-gather: the whole step stays differentiable to any order.  The reference
 reaches the same behaviour with DTensor ``Shard(0)`` parametrisations and a patched
 redistribute backward (``bergson/magic/fsdp.py:20-87``, ``dtensor_patch.py``).
 """
@@ -42,27 +42,13 @@ def shard_param(full: Tensor) -> Tensor:
 
 
 def gather_param(shard: Tensor, full_shape: torch.Size) -> Tensor:
-    """Differentiable inverse of ``shard_param``; the gradient is averaged over ranks."""
+    """Differentiable inverse of ``shard_param``.  Its adjoint is a *summing* reduce-scatter;
+    the trainer averages over ranks by scaling each rank's loss with ``1 / world`` instead,
+    which keeps second-order terms correctly scaled as well."""
     _, world = _world()
     if world == 1 or len(full_shape) == 0:
         return shard
-    # Pre-dividing by the world size makes the reduce-scatter in backward an average.
-    full = all_gather_rows(shard / world) * world if False else all_gather_rows(shard)
-    full = full[: full_shape[0]]
-    return _ScaleGrad.apply(full, 1.0 / world)
-
-
-class _ScaleGrad(torch.autograd.Function):
-    """Identity whose gradient is scaled by a constant (differentiable to any order)."""
-
-    @staticmethod
-    def forward(ctx, x: Tensor, scale: float):
-        ctx.scale = scale
-        return x.view_as(x)
-
-    @staticmethod
-    def backward(ctx, g: Tensor):
-        return _ScaleGrad.apply(g, 1.0) * ctx.scale, None
+    return all_gather_rows(shard)[: full_shape[0]]
 
 
 def simple_fsdp(params: dict[str, Tensor]) -> tuple[dict[str, Tensor], dict[str, torch.Size]]:

@@ -72,9 +72,11 @@ def _loss_of(outputs) -> torch.Tensor:
 
 
 def accumulate_grads(call_model: Callable[[dict, dict], Any], params: dict, inputs: dict, grad_accum_steps: int, *,
-                     create_graph: bool, rng_snapshots: list | None = None) -> tuple[dict, float]:
+                     create_graph: bool, rng_snapshots: list | None = None, loss_scale: float = 1.0) -> tuple[dict, float]:
     """Full-batch gradient as the sum of rescaled micro-batch gradients.
-    ``call_model(params, micro_batch)`` runs the forward pass with ``params``."""
+    ``call_model(params, micro_batch)`` runs the forward pass with ``params``.  ``loss_scale``
+    multiplies the differentiated loss (``1 / world`` under parameter sharding, where the
+    gradient reduction over ranks is a sum); the returned loss value is unscaled."""
     total = loss_denom(inputs)
     grads: dict | None = None
     loss_value = 0.0
@@ -84,7 +86,7 @@ def accumulate_grads(call_model: Callable[[dict, dict], Any], params: dict, inpu
         loss = _loss_of(call_model(params, mb))
         coef = loss_denom(mb) / total
         loss_value += float(loss.detach()) * coef
-        g = grad_tree(loss * coef, params, create_graph=create_graph)
+        g = grad_tree(loss * (coef * loss_scale), params, create_graph=create_graph)
         if grads is None:
             grads = dict(g)
         else:
@@ -97,6 +99,7 @@ def accumulate_grads(call_model: Callable[[dict, dict], Any], params: dict, inpu
 
 def microbatch_step_vjp(call_model, apply_update, fwd_state, inputs: dict[str, Any], param_grads: dict,
                         opt_grads: list, data_weights: torch.Tensor, *, model_training: bool = False,
+                        loss_scale: float = 1.0,
                         fsdp: bool = False, max_grad_norm: float | None = None, grad_accum_steps: int = 1,
                         double_backward_batch_size: int | None = None):
     """Returns ``(param_cotangents, opt_cotangents, weight_cotangent)`` of one step."""
@@ -108,7 +111,8 @@ def microbatch_step_vjp(call_model, apply_update, fwd_state, inputs: dict[str, A
     rng_restore((fwd_state.cpu_rng_state, fwd_state.cuda_rng_state))
     snaps: list = []
     detached = {k: v.detach().requires_grad_(True) for k, v in fwd_state.params.items()}
-    g0, _ = accumulate_grads(call_model, detached, inputs, grad_accum_steps, create_graph=False, rng_snapshots=snaps)
+    g0, _ = accumulate_grads(call_model, detached, inputs, grad_accum_steps, create_graph=False, rng_snapshots=snaps,
+                             loss_scale=loss_scale)
     g_vars = {k: v.detach().clone().requires_grad_(True) for k, v in g0.items() if v is not None}
 
     # Stage A: VJP through reduce / clip / update only.
@@ -136,7 +140,7 @@ def microbatch_step_vjp(call_model, apply_update, fwd_state, inputs: dict[str, A
         rng_restore(snap)
         params = fwd_state.params
         loss = _loss_of(call_model(params, mb))
-        mg = grad_tree(loss * (loss_denom(mb) / total), params, create_graph=True)
+        mg = grad_tree(loss * (loss_denom(mb) / total * loss_scale), params, create_graph=True)
         gk = [k for k, v in mg.items() if v is not None and k in g_cot]
         targets = [params[k] for k in gk]
         mb_w = mb.get("example_weight")

@@ -250,6 +250,11 @@ class Trainer:
         full = gather_params(params, self.param_shapes) if self.param_shapes is not None else params
         return functional_call(self.model, {**full, **(buffers or {})}, args=(), kwargs=inputs)
 
+    @staticmethod
+    def _loss_scale(fsdp: bool) -> float:
+        """Sharded parameters sum gradients over ranks; the mean comes from the loss."""
+        return 1.0 / dist.get_world_size() if fsdp and dist.is_initialized() else 1.0
+
     def _ops_mode(self, trace: bool):
         # Kernels of the fused path implement first-order backward only.
         return ops.composable() if trace else nullcontext()
@@ -264,7 +269,8 @@ class Trainer:
         params = state.params if trace else {k: v.detach().requires_grad_(True) for k, v in state.params.items()}
         call = lambda p, mb: self.call_model(p, mb, state.buffers)  # noqa: E731
         with self._ops_mode(trace):
-            grads, self._last_loss = accumulate_grads(call, params, inputs, grad_accum_steps, create_graph=trace)
+            grads, self._last_loss = accumulate_grads(call, params, inputs, grad_accum_steps, create_graph=trace,
+                                                      loss_scale=self._loss_scale(fsdp))
         return self._apply_update(state, grads, inplace=inplace, trace=trace, fsdp=fsdp, max_grad_norm=max_grad_norm)
 
     def _apply_update(self, state: TrainerState, grads: dict, *, inplace: bool = False, trace: bool = False,
@@ -300,7 +306,8 @@ class Trainer:
         with ops.composable():
             pg, og, wc = microbatch_step_vjp(
                 call, self._apply_update, fwd_state, inputs, bwd_state.param_grads, bwd_state.opt_grads, data_weights,
-                model_training=self.model.training, fsdp=fsdp, max_grad_norm=max_grad_norm,
+                model_training=self.model.training, loss_scale=self._loss_scale(fsdp), fsdp=fsdp,
+                max_grad_norm=max_grad_norm,
                 grad_accum_steps=grad_accum_steps, double_backward_batch_size=double_backward_batch_size)
         return BackwardState(pg, og, wc + bwd_state.weight_grads)
 

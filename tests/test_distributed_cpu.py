@@ -41,9 +41,10 @@ def test_ekfac_two_ranks_equals_one(tmp_path):
     assert np.corrcoef(s1.ravel(), s2.ravel())[0, 1] > 0.999
 
 
-def test_magic_two_ranks_equals_one(tmp_path):
+@pytest.mark.parametrize("fsdp", ["false", "true"])
+def test_magic_two_ranks_equals_one(tmp_path, fsdp):
     for n in (1, 2):
-        run("magic", tmp_path / f"m{n}", "--model", MODEL, "--data.dataset", "synthetic:zipf?n=16&len=12&vocab=256",
+        run("magic", tmp_path / f"m{n}", "--fsdp", fsdp, "--model", MODEL, "--data.dataset", "synthetic:zipf?n=16&len=12&vocab=256",
             "--query.dataset", "synthetic:zipf?n=4&len=12&vocab=256&seed=1", "--batch_size", "4", "--query_method", "mean",
             "--lr", "1e-3", "--nproc_per_node", n)
     a, b = load_scores(tmp_path / "m1" / "scores")[:], load_scores(tmp_path / "m2" / "scores")[:]
