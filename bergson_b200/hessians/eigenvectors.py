@@ -62,18 +62,41 @@ class LambdaCollector(HookCollectorBase):
         self.eigen_g = load("eigen_gradient_sharded")
         self.eigenvalue_corrections: dict[str, Tensor] = {}
         self.transformed_a_cache: dict[str, Tensor] = {}
+        self._splits: dict[tuple[str, str], Tensor] = {}
+
+    def _rotate(self, kind: str, name: str, x: Tensor, q: Tensor) -> Tensor:
+        """``x @ q`` in the accumulation dtype; bf16 activations on CUDA go through the
+        tensor-core rotation with an fp32-accurate split of ``q`` (cached per module)."""
+        from ..ops import attribution
+
+        if self.dtype == torch.float32 and x.is_cuda and x.dtype == torch.bfloat16 and x.shape[-1] % 8 == 0:
+            key = (kind, name)
+            if key not in self._splits:
+                self._splits[key] = attribution.split_hi_lo(q)
+            return attribution.rotate(x, q, self._splits[key])
+        return x.to(self.dtype) @ q
 
     def forward_hook(self, module: nn.Module, a: Tensor) -> None:
         name = assert_type(str, module._name)
         if module._collect_bias:
             a = torch.cat([a, a.new_ones(*a.shape[:-1], 1)], dim=-1)
-        self.transformed_a_cache[name] = a.to(self.dtype) @ self.eigen_a[name]
+        self.transformed_a_cache[name] = self._rotate("a", name, a, self.eigen_a[name])
 
     def backward_hook(self, module: nn.Module, g: Tensor) -> None:
         name = assert_type(str, module._name)
-        tg = g.to(self.dtype) @ self.eigen_g[name]  # [N, S, O]
+        tg = self._rotate("g", name, g, self.eigen_g[name])  # [N, S, O]
         ta = self.transformed_a_cache.pop(name)  # [N, S, I]
-        per_doc = tg.mT @ ta  # [N, O, I]
+        if tg.is_cuda and tg.dtype == torch.float32:
+            # Per-document outer products on TF32 tensor cores (fp32 accumulate); the result is
+            # squared and summed over documents, so 10-bit operand mantissas are ample.
+            prev = torch.backends.cuda.matmul.allow_tf32
+            torch.backends.cuda.matmul.allow_tf32 = True
+            try:
+                per_doc = tg.mT @ ta  # [N, O, I]
+            finally:
+                torch.backends.cuda.matmul.allow_tf32 = prev
+        else:
+            per_doc = tg.mT @ ta
         upd = per_doc.square_().sum(dim=0)
         if name in self.eigenvalue_corrections:
             self.eigenvalue_corrections[name].add_(upd)

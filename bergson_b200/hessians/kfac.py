@@ -47,46 +47,64 @@ class _FactorCollector(HookCollectorBase):
 
     # -- helpers --------------------------------------------------------------------------
 
+    def with_batch(self, collection_mask: Tensor | None = None):
+        """Row indices of collected / skipped positions are computed once per batch (one
+        host synchronisation) and reused by every hook."""
+        super().with_batch(collection_mask)
+        if collection_mask is not None:
+            flat = collection_mask.reshape(-1)
+            self._keep_idx = flat.nonzero(as_tuple=True)[0]
+            self._drop_idx = (~flat).nonzero(as_tuple=True)[0]
+        return self
+
     def _masked(self, x: Tensor) -> Tensor:
-        mask = self._current_collection_mask
-        assert mask is not None, "Collection mask not set."
-        return x[mask]
+        assert self._current_collection_mask is not None, "Collection mask not set."
+        return x.reshape(-1, x.shape[-1]).index_select(0, self._keep_idx)
 
     def _acc(self, store: dict[str, Tensor], name: str, d: int, device) -> Tensor:
         if name not in store:
             store[name] = torch.zeros(d, d, device=device, dtype=torch.float32)
         return store[name]
 
-    def _gram_into(self, acc: Tensor, x: Tensor, full: Tensor | None = None, scale: float | Tensor | None = None):
-        """``acc += scale * x^T x`` for masked rows ``x``.  When the unmasked tensor
-        ``full`` is given and the fused kernel applies, the Gram of all rows is taken in
-        place and the few masked-out rows are subtracted."""
-        if scale is None and attribution.gram_fused_ok(x):
-            attribution.gram_accumulate(acc, x)
+    def _gram_into(self, acc: Tensor, x3d: Tensor, ones_column: bool = False) -> None:
+        """``acc += X^T X`` over the collected positions of ``x3d [N, S, D]``.
+
+        Fused path: the SYRK kernel reads *all* rows in place (no compaction copy) and the
+        Gram of the few skipped rows (each sequence's last position, padding) is subtracted."""
+        x2 = x3d.reshape(-1, x3d.shape[-1])
+        n_drop = self._drop_idx.numel()
+        if not ones_column and attribution.gram_fused_ok(x2) and n_drop * 8 <= x2.shape[0]:
+            attribution.gram_accumulate(acc, x2)
+            if n_drop:
+                xd = x2.index_select(0, self._drop_idx).float()
+                acc.addmm_(xd.mT, xd, alpha=-1.0)
             return
-        xf = x.to(self.dtype if self.dtype != torch.bfloat16 else torch.float32)
-        upd = (xf.mT @ xf).float()
-        acc.add_(upd if scale is None else upd * scale)
+        xk = self._masked(x3d)
+        if ones_column:
+            xk = torch.cat([xk, xk.new_ones(xk.shape[0], 1)], dim=1)
+        xf = xk.to(self.dtype if self.dtype != torch.bfloat16 else torch.float32)
+        acc.add_((xf.mT @ xf).float())
 
     # -- hooks ----------------------------------------------------------------------------
 
     def forward_hook(self, module: nn.Module, a: Tensor) -> None:
+        if self.method == "kfac":
+            name = assert_type(str, module._name)
+            d = a.shape[-1] + (1 if module._collect_bias else 0)
+            self._gram_into(self._acc(self.A_full, name, d, a.device), a, ones_column=bool(module._collect_bias))
+            return
         a_bi = self._masked(a)
         if module._collect_bias:
             a_bi = torch.cat([a_bi, a_bi.new_ones(a_bi.shape[0], 1)], dim=1)
-        if self.method == "kfac":
-            name = assert_type(str, module._name)
-            self._gram_into(self._acc(self.A_full, name, a_bi.shape[1], a.device), a_bi)
-        else:
-            module._inputs = a_bi
+        module._inputs = a_bi
 
     def backward_hook(self, module: nn.Module, g: Tensor) -> None:
         name = assert_type(str, module._name)
-        g_bo = self._masked(g)
-        S = self._acc(self.S_full, name, g_bo.shape[1], g.device)
+        S = self._acc(self.S_full, name, g.shape[-1], g.device)
         if self.method == "kfac":
-            self._gram_into(S, g_bo)
+            self._gram_into(S, g)
             return
+        g_bo = self._masked(g)
         a_bi = module._inputs
         A = self._acc(self.A_full, name, a_bi.shape[1], g.device)
         wd = self.dtype if self.dtype != torch.bfloat16 else torch.float32

@@ -111,3 +111,31 @@ def gram_finalize(store: dict[str, Tensor]) -> None:
         if m.data_ptr() in _UPPER_ONLY:
             _UPPER_ONLY.discard(m.data_ptr())
             store[name] = torch.triu(m) + torch.triu(m, 1).T
+
+
+# --------------------------------------------------------------------------- #
+# fp32-accurate rotation on 16-bit tensor cores
+# --------------------------------------------------------------------------- #
+
+
+def split_hi_lo(q: Tensor) -> Tensor:
+    """``[2 * b, a]`` bf16 operand holding the rows of ``q^T`` split as ``hi + lo`` (``q`` is
+    ``[a, b]`` fp32).  ``hi`` is the bf16 rounding, ``lo`` the bf16 rounding of the residual,
+    so ``hi + lo`` carries about 16 mantissa bits."""
+    qt = q.float().T.contiguous()
+    hi = qt.to(torch.bfloat16)
+    lo = (qt - hi.float()).to(torch.bfloat16)
+    return torch.cat([hi, lo], dim=0).contiguous()
+
+
+def rotate(x: Tensor, q: Tensor, q_split: Tensor | None = None) -> Tensor:
+    """``x [..., a] @ q [a, b]`` in fp32 accuracy.  For bf16 ``x`` on CUDA the product runs on
+    the tcgen05 TN GEMM against the hi/lo split of ``q`` (the activations are exact in bf16,
+    the two partial products are accumulated in fp32); otherwise a plain fp32 matmul."""
+    lead, a = x.shape[:-1], x.shape[-1]
+    b = q.shape[1]
+    if x.dtype == torch.bfloat16 and a % 8 == 0 and use_fused(x, q):
+        qs = q_split if q_split is not None else split_hi_lo(q)
+        out = native.tn_gemm(x.reshape(-1, a).contiguous(), qs)  # [T, 2b] fp32
+        return (out[:, :b] + out[:, b:]).view(*lead, b)
+    return x.to(q.dtype) @ q

@@ -255,3 +255,16 @@ def test_adamw_step_and_row_sumsq(native):
     out = torch.ones(33, device="cuda")
     native.row_sumsq(x, out)
     torch.testing.assert_close(out, 1 + x.float().pow(2).sum(1), rtol=1e-4, atol=1e-3)
+
+
+def test_rotation_hi_lo_is_fp32_accurate(native):
+    from bergson_b200.ops import attribution
+
+    torch.manual_seed(10)
+    x = torch.randn(3, 700, 768, device="cuda", dtype=torch.bfloat16)
+    q = torch.linalg.qr(torch.randn(768, 768, device="cuda", dtype=torch.float64))[0].float()
+    got = attribution.rotate(x, q)
+    ref = (x.double() @ q.double()).float()
+    _status_ok(native)
+    assert got.dtype == torch.float32 and got.shape == ref.shape
+    assert (got - ref).abs().max() / ref.abs().max() < 2e-4
