@@ -119,6 +119,10 @@ class HookCollectorBase(ContextDecorator, ABC):
         self.target_info = self.discover_targets(
             self.model, self.target_modules, self.processor.include_bias, self.filter_modules
         )
+        # Tensor-parallel shards: name -> ("out" | "in", lo, hi, full size of the split dim).
+        self._tp_shards = {
+            n: m._tp_shard for n, m in self.model.named_modules() if n in self.target_info and hasattr(m, "_tp_shard")
+        }
         if unknown := set(self.attention_cfgs) - set(self.target_info):
             raise ValueError(
                 f"attention_cfgs contains module names not found in the model: {unknown}. "
@@ -247,11 +251,30 @@ class HookCollectorBase(ContextDecorator, ABC):
         key = (name, role, device)
         cache = self.processor._projection_matrices
         if key not in cache:
-            cache[key] = create_projection_matrix(
-                f"{name}/{role}", m, n, dtype, device,
+            shard = self._tp_shards.get(name)
+            split = shard is not None and ((role == "left" and shard[0] == "out") or (role == "right" and shard[0] == "in"))
+            full_n = shard[3] if split else n
+            mat = create_projection_matrix(
+                f"{name}/{role}", m, full_n, dtype, device,
                 self.processor.projection_type, self.processor.projection_scale,
             )
+            # A rank that holds a slice of the split dimension projects with the matching
+            # columns of the full matrix; the partial results are summed over the group.
+            cache[key] = mat[:, shard[1] : shard[2]].contiguous() if split else mat
         return cache[key]
+
+    def adafactor_scales(self, name: str, norm: AdafactorNormalizer) -> tuple[Tensor, Tensor]:
+        """(row scale [O_local], column scale [I_local]); statistics are those of the whole
+        layer, sliced to this rank's shard under tensor parallelism."""
+        row, col = norm.row_scale(), norm.col_scale()
+        shard = self._tp_shards.get(name)
+        if shard is not None:
+            dim, lo, hi, full = shard
+            if dim == "out" and row.shape[0] == full:
+                row = row[lo:hi]
+            if dim == "in" and col.shape[0] == full:
+                col = col[lo:hi]
+        return row, col
 
     def accumulate_global_projection(self, name: str, P: Tensor) -> bool:
         """``projection_target == "global"``: add ``P @ R_name^T`` into the single
@@ -385,8 +408,9 @@ class HookCollectorBase(ContextDecorator, ABC):
             p_out = self.projection(name, p, o, "left", device, dtype).float()
             norm = self.processor.normalizers.get(name)
             if isinstance(norm, AdafactorNormalizer):
-                p_in = p_in * norm.col_scale().to(device).float()[None, :]
-                p_out = p_out * norm.row_scale().to(device).float()[None, :]
+                row, col = self.adafactor_scales(name, norm)
+                p_in = p_in * col.to(device).float()[None, :]
+                p_out = p_out * row.to(device).float()[None, :]
             self._fused_mats[key] = (p_in.to(dtype).contiguous(), p_out.to(dtype).contiguous())
         return self._fused_mats[key]
 
@@ -435,7 +459,7 @@ class HookCollectorBase(ContextDecorator, ABC):
             module._inputs = a
             return
         if isinstance(norm, AdafactorNormalizer):
-            a = a * norm.col_scale().type_as(a)
+            a = a * self.adafactor_scales(name, norm)[1].type_as(a)
         # With a bias column the un-projected activations are needed in backward.
         if p is not None and not module._collect_bias:
             a = a @ self.projection(name, p, i, "right", a.device, a.dtype).T
@@ -489,7 +513,7 @@ class HookCollectorBase(ContextDecorator, ABC):
             if with_bias:
                 bias_grad = bias_of(norm.normalize_bias(g) if norm is not None else g)
             if isinstance(norm, AdafactorNormalizer):
-                g = g * norm.row_scale().type_as(g)
+                g = g * self.adafactor_scales(name, norm)[0].type_as(g)
             if with_bias and p is not None:
                 P = self.double_sided_projection_with_bias(name, g, a, bias_grad, p, o, i)
             else:
@@ -599,7 +623,10 @@ class CollectorComputer:
         self.collector.teardown()
         total = self._total_processed
         if dist.is_initialized():
+            from ..parallel import topology
+
             dist.all_reduce(total, op=dist.ReduceOp.SUM)
+            total = total // topology.tp_size()  # tensor-parallel peers counted the same positions
         if self.rank == 0:
             torch.save(total.cpu(), os.path.join(self.cfg.partial_run_path, "total_processed.pt"))
         self.logger.info(f"Total processed: {total.item()}")

@@ -15,6 +15,7 @@ from torch import Tensor
 
 from ..builder import Builder
 from ..config import IndexConfig, PreprocessConfig
+from ..gradients import AdamNormalizer
 from ..data import column_offsets
 from ..score.scorer import Scorer
 from ..utils.utils import convert_precision_to_torch, get_gradient_dtype
@@ -48,6 +49,15 @@ class GradientCollector(HookCollectorBase):
         self.attribute_tokens = self.cfg.attribute_tokens
         if self.cfg.attribute_tokens:
             assert self.preprocess_cfg.aggregation == "none", "attribute_tokens is incompatible with reduce mode."
+        from ..parallel import topology
+
+        self._tp = topology.tp_size()
+        self._tp_writer = topology.tp_rank() == 0
+        if self._tp > 1:
+            assert self.processor.projection_dim and self.processor.projection_target == "per_module", (
+                "tensor parallelism needs per-module projection (the blocks are summed over the group)")
+            assert not any(isinstance(n, AdamNormalizer) for n in self.processor.normalizers.values()), (
+                "elementwise (Adam) normalisation does not commute with the sum over tensor-parallel shards")
         self.save_dtype = resolve_save_dtype(self.model, self.cfg)
         self.lo = torch.finfo(self.save_dtype).min
         self.hi = torch.finfo(self.save_dtype).max
@@ -79,8 +89,8 @@ class GradientCollector(HookCollectorBase):
         P = self._compute_gradient(module, g)
         if self.accumulate_global_projection(name, P):
             return
-        if self._fused_enabled:
-            self.mod_grads[name] = P  # merged into the row accumulator in process_batch
+        if self._fused_enabled or self._tp > 1:
+            self.mod_grads[name] = P  # merged / reduced in process_batch
         elif self.save_index and self.preprocess_cfg.aggregation == "none":
             self.mod_grads[name] = P.to(device="cpu", dtype=self.save_dtype, non_blocking=True)
         else:
@@ -89,16 +99,20 @@ class GradientCollector(HookCollectorBase):
     def process_batch(self, indices: list[int], **kwargs):
         losses = kwargs.get("losses")
         assert losses is not None, "losses must be provided in kwargs"
+        if self._tp > 1:
+            self._reduce_over_tensor_parallel_group()
         if self._fused_enabled:
             rows = self.fused_rows()
-            if self.builder is not None:
+            if self._tp > 1:
+                dist.all_reduce(rows, group=self._tp_group())
+            if self.builder is not None and self._tp_writer:
                 self.builder.write_rows_async(indices, rows, self.lo, self.hi)
             if self.scorer is not None:
                 self.scorer.writer(indices, self.scorer.score_rows(rows.clamp(self.lo, self.hi)),
                                    query_offset=self.scorer.query_offset)
         else:
             self.finalize_global_projection()
-            if self.builder:
+            if self.builder and self._tp_writer:
                 self.builder(indices, self.mod_grads)
             if self.scorer:
                 self.scorer(indices, self.mod_grads)
@@ -106,8 +120,25 @@ class GradientCollector(HookCollectorBase):
         idx = torch.as_tensor(indices, device=self.per_doc_losses.device)
         self.per_doc_losses[idx] = losses.detach().to(self.per_doc_losses.dtype)
 
+    def _tp_group(self):
+        from ..parallel import topology
+
+        return topology.tp_group()
+
+    def _reduce_over_tensor_parallel_group(self) -> None:
+        """Torch-path blocks are partial sums over the group's shards: add them up, then
+        clamp / cast as the single-rank path does."""
+        if self._fused_enabled:
+            return  # the fused accumulator is reduced as a whole
+        for name, P in self.mod_grads.items():
+            P = P.float().contiguous()
+            dist.all_reduce(P, group=self._tp_group())
+            self.mod_grads[name] = P.clamp_(self.lo, self.hi).to(self.save_dtype)
+
     def teardown(self):
         if dist.is_initialized():
+            if self._tp > 1:
+                self.per_doc_losses /= self._tp  # every rank of a group holds the same losses
             dist.reduce(self.per_doc_losses, dst=0)
         if self.builder:
             self.builder.teardown()

@@ -38,6 +38,13 @@ def _rank_world() -> tuple[int, int]:
     return 0, 1
 
 
+def _data_rank_world() -> tuple[int, int]:
+    """(rank, world) for splitting data: the ranks of one tensor-parallel group share data."""
+    from .parallel import topology
+
+    return topology.data_rank_world()
+
+
 # --------------------------------------------------------------------------- #
 # synthetic data
 # --------------------------------------------------------------------------- #
@@ -239,7 +246,7 @@ def allocate_batches(
     doc_lengths: Sequence[int], N: int, seed: int = 42, max_batch_size: int | None = None
 ) -> list[list[int]]:
     """This rank's batches (see ``_allocate_batches_world``)."""
-    rank, world = _rank_world()
+    rank, world = _data_rank_world()
     (mine,) = _allocate_batches_world(doc_lengths, N, world, seed, ranks=[rank], max_batch_size=max_batch_size)
     return mine
 

@@ -29,16 +29,22 @@ class LlamaAttention(nn.Module):
         self.k_proj = nn.Linear(d, self.kv_heads * hd, bias=cfg.attention_bias)
         self.v_proj = nn.Linear(d, self.kv_heads * hd, bias=cfg.attention_bias)
         self.o_proj = nn.Linear(self.num_heads * hd, d, bias=cfg.attention_bias)
+        self.tp_group = None  # set by parallel.tensor_parallel.apply_tensor_parallel
 
     def forward(self, x: Tensor, cos: Tensor, sin: Tensor) -> Tensor:
         B, S, _ = x.shape
+        if self.tp_group is not None:
+            from ..parallel.tensor_parallel import copy_to_group, reduce_from_group
+
+            x = copy_to_group(x, self.tp_group)
         q = self.q_proj(x).view(B, S, self.num_heads, self.head_dim)
         k = self.k_proj(x).view(B, S, self.kv_heads, self.head_dim)
         v = self.v_proj(x).view(B, S, self.kv_heads, self.head_dim)
         q = ops.rotary(q, cos, sin, self.head_dim)
         k = ops.rotary(k, cos, sin, self.head_dim)
         o = ops.causal_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2))
-        return self.o_proj(o.transpose(1, 2).reshape(B, S, -1))
+        out = self.o_proj(o.transpose(1, 2).reshape(B, S, -1))
+        return reduce_from_group(out, self.tp_group) if self.tp_group is not None else out
 
 
 class LlamaMLP(nn.Module):
@@ -48,9 +54,15 @@ class LlamaMLP(nn.Module):
         self.gate_proj = nn.Linear(d, f, bias=cfg.mlp_bias)
         self.up_proj = nn.Linear(d, f, bias=cfg.mlp_bias)
         self.down_proj = nn.Linear(f, d, bias=cfg.mlp_bias)
+        self.tp_group = None  # set by parallel.tensor_parallel.apply_tensor_parallel
 
     def forward(self, x: Tensor) -> Tensor:
-        return self.down_proj(ops.swiglu(self.gate_proj(x), self.up_proj(x)))
+        if self.tp_group is None:
+            return self.down_proj(ops.swiglu(self.gate_proj(x), self.up_proj(x)))
+        from ..parallel.tensor_parallel import copy_to_group, reduce_from_group
+
+        x = copy_to_group(x, self.tp_group)
+        return reduce_from_group(self.down_proj(ops.swiglu(self.gate_proj(x), self.up_proj(x))), self.tp_group)
 
 
 class LlamaDecoderLayer(nn.Module):

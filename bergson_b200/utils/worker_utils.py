@@ -96,6 +96,13 @@ def setup_model_and_peft(cfg: ModelConfig, device_map_auto: bool = False, apply_
     else:
         model, target_modules = _load_hf_model(cfg, dtype, device, device_map_auto, model_kwargs)
 
+    if getattr(cfg, "tensor_parallel", 1) > 1:
+        from ..parallel import topology
+        from ..parallel.tensor_parallel import apply_tensor_parallel
+
+        topology.init_topology(cfg.tensor_parallel)
+        apply_tensor_parallel(model)
+
     reduction = getattr(cfg, "loss_reduction", "mean")
     model.loss_function = partial(weighted_causal_lm_ce, reduction=reduction)
     model.requires_grad_(False)

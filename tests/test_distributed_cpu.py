@@ -27,6 +27,15 @@ def test_build_two_ranks_equals_one(tmp_path):
     assert int(torch.load(tmp_path / "w1" / "total_processed.pt")) == int(torch.load(tmp_path / "w2" / "total_processed.pt"))
 
 
+def test_tensor_parallel_build_equals_single(tmp_path):
+    opt = ["--model", MODEL, "--data.dataset", TRAIN, "--projection_dim", "4", "--token_batch_size", "64"]
+    run("build", tmp_path / "tp1", *opt, "--nproc_per_node", 1)
+    run("build", tmp_path / "tp2", *opt, "--nproc_per_node", 2, "--tensor_parallel", 2)
+    a, b = np.asarray(load_gradients(tmp_path / "tp1")), np.asarray(load_gradients(tmp_path / "tp2"))
+    np.testing.assert_allclose(a, b, rtol=1e-3, atol=1e-5 * np.abs(a).max())
+    assert int(torch.load(tmp_path / "tp1" / "total_processed.pt")) == int(torch.load(tmp_path / "tp2" / "total_processed.pt"))
+
+
 def test_ekfac_two_ranks_equals_one(tmp_path):
     for n in (1, 2):
         run("ekfac", tmp_path / f"e{n}", "--model", MODEL, "--index_cfg.data.dataset", TRAIN,

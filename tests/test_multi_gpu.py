@@ -82,3 +82,30 @@ def test_fused_collectives_two_gpus():
         assert status == 0
         assert err_rs < 2e-3, (rank, err_rs)
         assert err_ag < 2e-2, (rank, err_ag)
+
+
+def test_tensor_parallel_fused_build_matches_single_gpu(tmp_path):
+    """CLI build on 1 GPU vs tensor-parallel over 2 GPUs (fused projection kernels, bf16)."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    import numpy as np
+
+    from bergson_b200.data import load_gradients
+
+    root = Path(__file__).resolve().parents[1]
+    common = [sys.executable, "-m", "bergson_b200", "build"]
+    opts = ["--model", "native:llama-tiny?hidden_size=128&intermediate_size=256&vocab_size=1024", "--precision", "bf16",
+            "--data.dataset", "synthetic:zipf?n=16&len=160&vocab=1024&min_len=90", "--projection_dim", "16",
+            "--token_batch_size", "640", "--store_dtype", "fp32"]
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    for name, extra in (("one", ["--nproc_per_node", "1"]), ("tp2", ["--nproc_per_node", "2", "--tensor_parallel", "2"])):
+        out = subprocess.run(common + [str(tmp_path / name)] + opts + extra, cwd=root, env=env, capture_output=True,
+                             text=True, timeout=600)
+        assert out.returncode == 0, out.stderr[-2000:]
+    a, b = np.asarray(load_gradients(tmp_path / "one")), np.asarray(load_gradients(tmp_path / "tp2"))
+    assert np.abs(b).max() > 0
+    assert np.abs(a - b).max() / np.abs(a).max() < 3e-2
