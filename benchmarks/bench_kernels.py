@@ -1,6 +1,6 @@
 """Micro-benchmarks of the attribution kernels against their rooflines.
 
-    python -m bergson_b200.ops.bench_kernels [--kernel NAME] [--small] [--iters N]
+    python benchmarks/bench_kernels.py [--kernel NAME] [--small] [--iters N]
 
 Each kernel is timed with CUDA events after warm-up, on inputs larger than L2, and
 reported as achieved bandwidth / throughput and as a fraction of the measured peaks in
@@ -17,9 +17,14 @@ from pathlib import Path
 
 import torch
 
+try:
+    from common import ROOT  # noqa: F401  (puts the repository root on sys.path)
+except ImportError:  # imported as benchmarks.bench_kernels
+    from .common import ROOT  # noqa: F401
+
 
 def _peaks() -> dict:
-    p = Path(__file__).resolve().parents[2] / "MEASURED_PEAKS.json"
+    p = Path(__file__).resolve().parents[1] / "MEASURED_PEAKS.json"
     if p.exists():
         d = json.loads(p.read_text())
         return {"hbm_gbs": d["hbm_gbs"], "tflops": d["bf16_tflops"], "src": "measured"}
@@ -40,7 +45,7 @@ def _time(fn, iters: int, warmup: int = 3) -> float:
 
 
 def bench_proj_right(small: bool, iters: int):
-    from . import native
+    from bergson_b200.ops import native
 
     T, K = (16384, 4096) if small else (65536, 4096)
     a = torch.randn(T, K, device="cuda", dtype=torch.bfloat16)
@@ -51,7 +56,7 @@ def bench_proj_right(small: bool, iters: int):
 
 
 def bench_proj_left_outer(small: bool, iters: int):
-    from . import native
+    from bergson_b200.ops import native
 
     N, S, K = (8, 2048, 4096) if small else (32, 2048, 4096)
     g = torch.randn(N, S, K, device="cuda", dtype=torch.bfloat16)
@@ -66,7 +71,7 @@ def bench_proj_left_outer(small: bool, iters: int):
 
 
 def bench_cov_syrk(small: bool, iters: int):
-    from . import native
+    from bergson_b200.ops import native
 
     T, D = (16384, 3072) if small else (65536, 4096)
     x = torch.randn(T, D, device="cuda", dtype=torch.bfloat16)
@@ -83,7 +88,7 @@ def bench_cov_syrk(small: bool, iters: int):
 
 
 def bench_tn_gemm(small: bool, iters: int):
-    from . import native
+    from bergson_b200.ops import native
 
     M, N, K = (8192, 1024, 8192) if small else (32768, 1024, 57344)
     a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
@@ -95,7 +100,7 @@ def bench_tn_gemm(small: bool, iters: int):
 
 
 def bench_ce(small: bool, iters: int):
-    from . import native
+    from bergson_b200.ops import native
 
     T, V = (4096, 128256) if small else (16384, 128256)
     z = torch.randn(T, V, device="cuda", dtype=torch.bfloat16)
@@ -106,13 +111,13 @@ def bench_ce(small: bool, iters: int):
 
 
 def bench_rmsnorm(small: bool, iters: int):
-    from . import native
+    from bergson_b200.ops import native
 
     T, D = (32768, 4096) if small else (131072, 4096)
     x = torch.randn(T, D, device="cuda", dtype=torch.bfloat16)
     w = torch.ones(D, device="cuda", dtype=torch.bfloat16)
     ms = _time(lambda: native.rmsnorm_fwd(x, w, 1e-5), iters)
-    from .functional import rms_norm_ref
+    from bergson_b200.ops.functional import rms_norm_ref
 
     ref = _time(lambda: rms_norm_ref(x, w, 1e-5), iters)
     return dict(kernel="rmsnorm_fwd", shape=[T, D], ms=ms, torch_ms=ref, bytes=2 * T * D * 2, flops=0)

@@ -100,7 +100,12 @@ def f_one_minus_exp(lr_times_steps: float) -> Callable[[Tensor], Tensor]:
 def _apply_eigfn_worker(rank, local_rank, world_size, cfg: EkfacConfig, lr_times_steps: float, fn_kind: str,
                         inversion_cfg: InversionConfig | None) -> None:
     init_dist(rank, local_rank, world_size)
-    if cfg.preconditioner_path and inversion_cfg is not None:
+    # The EK-FAC inverse only takes part in the optimizer-preconditioned hybrid, where it
+    # supplies the 1/sigma of f_segment after the diagonal multiplier; without a
+    # preconditioner grid the eigenvalue function carries the 1/sigma itself.
+    if not cfg.preconditioner_path:
+        inversion_cfg = None
+    if inversion_cfg is not None:
         fn = f_one_minus_exp(lr_times_steps)
     else:
         fn = {"f_segment": f_segment, "f_backward": f_backward}[fn_kind](lr_times_steps)

@@ -544,6 +544,24 @@ class HookCollectorBase(ContextDecorator, ABC):
         return True
 
 
+def check_kernel_status(device) -> None:
+    """Raise if a kernel on ``device`` gave up on one of its bounded waits (its output is
+    then incomplete).  Called once at the end of a run, before results are finalised: it
+    synchronises the device."""
+    device = torch.device(device)
+    if device.type != "cuda":
+        return
+    from ..ops import attribution, native
+
+    if not native.available():
+        return
+    status = attribution.kernel_status(device.index if device.index is not None else torch.cuda.current_device())
+    if status != 0:
+        raise RuntimeError(
+            f"a bergson_b200 kernel on {device} gave up on a bounded wait (status {status}); the rows or factors "
+            "accumulated in this run are incomplete and were not finalised")
+
+
 class CollectorComputer:
     """Runs forward/backward over the batches with a collector attached.
 
@@ -620,6 +638,7 @@ class CollectorComputer:
                     prof.step()  # type: ignore[union-attr]
                 else:
                     self.step(indices)
+        check_kernel_status(self.device)
         self.collector.teardown()
         total = self._total_processed
         if dist.is_initialized():

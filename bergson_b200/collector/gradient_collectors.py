@@ -78,8 +78,12 @@ class GradientCollector(HookCollectorBase):
                 and getattr(self.scorer, "supports_rows", False))
         )
         if wants_fused and self.processor.projection_target == "per_module":
-            offs = {n: lo for n, (lo, _) in column_offsets(self.grad_sizes).items()}
-            self.enable_fused(offs, sum(self.grad_sizes.values()))
+            spans = column_offsets(self.grad_sizes)
+            total = sum(self.grad_sizes.values())
+            # The scorer's modules may be a subset of the collected ones, in another order:
+            # it assembles its query operand in this collector's column layout, or declines.
+            if self.scorer is None or self.scorer.set_row_layout(spans, total):
+                self.enable_fused({n: lo for n, (lo, _) in spans.items()}, total)
 
     @HookCollectorBase.split_attention_heads
     def backward_hook(self, module: nn.Module, g: Tensor):

@@ -11,8 +11,8 @@ masked output gradients ``[T, O]`` (reference ``bergson/hessians/{kfac,tkfac,sha
 The reference all-reduces every update and keeps its row slice.  Every update is a sum
 over (rank, batch) units, so this implementation accumulates the full fp32 matrices
 locally and performs one reduce-scatter to row shards in ``teardown`` — through the
-fused SYRK kernel's peer-memory epilogue when a symmetric heap is available, else with
-``torch.distributed.reduce_scatter``-equivalent collectives.  On CUDA with 16-bit
+fused SYRK kernel's peer-memory epilogue on CUDA ranks (``BERGSON_B200_DISABLE_PEER=1`` on every
+rank selects library all-reduces instead; CPU ranks always use them).  On CUDA with 16-bit
 activations the K-FAC products run in the tcgen05 SYRK kernel, which reads the
 activations once in their own dtype with fp32 accumulation.
 """
@@ -131,11 +131,11 @@ class _FactorCollector(HookCollectorBase):
         memory; otherwise (CPU, single rank, no symmetric memory) by NCCL / Gloo."""
         sc = self.shard_computer
         names = [n for n in self.target_info if n in store]
-        if sc.dist and names and store[names[0]].is_cuda:
-            try:
-                return self._row_shards_peer(store, names)
-            except Exception as e:  # noqa: BLE001 - fall back to the library collective
-                self.logger.warning(f"peer-memory reduce-scatter unavailable ({e}); using all_reduce")
+        # The choice is made from facts that are equal on every rank (backend, device type, one
+        # environment switch), never from a per-rank try/except: ranks that disagreed would
+        # wait for each other in different collectives.  A failure on the peer path is fatal.
+        if sc.dist and names and store[names[0]].is_cuda and os.environ.get("BERGSON_B200_DISABLE_PEER") != "1":
+            return self._row_shards_peer(store, names)
         out = {}
         for name in names:
             full = store[name]
@@ -151,7 +151,10 @@ class _FactorCollector(HookCollectorBase):
         from .sharded_computation import shard_bounds
 
         if not symmetric_memory_available():
-            raise RuntimeError("symmetric memory not available")
+            raise RuntimeError(
+                "the K-FAC reduce-scatter runs over a symmetric peer-memory heap, which this process group does not "
+                "offer (needs the NCCL backend on CUDA); set BERGSON_B200_DISABLE_PEER=1 on every rank to use "
+                "library all-reduces instead")
         world, rank = self.shard_computer.world_size, self.shard_computer.rank
         # Same offsets on every rank: regions are sized for the largest (rank 0) shard.
         offsets, total = {}, 0
@@ -180,6 +183,9 @@ class _FactorCollector(HookCollectorBase):
         return out
 
     def teardown(self) -> None:
+        from ..collector.collector import check_kernel_status
+
+        check_kernel_status(next(self.model.parameters()).device)
         attribution.gram_finalize(self.A_full)
         attribution.gram_finalize(self.S_full)
         A = self._row_shards(self.A_full)

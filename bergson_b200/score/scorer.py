@@ -49,15 +49,39 @@ class Scorer:
     def __call__(self, indices: list[int], mod_grads: dict[str, Tensor]):
         self.writer(indices, self.score(mod_grads), query_offset=self.query_offset)
 
+    def set_row_layout(self, offsets: dict[str, tuple[int, int]], total: int) -> bool:
+        """Tell the scorer how a producer lays out concatenated rows: ``offsets`` maps module
+        names to their ``[lo, hi)`` columns of a ``total``-wide row.  The query operand of
+        ``score_rows`` is then assembled in that layout, with zero columns for modules that
+        this scorer does not score, so the producer's module set may be a superset of
+        ``self.modules`` in any order.  Returns False when concatenated-row scoring cannot
+        be used: a scored module is missing from the rows or has another width, or cosine
+        scoring would see the norm of columns outside ``self.modules``."""
+        if not self.supports_rows:
+            return False
+        for m in self.modules:
+            if m not in offsets or offsets[m][1] - offsets[m][0] != self.query_grads_t[m].shape[0]:
+                return False
+        if self.unit_normalize and set(offsets) != set(self.modules):
+            return False
+        n_q = next(iter(self.query_grads_t.values())).shape[1] if self.modules else 0
+        q = torch.zeros(n_q, total, device=self.device, dtype=self.dtype)
+        for m in self.modules:
+            lo, hi = offsets[m]
+            q[:, lo:hi] = self.query_grads_t[m].T
+        self._q_cat = q
+        return True
+
     def _q_rows(self) -> Tensor:
-        """Queries as ``[n_queries, sum_m dim_m]`` (K-major operand of the fused GEMM)."""
+        """Queries as ``[n_queries, row width]`` (K-major operand of the fused GEMM); module
+        order ``self.modules`` unless ``set_row_layout`` gave another layout."""
         if self._q_cat is None:
             self._q_cat = torch.cat([self.query_grads_t[m].T for m in self.modules], dim=1).contiguous()
         return self._q_cat
 
     @torch.inference_mode()
     def score_rows(self, rows: Tensor) -> Tensor:
-        """Score concatenated rows ``[B, sum_m dim_m]`` (module order = ``self.modules``)."""
+        """Score concatenated rows ``[B, row width]`` laid out as ``_q_rows`` describes."""
         from ..ops import attribution
 
         scores, sq = attribution.score_rows(rows.to(self.device), self._q_rows(), self.dtype, self.unit_normalize)

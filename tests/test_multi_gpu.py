@@ -98,7 +98,7 @@ def test_tensor_parallel_fused_build_matches_single_gpu(tmp_path):
 
     root = Path(__file__).resolve().parents[1]
     common = [sys.executable, "-m", "bergson_b200", "build"]
-    opts = ["--model", "native:llama-tiny?hidden_size=128&intermediate_size=256&vocab_size=1024", "--precision", "bf16",
+    opts = ["--model", "native:llama-tiny?hidden_size=128&intermediate_size=256&vocab_size=1024&max_position_embeddings=1024", "--precision", "bf16",
             "--data.dataset", "synthetic:zipf?n=16&len=160&vocab=1024&min_len=90", "--projection_dim", "16",
             "--token_batch_size", "640", "--store_dtype", "fp32"]
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
