@@ -22,7 +22,6 @@ import argparse
 import json
 import os
 import shutil
-import statistics
 import subprocess
 import sys
 import tempfile
@@ -55,53 +54,6 @@ def parse_args():
 
 def dist_env():
     return int(os.environ.get("RANK", 0)), int(os.environ.get("LOCAL_RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
-
-
-class ClockSampler:
-    """Samples SM clocks and throttle reasons of one GPU with nvidia-smi while running."""
-
-    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
-              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
-
-    def __init__(self, gpu_index: int):
-        self.path = Path(tempfile.mkstemp(prefix="clocks_", suffix=".csv")[1])
-        self.gpu = gpu_index
-        self.proc = None
-
-    def start(self):
-        try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "200",
-                 "-i", str(self.gpu)], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
-        except OSError:
-            self.proc = None
-
-    def stop(self) -> dict:
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-        sm, mx, reasons = [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in self.path.read_text().splitlines():
-            parts = [p.strip() for p in line.split(",")]
-            if len(parts) < 9:
-                continue
-            try:
-                sm.append(float(parts[1]))
-                mx.append(float(parts[2]))
-            except ValueError:
-                continue
-            for name, flag in zip(names, parts[5:9]):
-                if flag.lower().startswith("active"):
-                    reasons.add(name)
-        self.path.unlink(missing_ok=True)
-        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
 
 
 def make_dataset(world: int, per_rank_batches: int, seqs: int, seq_len: int, vocab: int):
@@ -176,6 +128,8 @@ def run_ours(args, rank, local_rank, world):
     assert collector._fused_enabled, "fused projection path is not active"
     computer = CollectorComputer(model=model, data=ds, collector=collector, batches=batches, cfg=cfg)
     row_bytes = sum(collector.grad_sizes.values()) * 2
+
+    from benchmarks.clocks import ClockSampler
 
     sampler = ClockSampler(local_rank)
     with collector:
@@ -291,6 +245,8 @@ def run_reference(args, rank, local_rank, world):
     barrier_sync(device)
     cfg = bergson.IndexConfig(run_path=str(run_dir), projection_dim=16, token_batch_size=B * S)
     cfg.partial_run_path.mkdir(parents=True, exist_ok=True)
+    from benchmarks.clocks import ClockSampler
+
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()

@@ -9,6 +9,7 @@
 
 #include "kernels.h"
 #include "kernels_cov.h"
+#include "kernels_gemm.h"
 
 namespace {
 
@@ -301,6 +302,82 @@ void cov_syrk(at::Tensor x, std::vector<int64_t> dst_ptrs, std::vector<int64_t> 
                      status_ptr(x), stream()), "cov_syrk");
 }
 
+
+// Persistent tcgen05 GEMM.  a: [M, K] (or [K, M] when a_mn), b: [N, K] (or [K, N] when b_mn); a
+// leading batch dimension on both selects the batched form.  Last dimensions contiguous.
+std::vector<at::Tensor> gemm(at::Tensor a, at::Tensor b, bool a_mn, bool b_mn, c10::optional<at::Tensor> out,
+                             bool out_f32, c10::optional<at::Tensor> bias, bool accumulate,
+                             c10::optional<at::Tensor> aux_p, int64_t cta_group, bool sq_accumulate,
+                             int64_t wait_cycles, c10::optional<at::Tensor> status) {
+  TORCH_CHECK(a.is_cuda() && b.is_cuda() && a.scalar_type() == b.scalar_type(), "gemm: CUDA operands of one dtype");
+  TORCH_CHECK((a.dim() == 2 || a.dim() == 3) && a.dim() == b.dim() && a.stride(-1) == 1 && b.stride(-1) == 1,
+              "gemm: 2-D or 3-D operands with contiguous last dimension");
+  c10::cuda::CUDAGuard guard(a.device());
+  const int fmt = fmt16(a);
+  const bool batched = a.dim() == 3;
+  const int64_t nb = batched ? a.size(0) : 1;
+  if (batched) { TORCH_CHECK(b.size(0) == nb, "gemm: batch sizes differ"); }
+  const int64_t M = a_mn ? a.size(-1) : a.size(-2), K = a_mn ? a.size(-2) : a.size(-1);
+  const int64_t N = b_mn ? b.size(-1) : b.size(-2), Kb = b_mn ? b.size(-2) : b.size(-1);
+  TORCH_CHECK(K == Kb, "gemm: reduction lengths differ (", K, " vs ", Kb, ")");
+  const auto out_type = out_f32 ? at::kFloat : a.scalar_type();
+  at::Tensor d;
+  if (out.has_value()) {
+    d = *out;
+    TORCH_CHECK(d.is_cuda() && d.scalar_type() == out_type && d.stride(-1) == 1, "gemm: bad output tensor");
+    if (sq_accumulate) {
+      TORCH_CHECK(d.dim() == 2 && d.size(0) == M && d.size(1) == N, "gemm: sq_accumulate output must be [M, N]");
+    } else {
+      TORCH_CHECK(d.dim() == a.dim() && d.size(-2) == M && d.size(-1) == N && (!batched || d.size(0) == nb),
+                  "gemm: output shape mismatch");
+    }
+  } else {
+    TORCH_CHECK(!accumulate && !sq_accumulate, "gemm: accumulation needs an output tensor");
+    d = batched ? at::empty({nb, M, N}, a.options().dtype(out_type)) : at::empty({M, N}, a.options().dtype(out_type));
+  }
+  BgnGemmArgs g = {};
+  g.a = a.data_ptr(); g.b = b.data_ptr(); g.d = d.data_ptr();
+  g.M = (int)M; g.N = (int)N; g.K = (int)K;
+  g.lda = a.stride(-2); g.ldb = b.stride(-2); g.ldd = d.stride(-2);
+  g.a_mn = a_mn; g.b_mn = b_mn; g.fmt = fmt; g.out_f32 = out_f32;
+  at::Tensor bias_c;
+  if (bias.has_value()) {
+    bias_c = bias->contiguous();
+    TORCH_CHECK(bias_c.numel() == N && (bias_c.scalar_type() == a.scalar_type() || bias_c.scalar_type() == at::kFloat));
+    g.bias = bias_c.data_ptr();
+    g.bias_f32 = bias_c.scalar_type() == at::kFloat;
+  }
+  g.accumulate = accumulate;
+  at::Tensor aux_out, aux_c;
+  if (aux_p.has_value()) {
+    aux_c = aux_p->contiguous();
+    TORCH_CHECK(aux_c.dim() == 2 && aux_c.size(1) == K && aux_c.scalar_type() == a.scalar_type() &&
+                aux_c.size(0) % 16 == 0 && aux_c.size(0) <= 64, "gemm: aux operand must be [16..64, K] of the input dtype");
+    aux_out = at::empty({nb * M, aux_c.size(0)}, a.options().dtype(at::kFloat));
+    g.aux_p = aux_c.data_ptr(); g.aux_n = (int)aux_c.size(0); g.aux_out = aux_out.data_ptr<float>();
+  }
+  g.batch = (int)nb;
+  g.a_batch_stride = batched ? a.stride(0) : 0;
+  g.b_batch_stride = batched ? b.stride(0) : 0;
+  g.d_batch_stride = (batched && !sq_accumulate) ? d.stride(0) : 0;
+  g.sq_accumulate = sq_accumulate;
+  g.cta_group = (int)cta_group;
+  g.sm_count = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
+  g.wait_cycles = wait_cycles;
+  int* st = status.has_value() ? status->data_ptr<int>() : status_ptr(a);
+  check(bgn_gemm(&g, st, stream()), "gemm");
+  return {d, aux_out};
+}
+
+at::Tensor wait_probe(int64_t budget_cycles, at::Tensor status) {
+  TORCH_CHECK(status.is_cuda() && status.scalar_type() == at::kInt && status.numel() == 1);
+  c10::cuda::CUDAGuard guard(status.device());
+  auto waited = at::zeros({1}, status.options().dtype(at::kLong));
+  check(bgn_wait_probe(budget_cycles, status.data_ptr<int>(), reinterpret_cast<long long*>(waited.data_ptr<int64_t>()),
+                       stream()), "wait_probe");
+  return waited;
+}
+
 at::Tensor kernel_status(int64_t device) { return status_tensor((int)device); }
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
@@ -324,5 +401,10 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("row_sumsq", &row_sumsq);
   m.def("cov_syrk", &cov_syrk, py::arg("x"), py::arg("dst_ptrs"), py::arg("row_start"), py::arg("local"),
         py::arg("full") = false, py::arg("num_rows") = -1);
+  m.def("gemm", &gemm, py::arg("a"), py::arg("b"), py::arg("a_mn") = false, py::arg("b_mn") = false,
+        py::arg("out") = py::none(), py::arg("out_f32") = false, py::arg("bias") = py::none(),
+        py::arg("accumulate") = false, py::arg("aux_p") = py::none(), py::arg("cta_group") = 2,
+        py::arg("sq_accumulate") = false, py::arg("wait_cycles") = 0, py::arg("status") = py::none());
+  m.def("wait_probe", &wait_probe);
   m.def("kernel_status", &kernel_status);
 }

@@ -1,0 +1,124 @@
+// Host side of the persistent tcgen05 GEMM (gemm.cuh): tensor maps for the four operand
+// layouts, grid sizing, and the cluster launch of the CTA-pair variant.
+#include "gemm.cuh"
+
+#include <mutex>
+
+#include "kernels_gemm.h"
+
+namespace bgn {
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn gemm_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  });
+  return fn;
+}
+
+// Row-major 16-bit tensor [batch, rows, inner] with row stride `ld` and batch stride `bs`
+// (elements); box = 64 x box_rows x 1 with the 128-byte swizzle.
+static bool gemm_tmap(CUtensorMap* map, const void* base, int fmt, uint64_t inner, uint64_t rows, uint64_t batch,
+                      uint64_t ld, uint64_t bs, uint32_t box_rows) {
+  EncodeTiledFn enc = gemm_encode_fn();
+  if (!enc || (reinterpret_cast<uintptr_t>(base) & 15) || (ld % 8) || (batch > 1 && bs % 8)) return false;
+  const CUtensorMapDataType dt = fmt == 1 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  cuuint64_t dims[3] = {inner, rows, batch > 1 ? batch : 1};
+  cuuint64_t strides[2] = {ld * 2, (batch > 1 ? bs : ld * rows) * 2};
+  cuuint32_t box[3] = {64, box_rows, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  return enc(map, dt, batch > 1 ? 3 : 2, const_cast<void*>(base), dims, strides, box, estr,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int CG, int FMT, bool OUT32>
+static cudaError_t launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tp, const GemmParams& p,
+                               int grid, int* status, cudaStream_t stream) {
+  auto kern = gemm_kernel<CG, FMT, OUT32>;
+  static bool attr_set = false;  // one flag per instantiation
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmSmemV2<CG>::kBytes);
+    if (e != cudaSuccess) return e;
+    attr_set = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid, 1, 1);
+  cfg.blockDim = dim3(kGemmThreadsV2, 1, 1);
+  cfg.dynamicSmemBytes = GemmSmemV2<CG>::kBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = CG;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, ta, tb, tp, p, status);
+}
+
+}  // namespace bgn
+
+using namespace bgn;
+
+extern "C" int bgn_gemm(const BgnGemmArgs* a, int* status, cudaStream_t stream) {
+  if (!a || a->M <= 0 || a->N <= 0 || a->K <= 0 || a->batch < 1) return int(cudaErrorInvalidValue);
+  const int cg = a->cta_group == 2 ? 2 : 1;
+  if (a->aux_n < 0 || a->aux_n > 64 || a->aux_n % 16) return int(cudaErrorInvalidValue);
+  if (a->sq_accumulate && !a->out_f32) return int(cudaErrorInvalidValue);
+  CUtensorMap ta, tb, tp;
+  const uint64_t B = uint64_t(a->batch);
+  // A: K-major [M, K] (box 64 k x 128 rows) or MN-major [K, M] (boxes of 64 m x 64 k).
+  const bool ok_a = a->a_mn ? gemm_tmap(&ta, a->a, a->fmt, a->M, a->K, B, a->lda, a->a_batch_stride, 64)
+                            : gemm_tmap(&ta, a->a, a->fmt, a->K, a->M, B, a->lda, a->a_batch_stride, 128);
+  const bool ok_b = a->b_mn ? gemm_tmap(&tb, a->b, a->fmt, a->N, a->K, B, a->ldb, a->b_batch_stride, 64)
+                            : gemm_tmap(&tb, a->b, a->fmt, a->K, a->N, B, a->ldb, a->b_batch_stride, kGemmTileN / cg);
+  if (!ok_a || !ok_b) return int(cudaErrorInvalidValue);
+  if (a->aux_n > 0) {
+    if (!a->aux_p || !a->aux_out || !gemm_tmap(&tp, a->aux_p, a->fmt, a->K, a->aux_n, 1, a->K, 0, a->aux_n / cg))
+      return int(cudaErrorInvalidValue);
+  } else {
+    tp = tb;
+  }
+  GemmParams p;
+  p.M = a->M; p.N = a->N; p.K = a->K;
+  p.a_mn = a->a_mn ? 1 : 0; p.b_mn = a->b_mn ? 1 : 0;
+  p.d = a->d; p.ldd = a->ldd;
+  p.bias = a->bias; p.bias_f32 = a->bias_f32;
+  p.accumulate = a->accumulate;
+  p.aux_n = a->aux_n; p.aux_out = a->aux_out; p.aux_ld = a->aux_n;
+  p.batch = a->batch; p.d_batch_stride = a->d_batch_stride; p.sq_accumulate = a->sq_accumulate;
+  p.wait_cycles = a->wait_cycles > 0 ? a->wait_cycles : kMaxWaitCycles;
+
+  const int tile_m = 128 * cg;
+  const long tiles_m = (a->M + tile_m - 1) / tile_m;
+  const long tiles_n = (a->N + kGemmTileN - 1) / kGemmTileN + (a->aux_n > 0 ? 1 : 0);
+  const long tiles = tiles_m * tiles_n * a->batch;
+  long groups = a->sm_count / cg;
+  if (groups < 1) groups = 1;
+  if (groups > tiles) groups = tiles;
+  const int grid = int(groups) * cg;
+  cudaError_t e;
+  const bool bf = a->fmt == 1;
+  if (cg == 2) {
+    e = a->out_f32 ? (bf ? launch_gemm<2, 1, true>(ta, tb, tp, p, grid, status, stream)
+                         : launch_gemm<2, 0, true>(ta, tb, tp, p, grid, status, stream))
+                   : (bf ? launch_gemm<2, 1, false>(ta, tb, tp, p, grid, status, stream)
+                         : launch_gemm<2, 0, false>(ta, tb, tp, p, grid, status, stream));
+  } else {
+    e = a->out_f32 ? (bf ? launch_gemm<1, 1, true>(ta, tb, tp, p, grid, status, stream)
+                         : launch_gemm<1, 0, true>(ta, tb, tp, p, grid, status, stream))
+                   : (bf ? launch_gemm<1, 1, false>(ta, tb, tp, p, grid, status, stream)
+                         : launch_gemm<1, 0, false>(ta, tb, tp, p, grid, status, stream));
+  }
+  return int(e);
+}
