@@ -17,10 +17,10 @@ from pathlib import Path
 
 import torch
 
-try:
-    from common import ROOT  # noqa: F401  (puts the repository root on sys.path)
-except ImportError:  # imported as benchmarks.bench_kernels
-    from .common import ROOT  # noqa: F401
+import sys
+
+sys.path.insert(0, str(Path(__file__).resolve().parent))
+from common import ROOT  # noqa: E402,F401  (puts the repository root on sys.path)
 
 
 def _peaks() -> dict:
@@ -123,8 +123,59 @@ def bench_rmsnorm(small: bool, iters: int):
     return dict(kernel="rmsnorm_fwd", shape=[T, D], ms=ms, torch_ms=ref, bytes=2 * T * D * 2, flops=0)
 
 
+def _time_interleaved(fns: dict, rounds: int = 6, inner: int = 5) -> dict:
+    """Median milliseconds per call of each function, the functions taking turns in short
+    bursts so that clock and temperature drift hits all of them alike."""
+    import statistics
+
+    for fn in fns.values():
+        for _ in range(3):
+            fn()
+    torch.cuda.synchronize()
+    samples = {k: [] for k in fns}
+    for _ in range(rounds):
+        for k, fn in fns.items():
+            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0.record()
+            for _ in range(inner):
+                fn()
+            t1.record()
+            torch.cuda.synchronize()
+            samples[k].append(t0.elapsed_time(t1) / inner)
+    return {k: statistics.median(v) for k, v in samples.items()}
+
+
+def bench_linear_gemm(small: bool, iters: int):
+    """The Linear-layer products of the 32-layer d4096 model (16384 tokens per step) on the
+    persistent tcgen05 GEMM (CTA-pair form, with and without the projection side output, and
+    the single-CTA form) against torch (cuBLAS), interleaved in time."""
+    from bergson_b200.ops import native
+
+    T = 4096 if small else 16384
+    shapes = [("fwd q/o", T, 4096, 4096, False), ("fwd k/v", T, 1024, 4096, False), ("fwd gate/up", T, 14336, 4096, False),
+              ("fwd down", T, 4096, 14336, False), ("dgrad q/o", T, 4096, 4096, True), ("dgrad k/v", T, 4096, 1024, True),
+              ("dgrad gate/up", T, 4096, 14336, True), ("dgrad down", T, 14336, 4096, True)]
+    out = []
+    for name, M, N, K, b_mn in shapes:
+        a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+        b = torch.randn((K, N) if b_mn else (N, K), device="cuda", dtype=torch.bfloat16)
+        d = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+        p = (torch.randn(16, K, device="cuda") / 4).to(torch.bfloat16)
+        ms = _time_interleaved({
+            "pair": lambda: native.gemm(a, b, False, b_mn, d, False, None, False, None, 2),
+            "pair_proj": lambda: native.gemm(a, b, False, b_mn, d, False, None, False, p, 2),
+            "pair_regstore": lambda: native.gemm(a, b, False, b_mn, d, False, None, False, None, 2, False, 0, None, 0, None, True),
+            "single": lambda: native.gemm(a, b, False, b_mn, d, False, None, False, None, 1),
+            "torch": (lambda: torch.matmul(a, b, out=d)) if b_mn else (lambda: torch.matmul(a, b.T, out=d)),
+        })
+        out.append(dict(kernel=f"gemm {name}", shape=[M, N, K], ms=ms["pair"], ms_with_projection=ms["pair_proj"],
+                        ms_register_store=ms["pair_regstore"], ms_single_cta=ms["single"], torch_ms=ms["torch"],
+                        bytes=(M * K + N * K + M * N) * 2, flops=2 * M * N * K))
+    return out
+
+
 BENCHES = {"proj_right": bench_proj_right, "proj_left_outer": bench_proj_left_outer, "cov_syrk": bench_cov_syrk,
-           "tn_gemm": bench_tn_gemm, "ce_fwd": bench_ce, "rmsnorm_fwd": bench_rmsnorm}
+           "tn_gemm": bench_tn_gemm, "ce_fwd": bench_ce, "rmsnorm_fwd": bench_rmsnorm, "linear_gemm": bench_linear_gemm}
 
 
 def main():
@@ -133,17 +184,23 @@ def main():
     ap.add_argument("--small", action="store_true")
     ap.add_argument("--iters", type=int, default=20)
     args = ap.parse_args()
+    from clocks import ClockSampler
+
     peaks = _peaks()
     for name, fn in BENCHES.items():
         if args.kernel and name != args.kernel:
             continue
-        r = fn(args.small, args.iters)
-        gbs = r["bytes"] / r["ms"] / 1e6
-        tf = r["flops"] / r["ms"] / 1e9
-        r.update(gbs=round(gbs, 1), tflops=round(tf, 1), frac_hbm=round(gbs / peaks["hbm_gbs"], 3),
-                 frac_tc=round(tf / peaks["tflops"], 3), speedup_vs_torch=round(r["torch_ms"] / r["ms"], 2),
-                 peaks=peaks["src"])
-        print(json.dumps(r))
+        with ClockSampler(torch.cuda.current_device(), period_ms=100) as sampler:
+            res = fn(args.small, args.iters)
+        clocks = sampler.result
+        for r in res if isinstance(res, list) else [res]:
+            gbs = r["bytes"] / r["ms"] / 1e6
+            tf = r["flops"] / r["ms"] / 1e9
+            r.update(gbs=round(gbs, 1), tflops=round(tf, 1), frac_hbm=round(gbs / peaks["hbm_gbs"], 3),
+                     frac_tc=round(tf / peaks["tflops"], 3), speedup_vs_torch=round(r["torch_ms"] / r["ms"], 2),
+                     peaks=peaks["src"], clocks=clocks,
+                     ms_x_mhz=round(r["ms"] * clocks["sm_mhz"], 1) if clocks.get("sm_mhz") else None)
+            print(json.dumps(r), flush=True)
         torch.cuda.empty_cache()
 
 

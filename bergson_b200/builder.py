@@ -65,8 +65,8 @@ class _StagedWriter:
             self.slots[slot] = buf
         return slot, buf
 
-    def submit(self, slot: int, n: int, indices: list[int], event: torch.cuda.Event) -> None:
-        self.work.put((slot, n, list(indices), event))
+    def submit(self, slot: int, n: int, indices, event: torch.cuda.Event) -> None:
+        self.work.put((slot, n, np.asarray(indices, dtype=np.int64), event))
 
     def _drain(self) -> None:
         while True:
@@ -169,14 +169,9 @@ class Builder:
 
     @property
     def supports_async_rows(self) -> bool:
-        """Fused row emission handles plain per-sequence stores without a
-        preconditioner; everything else takes ``__call__``."""
-        return (
-            self.in_memory_grad_buffer is None
-            and self.offsets is None
-            and self.preconditioner is None
-            and torch.cuda.is_available()
-        )
+        """Fused row emission handles per-sequence and per-token stores without a
+        preconditioner or aggregation; everything else takes ``__call__``."""
+        return self.in_memory_grad_buffer is None and self.preconditioner is None and torch.cuda.is_available()
 
     def write_rows_async(self, indices: list[int], acc: torch.Tensor, lo: float, hi: float) -> None:
         """``acc``: fp32 ``[n, total_dim]`` rows on the device.  Enqueues: finalise into a
@@ -187,11 +182,19 @@ class Builder:
         if self._writer is None:
             self._writer = _StagedWriter(self.grad_buffer, acc.shape[1], self.dtype)
         n = acc.shape[0]
+        rows: list[int] | np.ndarray = indices
+        if self.offsets is not None:
+            # Per-token store: the accumulator holds the documents' collected tokens in order.
+            rows = np.concatenate([np.arange(self.offsets[i], self.offsets[i + 1]) for i in indices]) if indices else \
+                np.zeros(0, dtype=np.int64)
+            assert len(rows) == n, f"token rows ({n}) do not match the store's offsets ({len(rows)})"
+            if n == 0:
+                return
         slot, buf = self._writer.acquire(n)
         native.finalize_rows(acc, buf[:n], None, lo, hi, self.preprocess_cfg.unit_normalize)
         ev = torch.cuda.Event()
         ev.record()
-        self._writer.submit(slot, n, indices, ev)
+        self._writer.submit(slot, n, rows, ev)
 
     # -- lifecycle ----------------------------------------------------------------------
 

@@ -81,6 +81,48 @@ def create_projection_matrix(
     return A
 
 
+TAP_PROJECTION_DIMS = (8, 16, 32, 64)
+
+
+def _tap_module_types() -> tuple[type, ...]:
+    from ..models.common import Conv1D
+    from ..ops.linear import Linear
+
+    return (Linear, Conv1D)
+
+
+class _FusedTap:
+    """Collector side of ``ops.linear``'s tap: hands the layer its two projection operands and
+    turns the projected activations / output gradients that come back into the module's block
+    of the batch's row accumulator."""
+
+    def __init__(self, collector: "HookCollectorBase", name: str):
+        self.collector, self.name = collector, name
+
+    def operands(self, module: nn.Module, x: Tensor):
+        c = self.collector
+        if not c._tap_accepts(module, x):
+            return None
+        module._tapped = True  # the forward hook that follows skips this call
+        i = getattr(module, LayerAdapter.in_attr(module))
+        o = getattr(module, LayerAdapter.out_attr(module))
+        return c._tap_matrices(self.name, o, i, x.device, x.dtype)
+
+    def collect(self, module: nn.Module, a_proj: Tensor, g_proj: Tensor, lead_shape) -> None:
+        from ..ops import native
+
+        c = self.collector
+        p = c.per_module_projection_dim
+        acc = c._row_acc[: c._fused_rows]
+        off = c._col_offsets[self.name]
+        if c.attribute_tokens:
+            native.proj_token_rows(g_proj, a_proj, c._token_index, acc, p, off)
+        else:
+            n, s = int(lead_shape[0]), int(lead_shape[1])
+            native.proj_contract(g_proj, a_proj, acc, n, s, p, off)
+        c._fused_written.add(self.name)
+
+
 @dataclass
 class HookCollectorBase(ContextDecorator, ABC):
     """Base class of every collector.
@@ -111,6 +153,8 @@ class HookCollectorBase(ContextDecorator, ABC):
         self._current_collection_mask: Tensor | None = None
         # fused-path state (enabled by subclasses through ``enable_fused``)
         self._fused_enabled = False
+        self._tap_dim_ok = False
+        self._hook_fused_ok = False
         self._row_acc: Tensor | None = None
         self._col_offsets: dict[str, int] = {}
         self._fused_mats: dict = {}
@@ -319,9 +363,14 @@ class HookCollectorBase(ContextDecorator, ABC):
             layer._name = name  # type: ignore[attr-defined]
             layer._collect_bias = self.target_info[name][2]  # type: ignore[attr-defined]
             self._fwd_hooks.append(layer.register_forward_hook(self._on_forward))
+            if self._fused_enabled and self._tap_dim_ok and isinstance(layer, _tap_module_types()):
+                # In-tree layers compute the projections inside their own GEMM passes.
+                layer._tap = _FusedTap(self, name)  # type: ignore[attr-defined]
         return self
 
     def _on_forward(self, module: nn.Module, inp: tuple, out):
+        if module.__dict__.pop("_tapped", False):
+            return  # this call was collected through the module's tap
         x = inp[0].detach()
         assert x.ndim == 3, f"Expected input of shape [N, S, I], got {x.shape}"
         self.forward_hook(module, x)
@@ -342,7 +391,7 @@ class HookCollectorBase(ContextDecorator, ABC):
         if self._depth > 0:
             return False
         for layer in self.model.modules():
-            for attr in ("_inputs", "_name", "_collect_bias", "_fused"):
+            for attr in ("_inputs", "_name", "_collect_bias", "_fused", "_tap", "_tapped"):
                 if hasattr(layer, attr):
                     delattr(layer, attr)
         for h in self._fwd_hooks:
@@ -364,13 +413,23 @@ class HookCollectorBase(ContextDecorator, ABC):
 
     # ------------------------------------------------------------------ fused path
 
-    def enable_fused(self, col_offsets: dict[str, int], total_dim: int) -> bool:
-        """Switch on the tcgen05 projection path if the configuration allows it.
-        ``col_offsets`` maps (head-expanded) module names to their first column."""
+    def enable_fused(self, col_offsets: dict[str, int], total_dim: int, token_rows: bool = False) -> bool:
+        """Switch on the tcgen05 projection paths if the configuration allows it.
+        ``col_offsets`` maps (head-expanded) module names to their first column.
+
+        Two paths feed the fp32 row accumulator: *taps* on in-tree layers (projections as
+        side outputs of the layers' own GEMMs; projection dims 8 / 16 / 32 / 64, per-sequence
+        or, with ``token_rows``, per-token rows) and, for any other ``nn.Linear``, the
+        stand-alone projection kernels behind the hooks (dim 16, per-sequence rows).  Modules
+        that neither path covers (bias columns, Adam normalisers, split heads) take the torch
+        expressions and are merged into the accumulator afterwards."""
         self._fused_enabled = False
-        if self.per_module_projection_dim != FUSED_PROJECTION_DIM or self.attribute_tokens:
+        p = self.per_module_projection_dim
+        self._tap_dim_ok = p in TAP_PROJECTION_DIMS
+        self._hook_fused_ok = p == FUSED_PROJECTION_DIM and not self.attribute_tokens
+        if not (self._tap_dim_ok or self._hook_fused_ok):
             return False
-        if self.attention_cfgs:
+        if self.attribute_tokens and not (token_rows and self._tap_dim_ok):
             return False
         dev = next(self.model.parameters()).device
         if dev.type != "cuda":
@@ -385,7 +444,7 @@ class HookCollectorBase(ContextDecorator, ABC):
         return True
 
     def _fused_eligible(self, module: nn.Module, x: Tensor) -> bool:
-        if not self._fused_enabled or module._collect_bias:
+        if not self._fused_enabled or not self._hook_fused_ok or module._collect_bias:
             return False
         if x.dtype not in (torch.bfloat16, torch.float16):
             return False
@@ -414,22 +473,58 @@ class HookCollectorBase(ContextDecorator, ABC):
             self._fused_mats[key] = (p_in.to(dtype).contiguous(), p_out.to(dtype).contiguous())
         return self._fused_mats[key]
 
-    def begin_fused_batch(self, n: int, device) -> None:
-        """Zero the fp32 row accumulator of the coming batch."""
+    def _tap_matrices(self, name: str, o: int, i: int, device, dtype) -> tuple[Tensor, Tensor]:
+        """(P_in [p16, I], P_out [p16, O]) for the GEMM side outputs: the projection matrices
+        with the Adafactor column / row scales folded in, rows zero-padded to a multiple of 16."""
+        key = ("tap", name, device, dtype)
+        if key not in self._fused_mats:
+            p = self.per_module_projection_dim
+            assert p is not None
+            p16 = (p + 15) // 16 * 16
+            p_in = self.projection(name, p, i, "right", device, dtype).float()
+            p_out = self.projection(name, p, o, "left", device, dtype).float()
+            norm = self.processor.normalizers.get(name)
+            if isinstance(norm, AdafactorNormalizer):
+                row, col = self.adafactor_scales(name, norm)
+                p_in = p_in * col.to(device).float()[None, :]
+                p_out = p_out * row.to(device).float()[None, :]
+            pad = lambda m: torch.cat([m, m.new_zeros(p16 - p, m.shape[1])]) if p16 > p else m  # noqa: E731
+            self._fused_mats[key] = (pad(p_in).to(dtype).contiguous(), pad(p_out).to(dtype).contiguous())
+        return self._fused_mats[key]
+
+    def _tap_accepts(self, module: nn.Module, x: Tensor) -> bool:
+        if not self._fused_enabled or not torch.is_grad_enabled() or module._collect_bias:
+            return False
+        if x.dtype not in (torch.bfloat16, torch.float16) or x.ndim != 3 or x.shape[0] != getattr(self, "_fused_n", -1):
+            return False
+        name = module._name
+        if name not in self._col_offsets or name in self.attention_cfgs:
+            return False
+        return not isinstance(self.processor.normalizers.get(name), AdamNormalizer)
+
+    def begin_fused_batch(self, n: int, device, collection_mask: Tensor | None = None) -> None:
+        """Zero the fp32 row accumulator of the coming batch (one row per document, or per
+        collected token when rows are per token)."""
         if not self._fused_enabled:
             return
-        if self._row_acc is None or self._row_acc.shape[0] < n or self._row_acc.device != device:
-            self._row_acc = torch.zeros(max(n, 1), self._total_dim, device=device, dtype=torch.float32)
-        else:
-            self._row_acc[:n].zero_()
-        self._fused_written.clear()
         self._fused_n = n
+        rows = n
+        if self.attribute_tokens:
+            assert collection_mask is not None, "per-token rows need the batch's collection mask"
+            self._token_index = collection_mask.reshape(-1).nonzero(as_tuple=True)[0]
+            rows = int(self._token_index.numel())
+        if self._row_acc is None or self._row_acc.shape[0] < rows or self._row_acc.device != device:
+            self._row_acc = torch.zeros(max(rows, 1), self._total_dim, device=device, dtype=torch.float32)
+        else:
+            self._row_acc[:rows].zero_()
+        self._fused_written.clear()
+        self._fused_rows = rows
 
     def fused_rows(self) -> Tensor:
         """fp32 ``[n, total_dim]`` accumulator of the current batch; blocks of modules
         that took the torch path are copied in from ``mod_grads`` first."""
         assert self._row_acc is not None
-        acc = self._row_acc[: self._fused_n]
+        acc = self._row_acc[: self._fused_rows]
         for name, P in self.mod_grads.items():
             if name in self._fused_written or name not in self._col_offsets:
                 continue
@@ -538,7 +633,7 @@ class HookCollectorBase(ContextDecorator, ABC):
         i = getattr(module, LayerAdapter.in_attr(module))
         _, p_out = self._fused_matrices(name, o, i, g.device, g.dtype)
         native.proj_left_outer(
-            g.contiguous(), p_out, module._inputs, self._row_acc[: self._fused_n], self._col_offsets[name]
+            g.contiguous(), p_out, module._inputs, self._row_acc[: self._fused_rows], self._col_offsets[name]
         )
         self._fused_written.add(name)
         return True
@@ -615,7 +710,7 @@ class CollectorComputer:
         if not hasattr(self, "_total_processed"):
             self._total_processed = torch.zeros((), dtype=torch.long, device=self.device)
         self._total_processed += mask.sum()
-        self.collector.begin_fused_batch(len(indices), self.device)
+        self.collector.begin_fused_batch(len(indices), self.device, mask)
         with self.collector.with_batch(mask):
             losses = self.forward_backward(self.model, x, y, batch)
         self.collector.process_batch(indices, losses=losses)

@@ -83,7 +83,8 @@ class GradientCollector(HookCollectorBase):
             # The scorer's modules may be a subset of the collected ones, in another order:
             # it assembles its query operand in this collector's column layout, or declines.
             if self.scorer is None or self.scorer.set_row_layout(spans, total):
-                self.enable_fused({n: lo for n, (lo, _) in spans.items()}, total)
+                self.enable_fused({n: lo for n, (lo, _) in spans.items()}, total,
+                                  token_rows=self.builder is not None and self._tp == 1)
 
     @HookCollectorBase.split_attention_heads
     def backward_hook(self, module: nn.Module, g: Tensor):

@@ -194,9 +194,9 @@ class Conv1D(nn.Module):
         self.bias = nn.Parameter(torch.zeros(nf))
 
     def forward(self, x: Tensor) -> Tensor:
-        return torch.addmm(self.bias, x.reshape(-1, x.shape[-1]), self.weight).view(
-            *x.shape[:-1], self.nf
-        )
+        from ..ops.linear import linear
+
+        return linear(x, self.weight, self.bias, layout="io", module=self, tap=getattr(self, "_tap", None))
 
     def extra_repr(self) -> str:
         return f"nf={self.nf}, nx={self.nx}"

@@ -72,7 +72,7 @@ class GPT2LMHeadModel(NativeCausalLM):
     def __init__(self, cfg: ModelArgs):
         super().__init__(cfg)
         self.transformer = GPT2Model(cfg)
-        self.lm_head = nn.Linear(cfg.hidden_size, cfg.vocab_size, bias=False)
+        self.lm_head = ops.Linear(cfg.hidden_size, cfg.vocab_size, bias=False)
         self._init_weights(cfg.initializer_range)
         self.lm_head.weight = self.transformer.wte.weight
 

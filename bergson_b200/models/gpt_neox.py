@@ -24,8 +24,8 @@ class NeoXAttention(nn.Module):
         self.head_dim = cfg.head_dim
         self.rot_dim = int(self.head_dim * cfg.rotary_pct)
         self.theta = cfg.rope_theta
-        self.query_key_value = nn.Linear(d, 3 * d, bias=True)
-        self.dense = nn.Linear(d, d, bias=True)
+        self.query_key_value = ops.Linear(d, 3 * d, bias=True)
+        self.dense = ops.Linear(d, d, bias=True)
 
     def forward(self, x: Tensor, cos: Tensor, sin: Tensor) -> Tensor:
         B, S, _ = x.shape
@@ -40,8 +40,8 @@ class NeoXAttention(nn.Module):
 class NeoXMLP(nn.Module):
     def __init__(self, cfg: ModelArgs):
         super().__init__()
-        self.dense_h_to_4h = nn.Linear(cfg.hidden_size, cfg.intermediate_size)
-        self.dense_4h_to_h = nn.Linear(cfg.intermediate_size, cfg.hidden_size)
+        self.dense_h_to_4h = ops.Linear(cfg.hidden_size, cfg.intermediate_size)
+        self.dense_4h_to_h = ops.Linear(cfg.intermediate_size, cfg.hidden_size)
 
     def forward(self, x: Tensor) -> Tensor:
         return self.dense_4h_to_h(ops.gelu(self.dense_h_to_4h(x)))
@@ -78,7 +78,7 @@ class GPTNeoXForCausalLM(NativeCausalLM):
     def __init__(self, cfg: ModelArgs):
         super().__init__(cfg)
         self.gpt_neox = NeoXModel(cfg)
-        self.embed_out = nn.Linear(cfg.hidden_size, cfg.vocab_size, bias=False)
+        self.embed_out = ops.Linear(cfg.hidden_size, cfg.vocab_size, bias=False)
         self._init_weights(cfg.initializer_range)
 
     def get_input_embeddings(self):

@@ -25,10 +25,10 @@ class LlamaAttention(nn.Module):
         super().__init__()
         d, hd = cfg.hidden_size, cfg.head_dim
         self.num_heads, self.kv_heads, self.head_dim = cfg.num_attention_heads, cfg.kv_heads, hd
-        self.q_proj = nn.Linear(d, self.num_heads * hd, bias=cfg.attention_bias)
-        self.k_proj = nn.Linear(d, self.kv_heads * hd, bias=cfg.attention_bias)
-        self.v_proj = nn.Linear(d, self.kv_heads * hd, bias=cfg.attention_bias)
-        self.o_proj = nn.Linear(self.num_heads * hd, d, bias=cfg.attention_bias)
+        self.q_proj = ops.Linear(d, self.num_heads * hd, bias=cfg.attention_bias)
+        self.k_proj = ops.Linear(d, self.kv_heads * hd, bias=cfg.attention_bias)
+        self.v_proj = ops.Linear(d, self.kv_heads * hd, bias=cfg.attention_bias)
+        self.o_proj = ops.Linear(self.num_heads * hd, d, bias=cfg.attention_bias)
         self.tp_group = None  # set by parallel.tensor_parallel.apply_tensor_parallel
 
     def forward(self, x: Tensor, cos: Tensor, sin: Tensor) -> Tensor:
@@ -51,9 +51,9 @@ class LlamaMLP(nn.Module):
     def __init__(self, cfg: ModelArgs):
         super().__init__()
         d, f = cfg.hidden_size, cfg.intermediate_size
-        self.gate_proj = nn.Linear(d, f, bias=cfg.mlp_bias)
-        self.up_proj = nn.Linear(d, f, bias=cfg.mlp_bias)
-        self.down_proj = nn.Linear(f, d, bias=cfg.mlp_bias)
+        self.gate_proj = ops.Linear(d, f, bias=cfg.mlp_bias)
+        self.up_proj = ops.Linear(d, f, bias=cfg.mlp_bias)
+        self.down_proj = ops.Linear(f, d, bias=cfg.mlp_bias)
         self.tp_group = None  # set by parallel.tensor_parallel.apply_tensor_parallel
 
     def forward(self, x: Tensor) -> Tensor:
@@ -92,7 +92,7 @@ class LlamaForCausalLM(NativeCausalLM):
     def __init__(self, cfg: ModelArgs):
         super().__init__(cfg)
         self.model = LlamaModel(cfg)
-        self.lm_head = nn.Linear(cfg.hidden_size, cfg.vocab_size, bias=False)
+        self.lm_head = ops.Linear(cfg.hidden_size, cfg.vocab_size, bias=False)
         self._init_weights(cfg.initializer_range)
         if cfg.tie_word_embeddings:
             self.lm_head.weight = self.model.embed_tokens.weight

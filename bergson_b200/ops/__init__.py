@@ -1,6 +1,7 @@
 """Operators: model-side ops (``functional``), attribution kernels (``attribution``)
 and the loader of the in-tree sm_100a extension (``native``)."""
 
+from .linear import Linear, linear
 from .functional import (
     causal_attention,
     composable,
@@ -15,6 +16,8 @@ from .functional import (
 )
 
 __all__ = [
+    "Linear",
+    "linear",
     "causal_attention",
     "composable",
     "gelu",

@@ -43,6 +43,7 @@ static EncodeTiledFn get_encode_fn() {
 // Row-major 16-bit tensor viewed as (K contiguous, rows, batch); box = 64 x box_rows x 1.
 static bool make_tmap_3d(CUtensorMap* map, const void* base, int fmt, uint64_t K, uint64_t rows,
                          uint64_t batch, uint32_t box_rows) {
+  ensure_context_bound();
   EncodeTiledFn enc = get_encode_fn();
   if (!enc) return false;
   cuuint64_t dims[3] = {K, rows, batch};
@@ -57,6 +58,7 @@ static bool make_tmap_3d(CUtensorMap* map, const void* base, int fmt, uint64_t K
 
 static bool make_tmap_2d(CUtensorMap* map, const void* base, int fmt, uint64_t K, uint64_t rows,
                          uint32_t box_rows) {
+  ensure_context_bound();
   EncodeTiledFn enc = get_encode_fn();
   if (!enc) return false;
   cuuint64_t dims[2] = {K, rows};
@@ -299,5 +301,115 @@ extern "C" int bgn_finalize_rows(const float* acc, void* out, const long* row_in
     default:
       finalize_rows_kernel<float><<<N, threads, 0, stream>>>(acc, (float*)out, row_index, D, out_ld, lo, hi, unit_norm);
   }
+  return int(cudaGetLastError());
+}
+
+// ---- per-example contraction of the projected operands ---------------------------------------
+//
+// The Linear layers' GEMMs emit A' = A P_in^T and G' = G P_out^T as fp32 side outputs ([T, ldp]
+// with the first p columns meaningful).  The stored block of example n is
+//   acc[n, col_off + i * p + j] = sum_s G'[n*S + s, i] * A'[n*S + s, j],
+// formed here by one CTA per example in a fixed order (no atomics: two runs give the same bits).
+
+namespace bgn {
+
+constexpr int kContractThreads = 1024;
+constexpr int kContractChunk = 64;  // tokens staged per step and group
+
+template <int P>
+__global__ void __launch_bounds__(kContractThreads)
+proj_contract_kernel(const float* __restrict__ g_proj, const float* __restrict__ a_proj, float* __restrict__ acc,
+                     int S, int ldp, long ld, long col_off) {
+  constexpr int kOut = P * P;
+  constexpr int kGroups = kOut >= kContractThreads ? 1 : (kContractThreads / kOut > 4 ? 4 : kContractThreads / kOut);  // token groups
+  constexpr int kPerThread = kOut >= kContractThreads ? kOut / kContractThreads : 1;
+  __shared__ float gs[kGroups][kContractChunk][P + 1];
+  __shared__ float as[kGroups][kContractChunk][P + 1];
+  __shared__ float red[kGroups][kOut >= kContractThreads ? 1 : kOut];
+  const int n = blockIdx.x;
+  const int tid = threadIdx.x;
+  const int grp = kOut >= kContractThreads ? 0 : tid / kOut;
+  const int o0 = kOut >= kContractThreads ? tid * kPerThread : tid % kOut;
+  const float* g0 = g_proj + long(n) * S * ldp;
+  const float* a0 = a_proj + long(n) * S * ldp;
+  float sum[kPerThread];
+#pragma unroll
+  for (int q = 0; q < kPerThread; ++q) sum[q] = 0.f;
+  // Token range of this group, walked in chunks that the whole CTA stages together.
+  const int per_group = (S + kGroups - 1) / kGroups;
+  for (int base = 0; base < per_group; base += kContractChunk) {
+    // cooperative load: every thread copies elements of every group's chunk
+    for (int e = tid; e < kGroups * kContractChunk * P; e += kContractThreads) {
+      const int gq = e / (kContractChunk * P);
+      const int r = (e / P) % kContractChunk;
+      const int c = e % P;
+      const int s_local = base + r;
+      const int s = gq * per_group + s_local;
+      const bool ok = s_local < per_group && s < S;
+      gs[gq][r][c] = ok ? g0[long(s) * ldp + c] : 0.f;
+      as[gq][r][c] = ok ? a0[long(s) * ldp + c] : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int q = 0; q < kPerThread; ++q) {
+      if (grp >= kGroups) break;  // threads beyond kGroups * kOut only help with the loads
+      const int o = o0 + q;
+      const int i = o / P, j = o % P;
+      float acc_q = sum[q];
+#pragma unroll 8
+      for (int r = 0; r < kContractChunk; ++r) acc_q = fmaf(gs[grp][r][i], as[grp][r][j], acc_q);
+      sum[q] = acc_q;
+    }
+    __syncthreads();
+  }
+  float* dst = acc + long(n) * ld + col_off;
+  if constexpr (kOut >= kContractThreads) {
+#pragma unroll
+    for (int q = 0; q < kPerThread; ++q) dst[o0 + q] = sum[0 + q];
+  } else {
+    if (grp < kGroups) red[grp][o0] = sum[0];
+    __syncthreads();
+    if (tid < kOut) {
+      float t = 0.f;
+#pragma unroll
+      for (int gq = 0; gq < kGroups; ++gq) t += red[gq][tid];  // fixed order
+      dst[tid] = t;
+    }
+  }
+}
+
+// Per-token rows: out[r, col_off + i * p + j] = G'[t, i] * A'[t, j] for the r-th collected token
+// t = token_index[r] (flat position in the [N * S] batch).
+__global__ void proj_token_rows_kernel(const float* __restrict__ g_proj, const float* __restrict__ a_proj,
+                                       const long* __restrict__ token_index, float* __restrict__ out, int p, int ldp,
+                                       long ld, long col_off) {
+  const long r = blockIdx.x;
+  const long t = token_index[r];
+  const float* g = g_proj + t * ldp;
+  const float* a = a_proj + t * ldp;
+  float* dst = out + r * ld + col_off;
+  for (int o = threadIdx.x; o < p * p; o += blockDim.x) dst[o] = g[o / p] * a[o % p];
+}
+
+}  // namespace bgn
+
+extern "C" int bgn_proj_contract(const float* g_proj, const float* a_proj, float* acc, int N, int S, int p, int ldp,
+                                 long ld, long col_off, cudaStream_t stream) {
+  if (N <= 0 || S <= 0 || ldp < p) return int(cudaErrorInvalidValue);
+  switch (p) {
+    case 8: proj_contract_kernel<8><<<N, kContractThreads, 0, stream>>>(g_proj, a_proj, acc, S, ldp, ld, col_off); break;
+    case 16: proj_contract_kernel<16><<<N, kContractThreads, 0, stream>>>(g_proj, a_proj, acc, S, ldp, ld, col_off); break;
+    case 32: proj_contract_kernel<32><<<N, kContractThreads, 0, stream>>>(g_proj, a_proj, acc, S, ldp, ld, col_off); break;
+    case 64: proj_contract_kernel<64><<<N, kContractThreads, 0, stream>>>(g_proj, a_proj, acc, S, ldp, ld, col_off); break;
+    default: return int(cudaErrorInvalidValue);
+  }
+  return int(cudaGetLastError());
+}
+
+extern "C" int bgn_proj_token_rows(const float* g_proj, const float* a_proj, const long* token_index, float* out,
+                                   long rows, int p, int ldp, long ld, long col_off, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (p <= 0 || ldp < p) return int(cudaErrorInvalidValue);
+  proj_token_rows_kernel<<<unsigned(rows), 256, 0, stream>>>(g_proj, a_proj, token_index, out, p, ldp, ld, col_off);
   return int(cudaGetLastError());
 }

@@ -308,7 +308,7 @@ void cov_syrk(at::Tensor x, std::vector<int64_t> dst_ptrs, std::vector<int64_t> 
 std::vector<at::Tensor> gemm(at::Tensor a, at::Tensor b, bool a_mn, bool b_mn, c10::optional<at::Tensor> out,
                              bool out_f32, c10::optional<at::Tensor> bias, bool accumulate,
                              c10::optional<at::Tensor> aux_p, int64_t cta_group, bool sq_accumulate,
-                             int64_t wait_cycles, c10::optional<at::Tensor> status) {
+                             int64_t wait_cycles, c10::optional<at::Tensor> status, int64_t panel, c10::optional<at::Tensor> trace, bool no_tma_store) {
   TORCH_CHECK(a.is_cuda() && b.is_cuda() && a.scalar_type() == b.scalar_type(), "gemm: CUDA operands of one dtype");
   TORCH_CHECK((a.dim() == 2 || a.dim() == 3) && a.dim() == b.dim() && a.stride(-1) == 1 && b.stride(-1) == 1,
               "gemm: 2-D or 3-D operands with contiguous last dimension");
@@ -364,9 +364,39 @@ std::vector<at::Tensor> gemm(at::Tensor a, at::Tensor b, bool a_mn, bool b_mn, c
   g.cta_group = (int)cta_group;
   g.sm_count = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
   g.wait_cycles = wait_cycles;
+  g.panel = (int)panel;
+  g.no_tma_store = no_tma_store;
+  if (trace.has_value()) {
+    TORCH_CHECK(trace->is_cuda() && trace->scalar_type() == at::kLong && trace->is_contiguous());
+    g.trace = reinterpret_cast<long long*>(trace->data_ptr<int64_t>());
+  }
   int* st = status.has_value() ? status->data_ptr<int>() : status_ptr(a);
   check(bgn_gemm(&g, st, stream()), "gemm");
   return {d, aux_out};
+}
+
+void proj_contract(at::Tensor g_proj, at::Tensor a_proj, at::Tensor acc, int64_t n, int64_t s, int64_t p, int64_t col_off) {
+  CHECK_CUDA_CONTIG(g_proj); CHECK_CUDA_CONTIG(a_proj);
+  TORCH_CHECK(g_proj.scalar_type() == at::kFloat && a_proj.scalar_type() == at::kFloat && g_proj.dim() == 2 &&
+              g_proj.sizes() == a_proj.sizes() && g_proj.size(0) == n * s && g_proj.size(1) >= p);
+  TORCH_CHECK(acc.is_cuda() && acc.scalar_type() == at::kFloat && acc.dim() == 2 && acc.stride(1) == 1 &&
+              acc.size(0) >= n && col_off + p * p <= acc.size(1));
+  c10::cuda::CUDAGuard guard(acc.device());
+  check(bgn_proj_contract(g_proj.data_ptr<float>(), a_proj.data_ptr<float>(), acc.data_ptr<float>(), (int)n, (int)s,
+                          (int)p, (int)g_proj.size(1), acc.stride(0), col_off, stream()), "proj_contract");
+}
+
+void proj_token_rows(at::Tensor g_proj, at::Tensor a_proj, at::Tensor token_index, at::Tensor out, int64_t p,
+                     int64_t col_off) {
+  CHECK_CUDA_CONTIG(g_proj); CHECK_CUDA_CONTIG(a_proj); CHECK_CUDA_CONTIG(token_index);
+  TORCH_CHECK(g_proj.scalar_type() == at::kFloat && g_proj.sizes() == a_proj.sizes() && g_proj.size(1) >= p &&
+              token_index.scalar_type() == at::kLong);
+  TORCH_CHECK(out.is_cuda() && out.scalar_type() == at::kFloat && out.dim() == 2 && out.stride(1) == 1 &&
+              out.size(0) >= token_index.numel() && col_off + p * p <= out.size(1));
+  c10::cuda::CUDAGuard guard(out.device());
+  check(bgn_proj_token_rows(g_proj.data_ptr<float>(), a_proj.data_ptr<float>(), token_index.data_ptr<int64_t>(),
+                            out.data_ptr<float>(), token_index.numel(), (int)p, (int)g_proj.size(1), out.stride(0),
+                            col_off, stream()), "proj_token_rows");
 }
 
 at::Tensor wait_probe(int64_t budget_cycles, at::Tensor status) {
@@ -404,7 +434,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm", &gemm, py::arg("a"), py::arg("b"), py::arg("a_mn") = false, py::arg("b_mn") = false,
         py::arg("out") = py::none(), py::arg("out_f32") = false, py::arg("bias") = py::none(),
         py::arg("accumulate") = false, py::arg("aux_p") = py::none(), py::arg("cta_group") = 2,
-        py::arg("sq_accumulate") = false, py::arg("wait_cycles") = 0, py::arg("status") = py::none());
+        py::arg("sq_accumulate") = false, py::arg("wait_cycles") = 0, py::arg("status") = py::none(), py::arg("panel") = 0, py::arg("trace") = py::none(), py::arg("no_tma_store") = false);
+  m.def("proj_contract", &proj_contract);
+  m.def("proj_token_rows", &proj_token_rows);
   m.def("wait_probe", &wait_probe);
   m.def("kernel_status", &kernel_status);
 }

@@ -11,6 +11,19 @@
 
 namespace bgn {
 
+// Tensor maps are built with a driver-API call, which needs the device's primary context to be
+// current on the calling thread.  Runtime-API calls bind it implicitly, driver calls do not, and
+// a thread that has not touched the runtime yet (an autograd worker running its first node)
+// would get an invalid-context error.  Cheap after the first call per thread and device.
+inline void ensure_context_bound() {
+  static thread_local int bound_device = -1;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev == bound_device) return;
+  cudaSetDevice(dev);
+  cudaFree(nullptr);
+  bound_device = dev;
+}
+
 // Status word values written by kernels that give up on a wait.
 enum KernelStatus : int {
   kStatusOk = 0,

@@ -237,6 +237,7 @@ extern "C" int bgn_cov_syrk(const void* x, long T, int D, int fmt, float* const*
   if (D % 8 != 0 || (reinterpret_cast<uintptr_t>(x) & 15) || world < 1 || world > 8)
     return int(cudaErrorInvalidValue);
   if (T <= 0 && local == nullptr) return 0;
+  ensure_context_bound();
   EncodeTiledFn enc = cov_encode_fn();
   if (!enc) return int(cudaErrorInvalidValue);
   CUtensorMap tmap;

@@ -29,6 +29,7 @@ static EncodeTiledFn gemm_encode_fn() {
 // (elements); box = 64 x box_rows x 1 with the 128-byte swizzle.
 static bool gemm_tmap(CUtensorMap* map, const void* base, int fmt, uint64_t inner, uint64_t rows, uint64_t batch,
                       uint64_t ld, uint64_t bs, uint32_t box_rows) {
+  ensure_context_bound();
   EncodeTiledFn enc = gemm_encode_fn();
   if (!enc || (reinterpret_cast<uintptr_t>(base) & 15) || (ld % 8) || (batch > 1 && bs % 8)) return false;
   const CUtensorMapDataType dt = fmt == 1 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
@@ -41,9 +42,27 @@ static bool gemm_tmap(CUtensorMap* map, const void* base, int fmt, uint64_t inne
              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// MN-major operand [batch, K, mn] (mn contiguous, a multiple of 64) viewed as
+// (64 mn-in-block, K, mn / 64 blocks[, batch]); box = 64 x 64 x blocks x 1, so one load brings
+// `blocks` consecutive 64-wide column blocks, each as its own 8 KB swizzled slab.
+static bool gemm_tmap_blocked(CUtensorMap* map, const void* base, int fmt, uint64_t mn, uint64_t K, uint64_t batch,
+                              uint64_t ld, uint64_t bs, uint32_t blocks) {
+  ensure_context_bound();
+  EncodeTiledFn enc = gemm_encode_fn();
+  if (!enc || (reinterpret_cast<uintptr_t>(base) & 15) || (ld % 8) || (batch > 1 && bs % 8) || (mn % 64)) return false;
+  const CUtensorMapDataType dt = fmt == 1 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  cuuint64_t dims[4] = {64, K, mn / 64, batch > 1 ? batch : 1};
+  cuuint64_t strides[3] = {ld * 2, 128, (batch > 1 ? bs : ld * K) * 2};
+  cuuint32_t box[4] = {64, 64, blocks, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  return enc(map, dt, batch > 1 ? 4 : 3, const_cast<void*>(base), dims, strides, box, estr,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 template <int CG, int FMT, bool OUT32>
-static cudaError_t launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tp, const GemmParams& p,
-                               int grid, int* status, cudaStream_t stream) {
+static cudaError_t launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tp, const CUtensorMap& td,
+                               const GemmParams& p, int grid, int* status, cudaStream_t stream) {
   auto kern = gemm_kernel<CG, FMT, OUT32>;
   static bool attr_set = false;  // one flag per instantiation
   if (!attr_set) {
@@ -63,7 +82,7 @@ static cudaError_t launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, con
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, kern, ta, tb, tp, p, status);
+  return cudaLaunchKernelEx(&cfg, kern, ta, tb, tp, td, p, status);
 }
 
 }  // namespace bgn
@@ -77,15 +96,23 @@ extern "C" int bgn_gemm(const BgnGemmArgs* a, int* status, cudaStream_t stream) 
   if (a->sq_accumulate && !a->out_f32) return int(cudaErrorInvalidValue);
   CUtensorMap ta, tb, tp;
   const uint64_t B = uint64_t(a->batch);
-  // A: K-major [M, K] (box 64 k x 128 rows) or MN-major [K, M] (boxes of 64 m x 64 k).
-  const bool ok_a = a->a_mn ? gemm_tmap(&ta, a->a, a->fmt, a->M, a->K, B, a->lda, a->a_batch_stride, 64)
-                            : gemm_tmap(&ta, a->a, a->fmt, a->K, a->M, B, a->lda, a->a_batch_stride, 128);
-  const bool ok_b = a->b_mn ? gemm_tmap(&tb, a->b, a->fmt, a->N, a->K, B, a->ldb, a->b_batch_stride, 64)
-                            : gemm_tmap(&tb, a->b, a->fmt, a->K, a->N, B, a->ldb, a->b_batch_stride, kGemmTileN / cg);
-  if (!ok_a || !ok_b) return int(cudaErrorInvalidValue);
+  // A: K-major [M, K] (box 64 k x 128 rows) or MN-major [K, M] (64 m x 64 k slabs; one blocked
+  // load when M is a multiple of 64, else one load per slab).
+  const bool a_blocked = a->a_mn && a->M % 64 == 0;
+  const bool b_blocked = a->b_mn && a->N % 64 == 0;
+  const bool ok_a = !a->a_mn ? gemm_tmap(&ta, a->a, a->fmt, a->K, a->M, B, a->lda, a->a_batch_stride, 128)
+                    : a_blocked ? gemm_tmap_blocked(&ta, a->a, a->fmt, a->M, a->K, B, a->lda, a->a_batch_stride, 2)
+                                : gemm_tmap(&ta, a->a, a->fmt, a->M, a->K, B, a->lda, a->a_batch_stride, 64);
+  const bool ok_b = !a->b_mn ? gemm_tmap(&tb, a->b, a->fmt, a->K, a->N, B, a->ldb, a->b_batch_stride, kGemmTileN / cg)
+                    : b_blocked ? gemm_tmap_blocked(&tb, a->b, a->fmt, a->N, a->K, B, a->ldb, a->b_batch_stride,
+                                                    kGemmTileN / cg / 64)
+                                : gemm_tmap(&tb, a->b, a->fmt, a->N, a->K, B, a->ldb, a->b_batch_stride, 64);
+  // Distinct codes tell the caller which operand's layout was rejected (alignment, strides).
+  if (!ok_a) return int(cudaErrorInvalidPitchValue);
+  if (!ok_b) return int(cudaErrorInvalidSymbol);
   if (a->aux_n > 0) {
     if (!a->aux_p || !a->aux_out || !gemm_tmap(&tp, a->aux_p, a->fmt, a->K, a->aux_n, 1, a->K, 0, a->aux_n / cg))
-      return int(cudaErrorInvalidValue);
+      return int(cudaErrorInvalidTexture);
   } else {
     tp = tb;
   }
@@ -98,11 +125,38 @@ extern "C" int bgn_gemm(const BgnGemmArgs* a, int* status, cudaStream_t stream) 
   p.aux_n = a->aux_n; p.aux_out = a->aux_out; p.aux_ld = a->aux_n;
   p.batch = a->batch; p.d_batch_stride = a->d_batch_stride; p.sq_accumulate = a->sq_accumulate;
   p.wait_cycles = a->wait_cycles > 0 ? a->wait_cycles : kMaxWaitCycles;
+  p.trace = a->trace;
+  // 16-bit outputs that are simply overwritten go through shared-memory staging and TMA stores
+  // (box 64 columns x 32 rows); anything else is written from registers.
+  CUtensorMap td = ta;
+  p.tma_store = 0;
+  if (!a->out_f32 && !a->accumulate && a->batch == 1 && !a->no_tma_store) {
+    EncodeTiledFn enc = gemm_encode_fn();
+    if (enc && (reinterpret_cast<uintptr_t>(a->d) & 15) == 0 && a->ldd % 8 == 0) {
+      cuuint64_t dims[2] = {cuuint64_t(a->N), cuuint64_t(a->M)};
+      cuuint64_t strides[1] = {cuuint64_t(a->ldd) * 2};
+      cuuint32_t box[2] = {64, 32};
+      cuuint32_t estr[2] = {1, 1};
+      const CUtensorMapDataType dt = a->fmt == 1 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+      if (enc(&td, dt, 2, a->d, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+              CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS)
+        p.tma_store = 1;
+    }
+  }
+  p.a_blocked = a_blocked ? 1 : 0;
+  p.b_blocked = b_blocked ? 1 : 0;
 
   const int tile_m = 128 * cg;
   const long tiles_m = (a->M + tile_m - 1) / tile_m;
   const long tiles_n = (a->N + kGemmTileN - 1) / kGemmTileN + (a->aux_n > 0 ? 1 : 0);
   const long tiles = tiles_m * tiles_n * a->batch;
+  // Rasterisation panel: as many tile columns as keep the panel's B slab (256 K-long rows per
+  // column) around 32 MB, so that it stays in L2 while the tile rows stream past it.
+  long panel = a->panel > 0 ? a->panel : (32l << 20) / (long(kGemmTileN) * a->K * 2);
+  if (panel < 2) panel = 2;
+  if (panel > 16 && a->panel <= 0) panel = 16;
+  if (panel > tiles_n) panel = tiles_n;
+  p.panel = int(panel);
   long groups = a->sm_count / cg;
   if (groups < 1) groups = 1;
   if (groups > tiles) groups = tiles;
@@ -110,15 +164,15 @@ extern "C" int bgn_gemm(const BgnGemmArgs* a, int* status, cudaStream_t stream) 
   cudaError_t e;
   const bool bf = a->fmt == 1;
   if (cg == 2) {
-    e = a->out_f32 ? (bf ? launch_gemm<2, 1, true>(ta, tb, tp, p, grid, status, stream)
-                         : launch_gemm<2, 0, true>(ta, tb, tp, p, grid, status, stream))
-                   : (bf ? launch_gemm<2, 1, false>(ta, tb, tp, p, grid, status, stream)
-                         : launch_gemm<2, 0, false>(ta, tb, tp, p, grid, status, stream));
+    e = a->out_f32 ? (bf ? launch_gemm<2, 1, true>(ta, tb, tp, td, p, grid, status, stream)
+                         : launch_gemm<2, 0, true>(ta, tb, tp, td, p, grid, status, stream))
+                   : (bf ? launch_gemm<2, 1, false>(ta, tb, tp, td, p, grid, status, stream)
+                         : launch_gemm<2, 0, false>(ta, tb, tp, td, p, grid, status, stream));
   } else {
-    e = a->out_f32 ? (bf ? launch_gemm<1, 1, true>(ta, tb, tp, p, grid, status, stream)
-                         : launch_gemm<1, 0, true>(ta, tb, tp, p, grid, status, stream))
-                   : (bf ? launch_gemm<1, 1, false>(ta, tb, tp, p, grid, status, stream)
-                         : launch_gemm<1, 0, false>(ta, tb, tp, p, grid, status, stream));
+    e = a->out_f32 ? (bf ? launch_gemm<1, 1, true>(ta, tb, tp, td, p, grid, status, stream)
+                         : launch_gemm<1, 0, true>(ta, tb, tp, td, p, grid, status, stream))
+                   : (bf ? launch_gemm<1, 1, false>(ta, tb, tp, td, p, grid, status, stream)
+                         : launch_gemm<1, 0, false>(ta, tb, tp, td, p, grid, status, stream));
   }
   return int(e);
 }

@@ -6,15 +6,16 @@
 // weight-gradient (g^T x) products of a Linear layer without any transposed copy.
 //
 // Structure (one CTA, or a pair of CTAs on neighbouring SMs when CG == 2):
-//   * warp 0, one lane: TMA producer; a ring of shared-memory stages, each holding a
-//     128-row slab of A and (256 / CG) rows of B, 64 reduction elements deep;
+//   * warps 0 and 6, one lane each: TMA producers of the A and of the B operand; a ring of
+//     shared-memory stages, each holding a 128-row slab of A and (256 / CG) rows of B, 64
+//     reduction elements deep (one TMA instruction per operand and stage);
 //   * warp 1, one lane of the leader CTA: issues tcgen05.mma (cta_group::CG); with CG == 2
 //     the instruction spans both CTAs (M = 256: 128 accumulator rows in each CTA's TMEM,
 //     each CTA supplies half of B), which halves the shared-memory traffic per flop;
 //   * warps 2..5: epilogue; they drain one of two TMEM accumulator stages (256 columns
 //     each) while the tensor cores fill the other for the CTA's next tile.
 // CTAs are persistent: tile indices are dealt round-robin over the grid, rasterised in
-// panels of 8 tile columns so that a wave of CTAs shares its A and B slabs through L2.
+// panels of a few tile columns so that a wave of CTAs shares its A and B slabs through L2.
 //
 // Optional extra output ("aux tile"): one more tile column per tile row whose B operand is a
 // small matrix P [aux_n, K] (aux_n <= 64), written as fp32 [M, aux_n].  The Linear layers use it
@@ -32,8 +33,7 @@ namespace bgn {
 
 constexpr int kGemmBlockK = 64;
 constexpr int kGemmTileN = 256;
-constexpr int kGemmThreadsV2 = 192;
-constexpr int kGemmPanel = 8;  // tile columns per rasterisation panel
+constexpr int kGemmThreadsV2 = 224;
 
 struct GemmParams {
   int M, N, K;
@@ -50,7 +50,12 @@ struct GemmParams {
   long d_batch_stride; // elements between consecutive batch items of d (0: all batches add
                        // into the same matrix, see sq_accumulate)
   int sq_accumulate;   // 1: d (fp32) += result^2 with vector reductions (batched sum of squares)
+  int panel;           // tile columns per rasterisation panel
+  int a_blocked;       // MN-major A addressed through a (64, K, M/64[, batch]) map: one load per stage
+  int b_blocked;       // likewise for an MN-major B
+  int tma_store;       // 16-bit output written through shared-memory staging and TMA stores
   long long wait_cycles;
+  long long* trace;    // optional: per-tile timestamps of CTA group 0 (8 values per tile); null in production
 };
 
 template <int CG>
@@ -59,8 +64,10 @@ struct GemmSmemV2 {
   static constexpr int kBRows = kGemmTileN / CG;                        // rows of B per CTA
   static constexpr int kBBytes = kBRows * kGemmBlockK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kStages = (227 * 1024 - 2048) / kStageBytes;     // 4 (CG 1) or 6 (CG 2)
-  static constexpr int kBytes = kStages * kStageBytes + 1024 + 512;
+  // Output staging for the TMA-store epilogue: 128 rows x 256 columns of a 16-bit type.
+  static constexpr int kStagingBytes = 128 * kGemmTileN * 2;            // 64 KB
+  static constexpr int kStages = (227 * 1024 - 2048 - kStagingBytes) / kStageBytes;  // 3 (CG 1) or 5 (CG 2)
+  static constexpr int kBytes = kStages * kStageBytes + kStagingBytes + 1024 + 512;
 };
 
 // ---- cluster helpers ------------------------------------------------------------------------
@@ -86,36 +93,51 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 
+// One tiled TMA load of rank 2..4 into this CTA's shared memory.  With CG == 2 the barrier
+// address may belong to the leader CTA (pair form of the instruction); no multicast.
 template <int CG>
-__device__ __forceinline__ void tma_load_nd(uint32_t dst, const CUtensorMap* m, uint32_t bar, int c0, int c1, int c2,
-                                            bool three_d) {
+__device__ __forceinline__ void tma_load_nd(uint32_t dst, const CUtensorMap* m, uint32_t bar, int rank, int c0, int c1,
+                                            int c2, int c3) {
+  const uint64_t map = reinterpret_cast<uint64_t>(m);
   if constexpr (CG == 1) {
-    if (three_d) {
-      asm volatile(
-          "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
-          ::"r"(dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
-          : "memory");
+    if (rank == 2) {
+      asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                   ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1) : "memory");
+    } else if (rank == 3) {
+      asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+                   ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2) : "memory");
     } else {
-      asm volatile(
-          "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-          ::"r"(dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(c0), "r"(c1)
-          : "memory");
+      asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+                   ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
     }
   } else {
-    // Pair form: the destination is this CTA's shared memory, the barrier the leader CTA's.
-    if (three_d) {
-      asm volatile(
-          "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, "
-          "%4, %5}], [%2];" ::"r"(dst),
-          "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
-          : "memory");
+    if (rank == 2) {
+      asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                   ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1) : "memory");
+    } else if (rank == 3) {
+      asm volatile("cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+                   ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2) : "memory");
     } else {
-      asm volatile(
-          "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, "
-          "%4}], [%2];" ::"r"(dst),
-          "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(c0), "r"(c1)
-          : "memory");
+      asm volatile("cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+                   ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
     }
+  }
+}
+
+// Load `rows` rows (a multiple of 64 when MN-major) x 64 reduction elements of one operand.
+//   K-major:            box (64 k, rows)            at (k0, row0[, batch])
+//   MN-major, blocked:  box (64 mn, 64 k, rows/64)  at (0, k0, row0 / 64[, batch])
+//   MN-major, plain:    rows/64 boxes (64 mn, 64 k) at (row0 + 64 b, k0[, batch])
+template <int CG>
+__device__ __forceinline__ void load_operand(uint32_t dst, const CUtensorMap* m, uint32_t bar, bool mn, bool blocked,
+                                             int rows, int row0, int k0, int batch, bool batched) {
+  if (!mn) {
+    tma_load_nd<CG>(dst, m, bar, batched ? 3 : 2, k0, row0, batch, 0);
+  } else if (blocked) {
+    tma_load_nd<CG>(dst, m, bar, batched ? 4 : 3, 0, k0, row0 >> 6, batch);
+  } else {
+    for (int b = 0; b < (rows >> 6); ++b)
+      tma_load_nd<CG>(dst + b * 8192, m, bar, batched ? 3 : 2, row0 + b * 64, k0, batch, 0);
   }
 }
 
@@ -204,18 +226,18 @@ struct GemmTile {
 };
 
 // Tile `t` of the flattened (batch, panel, row, column) order; tiles_nt counts the aux column.
-__device__ __forceinline__ GemmTile gemm_tile(long t, int tiles_m, int tiles_n, int tiles_nt) {
+__device__ __forceinline__ GemmTile gemm_tile(long t, int tiles_m, int tiles_n, int tiles_nt, int panel_w) {
   GemmTile r;
   const long per_batch = long(tiles_m) * tiles_nt;
   r.batch = int(t / per_batch);
   const int u = int(t - r.batch * per_batch);
-  const int per_panel = kGemmPanel * tiles_m;
+  const int per_panel = panel_w * tiles_m;
   const int panel = u / per_panel;
   const int rem = u - panel * per_panel;
-  const int left = tiles_nt - panel * kGemmPanel;
-  const int width = left < kGemmPanel ? left : kGemmPanel;
+  const int left = tiles_nt - panel * panel_w;
+  const int width = left < panel_w ? left : panel_w;
   r.tm = rem / width;
-  r.tn = panel * kGemmPanel + rem % width;
+  r.tn = panel * panel_w + rem % width;
   r.aux = r.tn >= tiles_n;
   return r;
 }
@@ -223,7 +245,8 @@ __device__ __forceinline__ GemmTile gemm_tile(long t, int tiles_m, int tiles_n, 
 template <int CG, int FMT, bool OUT32>
 __global__ void __launch_bounds__(kGemmThreadsV2, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-            const __grid_constant__ CUtensorMap tmap_p, GemmParams p, int* status) {
+            const __grid_constant__ CUtensorMap tmap_p, const __grid_constant__ CUtensorMap tmap_d, GemmParams p,
+            int* status) {
   using S = GemmSmemV2<CG>;
   using InT = typename std::conditional<FMT == 1, __nv_bfloat16, __half>::type;
   constexpr int kStages = S::kStages;
@@ -231,7 +254,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(tiles + kStages * S::kStageBytes);
+  uint8_t* staging = tiles + kStages * S::kStageBytes;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(staging + S::kStagingBytes);
   uint64_t* empty_bar = full_bar + kStages;
   uint64_t* tmem_full_bar = empty_bar + kStages;   // [2]
   uint64_t* tmem_empty_bar = tmem_full_bar + 2;    // [2]
@@ -262,6 +286,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     tma_prefetch_desc(&tmap_a);
     tma_prefetch_desc(&tmap_b);
     if (p.aux_n > 0) tma_prefetch_desc(&tmap_p);
+    if (p.tma_store) tma_prefetch_desc(&tmap_d);
   }
   if (warp == 1) tmem_alloc_cg<CG>(tmem_slot, 512);
   tc_fence_before();
@@ -270,73 +295,73 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 0) {
+  if (warp == 0 || warp == 6) {
     if (lane == 0) {
-      // ---------------- producer: this CTA's halves of every stage ----------------
-      long it = 0;  // k-block counter across tiles
+      // ---------------- producers: warp 0 loads this CTA's slab of A, warp 6 its rows of B ----------------
+      const bool is_a = warp == 0;
+      uint32_t stage = 0, phase = 0;
+      long issued = 0;
       bool ok = true;
       for (long t = group; t < num_tiles && ok; t += num_groups) {
-        const GemmTile tile = gemm_tile(t, tiles_m, tiles_n, tiles_nt);
+        const GemmTile tile = gemm_tile(t, tiles_m, tiles_n, tiles_nt, p.panel);
         const int m0 = tile.tm * kTileM + int(cta_rank) * 128;
         const int b_rows = tile.aux ? p.aux_n / CG : S::kBRows;
         const int n0 = tile.aux ? int(cta_rank) * b_rows : tile.tn * kGemmTileN + int(cta_rank) * b_rows;
         const CUtensorMap* mb = tile.aux ? &tmap_p : &tmap_b;
         const bool b_mn = tile.aux ? false : p.b_mn != 0;
         const uint32_t stage_tx = uint32_t(CG) * uint32_t(S::kABytes + b_rows * kGemmBlockK * 2);
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
-          const int s = int(it % kStages);
-          if (!mbar_wait_budget(&empty_bar[s], (uint32_t(it / kStages) & 1u) ^ 1u, p.wait_cycles)) {
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait_budget(&empty_bar[stage], phase ^ 1u, p.wait_cycles)) {
             atomicCAS(status, kStatusOk, kStatusTimeoutProducer);
             ok = false;
             break;
           }
-          const uint32_t a_dst = smem_u32(tiles + s * S::kStageBytes);
-          const uint32_t b_dst = a_dst + S::kABytes;
-          uint32_t bar = smem_u32(&full_bar[s]);
-          if (leader) mbar_expect_tx(&full_bar[s], stage_tx);
+          const uint32_t a_dst = smem_u32(tiles + stage * S::kStageBytes);
+          uint32_t bar = smem_u32(&full_bar[stage]);
+          if (is_a && leader) mbar_expect_tx(&full_bar[stage], stage_tx);
           if constexpr (CG == 2) bar = map_to_cta(bar, 0);
           const int k0 = kb * kGemmBlockK;
-          if (p.a_mn) {
-#pragma unroll
-            for (int b = 0; b < 2; ++b)
-              tma_load_nd<CG>(a_dst + b * 8192, &tmap_a, bar, m0 + b * 64, k0, tile.batch, three_d);
+          if (is_a) {
+            load_operand<CG>(a_dst, &tmap_a, bar, p.a_mn != 0, p.a_blocked != 0, 128, m0, k0, tile.batch, three_d);
           } else {
-            tma_load_nd<CG>(a_dst, &tmap_a, bar, k0, m0, tile.batch, three_d);
+            load_operand<CG>(a_dst + S::kABytes, mb, bar, b_mn, p.b_blocked != 0, b_rows, n0, k0, tile.batch,
+                             three_d && !tile.aux);
           }
-          if (b_mn) {
-            for (int b = 0; b < b_rows / 64; ++b)
-              tma_load_nd<CG>(b_dst + b * 8192, mb, bar, n0 + b * 64, k0, tile.batch, three_d);
-          } else {
-            tma_load_nd<CG>(b_dst, mb, bar, k0, n0, tile.aux ? 0 : tile.batch, three_d && !tile.aux);
+          ++issued;
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
           }
         }
       }
       if (!ok) {
         // Give-up path: loads already issued may still be landing in this CTA's shared memory.
-        // The leader waits (bounded) for the stages it armed; the peer, whose loads signal the
-        // leader's barriers, waits out a fixed interval far above a TMA round trip.
-        if (leader) {
-          for (long j = it > kStages ? it - kStages : 0; j < it; ++j)
-            mbar_wait_budget(&full_bar[j % kStages], uint32_t(j / kStages) & 1u, p.wait_cycles);
-        } else {
-          const long long start = clock64();
-          while (clock64() - start < 200000) {
-          }
+        // Wait out a fixed interval far above a TMA round trip before heading for the exit.
+        const long long start = clock64();
+        while (clock64() - start < 400000) {
         }
       }
+      (void)issued;
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer (leader CTA only) ----------------
     if (leader) {
-      long it = 0;
+      uint32_t stage = 0, phase = 0;
       long local_tile = 0;
       bool ok = true;
+      long long g_start = 0, g_wait = 0;
+      if (p.trace != nullptr && lane == 0) asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g_start));
       for (long t = group; t < num_tiles && ok; t += num_groups, ++local_tile) {
-        const GemmTile tile = gemm_tile(t, tiles_m, tiles_n, tiles_nt);
+        const GemmTile tile = gemm_tile(t, tiles_m, tiles_n, tiles_nt, p.panel);
         const int as = int(local_tile & 1);
         const uint32_t use = uint32_t(local_tile >> 1);
         // Wait until the epilogue has drained this accumulator stage (first use: free).
+        const bool tracing = p.trace != nullptr && lane == 0 && group == 0;
+        const bool tracing_all = p.trace != nullptr && lane == 0;
+        const long long t_begin = tracing ? clock64() : 0;
+        long long full_wait = 0;
         ok = mbar_wait_budget(&tmem_empty_bar[as], (use & 1u) ^ 1u, p.wait_cycles);
+        const long long t_acc_free = tracing ? clock64() : 0;
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) {
           if (lane == 0) atomicCAS(status, kStatusOk, kStatusTimeoutMma);
@@ -347,9 +372,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         const int n_inst = tile.aux ? p.aux_n : kGemmTileN;
         const uint32_t idesc = make_idesc_f16(kTileM, n_inst, FMT, p.a_mn, b_mn ? 1 : 0);
         const uint32_t d_addr = tmem_base + uint32_t(as) * kGemmTileN;
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
-          const int s = int(it % kStages);
-          ok = mbar_wait_budget(&full_bar[s], uint32_t(it / kStages) & 1u, p.wait_cycles);
+        const uint32_t a_step = p.a_mn ? 2048u : 32u, b_step = b_mn ? 2048u : 32u;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          const long long w0 = tracing_all ? clock64() : 0;
+          ok = mbar_wait_budget(&full_bar[stage], phase, p.wait_cycles);
+          if (tracing_all) full_wait += clock64() - w0;
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) {
             if (lane == 0) atomicCAS(status, kStatusOk, kStatusTimeoutMma);
@@ -357,25 +384,46 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           }
           tc_fence_after();
           if (lane == 0) {
-            const uint32_t a_addr = smem_u32(tiles + s * S::kStageBytes);
+            const uint32_t a_addr = smem_u32(tiles + stage * S::kStageBytes);
             const uint32_t b_addr = a_addr + S::kABytes;
+            const uint64_t da0 = p.a_mn ? make_mnmajor_sw128_desc(a_addr, 8192) : make_kmajor_sw128_desc(a_addr);
+            const uint64_t db0 = b_mn ? make_mnmajor_sw128_desc(b_addr, 8192) : make_kmajor_sw128_desc(b_addr);
 #pragma unroll
             for (int k = 0; k < kGemmBlockK / 16; ++k) {
-              const uint64_t da = p.a_mn ? make_mnmajor_sw128_desc(a_addr + k * 2048, 8192)
-                                         : make_kmajor_sw128_desc(a_addr + k * 32);
-              const uint64_t db = b_mn ? make_mnmajor_sw128_desc(b_addr + k * 2048, 8192)
-                                       : make_kmajor_sw128_desc(b_addr + k * 32);
-              umma_f16_cg<CG>(d_addr, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+              // The start-address field counts 16-byte units; the steps keep it inside the stage.
+              umma_f16_cg<CG>(d_addr, da0 + uint64_t((a_step * k) >> 4), db0 + uint64_t((b_step * k) >> 4), idesc,
+                              (kb | k) != 0 ? 1u : 0u);
             }
-            umma_commit_cg<CG>(&empty_bar[s]);
+            umma_commit_cg<CG>(&empty_bar[stage]);
           }
           __syncwarp();
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
         }
         if (ok && lane == 0) umma_commit_cg<CG>(&tmem_full_bar[as]);
+        if (tracing) {
+          long long* tr = p.trace + local_tile * 8;
+          tr[0] = t_begin;
+          tr[1] = t_acc_free;
+          tr[2] = clock64();
+          tr[3] = full_wait;
+        }
+        g_wait += full_wait;
         __syncwarp();
       }
+      if (p.trace != nullptr && lane == 0) {
+        long long g_end;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(g_end));
+        long long* tr = p.trace + 512 + group * 4;
+        tr[0] = g_start;
+        tr[1] = g_end;
+        tr[2] = local_tile;
+        tr[3] = g_wait;
+      }
     }
-  } else {
+  } else if (warp < 6) {
     // ---------------- epilogue ----------------
     const int quad = warp & 3;
     const int row_in_tile = quad * 32 + lane;
@@ -388,15 +436,18 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       if constexpr (CG == 2) empty_addr[a] = map_to_cta(empty_addr[a], 0);
     }
     for (long t = group; t < num_tiles && ok; t += num_groups, ++local_tile) {
-      const GemmTile tile = gemm_tile(t, tiles_m, tiles_n, tiles_nt);
+      const GemmTile tile = gemm_tile(t, tiles_m, tiles_n, tiles_nt, p.panel);
       const int as = int(local_tile & 1);
       const uint32_t use = uint32_t(local_tile >> 1);
+      const bool tracing = p.trace != nullptr && group == 0 && leader && warp == 2 && lane == 0;
+      const long long e0 = tracing ? clock64() : 0;
       ok = mbar_wait_budget(&tmem_full_bar[as], use & 1u, p.wait_cycles);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) {
         if (lane == 0) atomicCAS(status, kStatusOk, kStatusTimeoutEpilogue);
         break;
       }
+      const long long e1 = tracing ? clock64() : 0;
       tc_fence_after();
       const long row = long(tile.tm) * kTileM + long(cta_rank) * 128 + row_in_tile;
       const bool row_ok = row < p.M;
@@ -411,6 +462,60 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             for (int i = 0; i < 16; i += 4)
               *reinterpret_cast<float4*>(dst + c + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
           }
+        }
+      } else if (!OUT32 && p.tma_store) {
+        // Stage this warp's 32 rows x 256 columns in shared memory (four 64-column slabs in the
+        // 128-byte swizzle) and hand them to TMA stores, which clip at the matrix edges.
+        const int col0 = tile.tn * kGemmTileN;
+        const int n_valid = p.N - col0 < kGemmTileN ? p.N - col0 : kGemmTileN;
+        uint8_t* stg = staging + quad * 16384;
+        if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // previous tile's stores
+        __syncwarp();
+        const uint32_t stg_row = smem_u32(stg) + uint32_t(lane) * 128u;
+#pragma unroll 1
+        for (int c = 0; c < kGemmTileN; c += 32) {
+          if (c >= n_valid) break;  // uniform over the CTA
+          float v[32];
+          tmem_ld_32x32(t_addr + c, v);
+          if (p.bias != nullptr) {
+            const int nv = n_valid - c < 32 ? n_valid - c : 32;
+            if (p.bias_f32) {
+              const float* b = reinterpret_cast<const float*>(p.bias) + col0 + c;
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                if (i < nv) v[i] += __ldg(b + i);
+            } else {
+              const InT* b = reinterpret_cast<const InT*>(p.bias) + col0 + c;
+#pragma unroll
+              for (int i = 0; i < 32; ++i)
+                if (i < nv) v[i] += to_float<InT>(b[i]);
+            }
+          }
+          const uint32_t slab = stg_row + uint32_t(c >> 6) * 4096u;
+          const uint32_t chunk0 = uint32_t(c & 63) >> 3;  // 16-byte chunk of the 128-byte row: 0 or 4
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            union { uint4 u; InT h[8]; } o;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) o.h[e] = from_float<InT>(v[j * 8 + e]);
+            const uint32_t addr = slab + (((chunk0 + j) ^ (uint32_t(lane) & 7u)) << 4);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(o.u.x), "r"(o.u.y), "r"(o.u.z),
+                         "r"(o.u.w)
+                         : "memory");
+          }
+        }
+        fence_proxy_async();
+        __syncwarp();
+        const int row0 = tile.tm * kTileM + int(cta_rank) * 128 + quad * 32;
+        if (lane == 0 && row0 < p.M) {
+          for (int b = 0; b < 4; ++b) {
+            if (b * 64 >= n_valid) break;
+            asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
+                             reinterpret_cast<uint64_t>(&tmap_d)),
+                         "r"(smem_u32(stg) + uint32_t(b) * 4096u), "r"(col0 + b * 64), "r"(row0)
+                         : "memory");
+          }
+          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
         }
       } else {
         const int col0 = tile.tn * kGemmTileN;
@@ -489,6 +594,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           }
         }
       }
+      if (tracing) {
+        long long* tr = p.trace + local_tile * 8;
+        tr[4] = e0;
+        tr[5] = e1;
+        tr[6] = clock64();
+      }
       // All reads of this accumulator stage by this warp are complete (tcgen05.wait::ld).
       tc_fence_before();
       __syncwarp();
@@ -499,6 +610,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     }
   }
 
+  if (warp >= 2 && warp < 6 && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
   tc_fence_before();
   __syncthreads();
   if constexpr (CG == 2) cluster_sync_all();  // the peer may still be reading this CTA's operands

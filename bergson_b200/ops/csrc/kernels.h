@@ -32,6 +32,16 @@ int bgn_tn_gemm(const void* a, const void* b, float* c, long M, int N, int K, lo
 int bgn_tn_gemm_gathered(const void* a, const void* const* b, int world, float* c, long M, int N, int K,
                          long ldc, int fmt, int* status, cudaStream_t stream);
 
+// acc[n, col_off + i*p + j] = sum_s g_proj[n*S + s, i] * a_proj[n*S + s, j]  (overwrites; fixed
+// summation order).  g_proj / a_proj: fp32 [N*S, ldp] with p <= ldp meaningful columns;
+// p in {8, 16, 32, 64}.
+int bgn_proj_contract(const float* g_proj, const float* a_proj, float* acc, int N, int S, int p, int ldp,
+                      long ld, long col_off, cudaStream_t stream);
+
+// out[r, col_off + i*p + j] = g_proj[t, i] * a_proj[t, j] with t = token_index[r], r < rows.
+int bgn_proj_token_rows(const float* g_proj, const float* a_proj, const long* token_index, float* out,
+                        long rows, int p, int ldp, long ld, long col_off, cudaStream_t stream);
+
 // acc fp32 [N, D] -> out rows (type code `out_type`) with clamp to [lo, hi]; if unit_norm,
 // every row is divided by max(||row||, eps) computed on the rounded values.  Row r goes to
 // out + row_index[r] * out_ld (row_index == nullptr means r).

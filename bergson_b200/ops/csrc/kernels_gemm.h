@@ -35,7 +35,10 @@ struct BgnGemmArgs {
   int sq_accumulate;
   int cta_group;
   int sm_count;
+  int panel;  // tile columns per rasterisation panel; <= 0 picks one from K
   long long wait_cycles;
+  int no_tma_store;  // 1: write 16-bit outputs from registers instead of through TMA stores
+  long long* trace;  // optional device buffer for per-tile timestamps of the first CTA group (debugging aid)
 };
 
 int bgn_gemm(const BgnGemmArgs* args, int* status, cudaStream_t stream);

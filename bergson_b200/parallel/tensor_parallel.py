@@ -62,7 +62,9 @@ def _shard_linear(lin: nn.Linear, dim: str, rank: int, size: int) -> nn.Linear:
     step = full // size
     lo, hi = rank * step, (rank + 1) * step
     w = lin.weight.data[lo:hi] if dim == "out" else lin.weight.data[:, lo:hi]
-    new = nn.Linear(w.shape[1], w.shape[0], bias=False, device=w.device, dtype=w.dtype)
+    from ..ops.linear import Linear
+
+    new = Linear(w.shape[1], w.shape[0], bias=False, device=w.device, dtype=w.dtype)
     new.weight = nn.Parameter(w.clone().contiguous(), requires_grad=lin.weight.requires_grad)
     if lin.bias is not None:
         raise ValueError("tensor parallelism supports bias-free projections only")
