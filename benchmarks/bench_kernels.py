@@ -164,12 +164,14 @@ def bench_linear_gemm(small: bool, iters: int):
         ms = _time_interleaved({
             "pair": lambda: native.gemm(a, b, False, b_mn, d, False, None, False, None, 2),
             "pair_proj": lambda: native.gemm(a, b, False, b_mn, d, False, None, False, p, 2),
-            "pair_regstore": lambda: native.gemm(a, b, False, b_mn, d, False, None, False, None, 2, False, 0, None, 0, None, True),
+            "wide": lambda: native.gemm(a, b, False, b_mn, d, False, None, False, None, 2, wide=True),
+            "wide_proj": lambda: native.gemm(a, b, False, b_mn, d, False, None, False, p, 2, wide=True),
             "single": lambda: native.gemm(a, b, False, b_mn, d, False, None, False, None, 1),
             "torch": (lambda: torch.matmul(a, b, out=d)) if b_mn else (lambda: torch.matmul(a, b.T, out=d)),
         })
-        out.append(dict(kernel=f"gemm {name}", shape=[M, N, K], ms=ms["pair"], ms_with_projection=ms["pair_proj"],
-                        ms_register_store=ms["pair_regstore"], ms_single_cta=ms["single"], torch_ms=ms["torch"],
+        out.append(dict(kernel=f"gemm {name}", shape=[M, N, K], ms=ms["wide"], ms_with_projection=ms["wide_proj"],
+                        ms_pair=ms["pair"], ms_pair_with_projection=ms["pair_proj"], ms_single_cta=ms["single"],
+                        torch_ms=ms["torch"],
                         bytes=(M * K + N * K + M * N) * 2, flops=2 * M * N * K))
     return out
 

@@ -121,6 +121,7 @@ class _FusedTap:
             n, s = int(lead_shape[0]), int(lead_shape[1])
             native.proj_contract(g_proj, a_proj, acc, n, s, p, off)
         c._fused_written.add(self.name)
+        c._tap_calls += 1
 
 
 @dataclass
@@ -155,6 +156,7 @@ class HookCollectorBase(ContextDecorator, ABC):
         self._fused_enabled = False
         self._tap_dim_ok = False
         self._hook_fused_ok = False
+        self._tap_calls = 0  # modules x batches collected through GEMM taps (diagnostic)
         self._row_acc: Tensor | None = None
         self._col_offsets: dict[str, int] = {}
         self._fused_mats: dict = {}
@@ -493,7 +495,7 @@ class HookCollectorBase(ContextDecorator, ABC):
         return self._fused_mats[key]
 
     def _tap_accepts(self, module: nn.Module, x: Tensor) -> bool:
-        if not self._fused_enabled or not torch.is_grad_enabled() or module._collect_bias:
+        if not self._fused_enabled or module._collect_bias:
             return False
         if x.dtype not in (torch.bfloat16, torch.float16) or x.ndim != 3 or x.shape[0] != getattr(self, "_fused_n", -1):
             return False

@@ -308,7 +308,7 @@ void cov_syrk(at::Tensor x, std::vector<int64_t> dst_ptrs, std::vector<int64_t> 
 std::vector<at::Tensor> gemm(at::Tensor a, at::Tensor b, bool a_mn, bool b_mn, c10::optional<at::Tensor> out,
                              bool out_f32, c10::optional<at::Tensor> bias, bool accumulate,
                              c10::optional<at::Tensor> aux_p, int64_t cta_group, bool sq_accumulate,
-                             int64_t wait_cycles, c10::optional<at::Tensor> status, int64_t panel, c10::optional<at::Tensor> trace, bool no_tma_store) {
+                             int64_t wait_cycles, c10::optional<at::Tensor> status, int64_t panel, c10::optional<at::Tensor> trace, bool no_tma_store, bool wide) {
   TORCH_CHECK(a.is_cuda() && b.is_cuda() && a.scalar_type() == b.scalar_type(), "gemm: CUDA operands of one dtype");
   TORCH_CHECK((a.dim() == 2 || a.dim() == 3) && a.dim() == b.dim() && a.stride(-1) == 1 && b.stride(-1) == 1,
               "gemm: 2-D or 3-D operands with contiguous last dimension");
@@ -366,6 +366,7 @@ std::vector<at::Tensor> gemm(at::Tensor a, at::Tensor b, bool a_mn, bool b_mn, c
   g.wait_cycles = wait_cycles;
   g.panel = (int)panel;
   g.no_tma_store = no_tma_store;
+  g.wide = wide;
   if (trace.has_value()) {
     TORCH_CHECK(trace->is_cuda() && trace->scalar_type() == at::kLong && trace->is_contiguous());
     g.trace = reinterpret_cast<long long*>(trace->data_ptr<int64_t>());
@@ -434,7 +435,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm", &gemm, py::arg("a"), py::arg("b"), py::arg("a_mn") = false, py::arg("b_mn") = false,
         py::arg("out") = py::none(), py::arg("out_f32") = false, py::arg("bias") = py::none(),
         py::arg("accumulate") = false, py::arg("aux_p") = py::none(), py::arg("cta_group") = 2,
-        py::arg("sq_accumulate") = false, py::arg("wait_cycles") = 0, py::arg("status") = py::none(), py::arg("panel") = 0, py::arg("trace") = py::none(), py::arg("no_tma_store") = false);
+        py::arg("sq_accumulate") = false, py::arg("wait_cycles") = 0, py::arg("status") = py::none(), py::arg("panel") = 0, py::arg("trace") = py::none(), py::arg("no_tma_store") = false, py::arg("wide") = false);
   m.def("proj_contract", &proj_contract);
   m.def("proj_token_rows", &proj_token_rows);
   m.def("wait_probe", &wait_probe);

@@ -1,6 +1,7 @@
 // Host side of the persistent tcgen05 GEMM (gemm.cuh): tensor maps for the four operand
 // layouts, grid sizing, and the cluster launch of the CTA-pair variant.
 #include "gemm.cuh"
+#include "gemm_wide.cuh"
 
 #include <mutex>
 
@@ -85,6 +86,31 @@ static cudaError_t launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, con
   return cudaLaunchKernelEx(&cfg, kern, ta, tb, tp, td, p, status);
 }
 
+template <int FMT, bool OUT32>
+static cudaError_t launch_gemm_wide(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tp,
+                                    const GemmParams& p, int grid, int* status, cudaStream_t stream) {
+  auto kern = gemm_wide_kernel<FMT, OUT32>;
+  static bool attr_set = false;  // one flag per instantiation
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kWideSmemBytes);
+    if (e != cudaSuccess) return e;
+    attr_set = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid, 1, 1);
+  cfg.blockDim = dim3(kWideThreads, 1, 1);
+  cfg.dynamicSmemBytes = kWideSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, ta, tb, tp, p, status);
+}
+
 }  // namespace bgn
 
 using namespace bgn;
@@ -146,7 +172,8 @@ extern "C" int bgn_gemm(const BgnGemmArgs* a, int* status, cudaStream_t stream) 
   p.a_blocked = a_blocked ? 1 : 0;
   p.b_blocked = b_blocked ? 1 : 0;
 
-  const int tile_m = 128 * cg;
+  const bool wide = cg == 2 && a->wide;
+  const int tile_m = wide ? kWideTileM : 128 * cg;
   const long tiles_m = (a->M + tile_m - 1) / tile_m;
   const long tiles_n = (a->N + kGemmTileN - 1) / kGemmTileN + (a->aux_n > 0 ? 1 : 0);
   const long tiles = tiles_m * tiles_n * a->batch;
@@ -163,7 +190,12 @@ extern "C" int bgn_gemm(const BgnGemmArgs* a, int* status, cudaStream_t stream) 
   const int grid = int(groups) * cg;
   cudaError_t e;
   const bool bf = a->fmt == 1;
-  if (cg == 2) {
+  if (wide) {
+    e = a->out_f32 ? (bf ? launch_gemm_wide<1, true>(ta, tb, tp, p, grid, status, stream)
+                         : launch_gemm_wide<0, true>(ta, tb, tp, p, grid, status, stream))
+                   : (bf ? launch_gemm_wide<1, false>(ta, tb, tp, p, grid, status, stream)
+                         : launch_gemm_wide<0, false>(ta, tb, tp, p, grid, status, stream));
+  } else if (cg == 2) {
     e = a->out_f32 ? (bf ? launch_gemm<2, 1, true>(ta, tb, tp, td, p, grid, status, stream)
                          : launch_gemm<2, 0, true>(ta, tb, tp, td, p, grid, status, stream))
                    : (bf ? launch_gemm<2, 1, false>(ta, tb, tp, td, p, grid, status, stream)

@@ -1,0 +1,346 @@
+// Wide form of the persistent tcgen05 GEMM: a CTA pair owns a 512 x 256 output tile.
+//
+// Each CTA holds two 128-row blocks of A per stage (rows r and r + 256 of the tile, r being the
+// CTA's 128-row share of a 256-row MMA) and its 128-row half of B, so that every B slab in
+// shared memory feeds two cta_group::2 MMAs (M = 256, N = 256) instead of one.  Per flop that
+// is a quarter less shared-memory fill traffic than the 256 x 256 pair tile of gemm.cuh, which
+// is what limits that kernel's tensor-pipe utilisation.  The price is TMEM: the two 128 x 256
+// fp32 accumulators fill all 512 columns, so there is one accumulator stage and the epilogue of
+// a tile overlaps only the first k-block of the next one.  Eight epilogue warps (two per TMEM
+// lane quadrant, each taking half of the columns) and 32-byte stores keep that epilogue short;
+// the two row blocks are released to the MMA warp separately.
+//
+// Warp roles: 0 = A producer, 1 = MMA issuer (leader CTA), 2..9 = epilogue, 10 = B producer.
+// Operand layouts, the aux (projection) tile column, bias, accumulation, the batched
+// sum-of-squares form and the bounded waits are those of gemm.cuh.
+#pragma once
+
+#include "gemm.cuh"
+
+namespace bgn {
+
+constexpr int kWideThreads = 352;
+constexpr int kWideTileM = 512;     // rows per CTA pair
+constexpr int kWideABytes = 2 * 128 * kGemmBlockK * 2;   // two row blocks
+constexpr int kWideBBytes = 128 * kGemmBlockK * 2;
+constexpr int kWideStageBytes = kWideABytes + kWideBBytes;  // 48 KB
+constexpr int kWideStages = 4;
+constexpr int kWideSmemBytes = kWideStages * kWideStageBytes + 1024 + 512;
+
+// 32 bytes per thread in one instruction: a full sector per row.
+__device__ __forceinline__ void st_global_v8(void* ptr, const uint32_t (&r)[8]) {
+  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(ptr), "r"(r[0]), "r"(r[1]), "r"(r[2]),
+               "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+               : "memory");
+}
+
+template <int FMT, bool OUT32>
+__global__ void __launch_bounds__(kWideThreads, 1)
+gemm_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                 const __grid_constant__ CUtensorMap tmap_p, GemmParams p, int* status) {
+  constexpr int CG = 2;
+  using InT = typename std::conditional<FMT == 1, __nv_bfloat16, __half>::type;
+  constexpr int kStages = kWideStages;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(tiles + kStages * kWideStageBytes);
+  uint64_t* empty_bar = full_bar + kStages;
+  uint64_t* tmem_full_bar = empty_bar + kStages;   // [1]
+  uint64_t* tmem_empty_bar = tmem_full_bar + 1;    // [2]: one per row block
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty_bar + 2);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t cta_rank = cluster_ctarank();
+  const bool leader = cta_rank == 0;
+  const int group = blockIdx.x / CG, num_groups = gridDim.x / CG;
+
+  const int tiles_m = (p.M + kWideTileM - 1) / kWideTileM;
+  const int tiles_n = (p.N + kGemmTileN - 1) / kGemmTileN;
+  const int tiles_nt = tiles_n + (p.aux_n > 0 ? 1 : 0);
+  const long num_tiles = long(tiles_m) * tiles_nt * p.batch;
+  const int num_kb = (p.K + kGemmBlockK - 1) / kGemmBlockK;
+  const bool three_d = p.batch > 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    mbar_init(tmem_full_bar, 1);
+    mbar_init(&tmem_empty_bar[0], 8 * CG);  // one arrival per epilogue warp of every CTA
+    mbar_init(&tmem_empty_bar[1], 8 * CG);
+    fence_barrier_init();
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+    if (p.aux_n > 0) tma_prefetch_desc(&tmap_p);
+  }
+  if (warp == 1) tmem_alloc_cg<CG>(tmem_slot, 512);
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0 || warp == 10) {
+    if (lane == 0) {
+      // ---------------- producers ----------------
+      const bool is_a = warp == 0;
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      for (long t = group; t < num_tiles && ok; t += num_groups) {
+        const GemmTile tile = gemm_tile(t, tiles_m, tiles_n, tiles_nt, p.panel);
+        const int m0 = tile.tm * kWideTileM + int(cta_rank) * 128;  // row block 1 starts 256 rows further
+        const int b_rows = tile.aux ? p.aux_n / CG : 128;
+        const int n0 = tile.aux ? int(cta_rank) * b_rows : tile.tn * kGemmTileN + int(cta_rank) * b_rows;
+        const CUtensorMap* mb = tile.aux ? &tmap_p : &tmap_b;
+        const bool b_mn = tile.aux ? false : p.b_mn != 0;
+        const uint32_t stage_tx = uint32_t(CG) * uint32_t(kWideABytes + b_rows * kGemmBlockK * 2);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait_budget(&empty_bar[stage], phase ^ 1u, p.wait_cycles)) {
+            atomicCAS(status, kStatusOk, kStatusTimeoutProducer);
+            ok = false;
+            break;
+          }
+          const uint32_t a_dst = smem_u32(tiles + stage * kWideStageBytes);
+          if (is_a && leader) mbar_expect_tx(&full_bar[stage], stage_tx);
+          const uint32_t bar = map_to_cta(smem_u32(&full_bar[stage]), 0);
+          const int k0 = kb * kGemmBlockK;
+          if (is_a) {
+            load_operand<CG>(a_dst, &tmap_a, bar, p.a_mn != 0, p.a_blocked != 0, 128, m0, k0, tile.batch, three_d);
+            load_operand<CG>(a_dst + 16384, &tmap_a, bar, p.a_mn != 0, p.a_blocked != 0, 128, m0 + 256, k0,
+                             tile.batch, three_d);
+          } else {
+            load_operand<CG>(a_dst + kWideABytes, mb, bar, b_mn, p.b_blocked != 0, b_rows, n0, k0, tile.batch,
+                             three_d && !tile.aux);
+          }
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+      if (!ok) {
+        // Give-up path: wait out in-flight loads (far above a TMA round trip) before the exit.
+        const long long start = clock64();
+        while (clock64() - start < 400000) {
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer (leader CTA only) ----------------
+    if (leader) {
+      uint32_t stage = 0, phase = 0;
+      long local_tile = 0;
+      bool ok = true;
+      for (long t = group; t < num_tiles && ok; t += num_groups, ++local_tile) {
+        const GemmTile tile = gemm_tile(t, tiles_m, tiles_n, tiles_nt, p.panel);
+        const uint32_t acc_parity = (uint32_t(local_tile) & 1u) ^ 1u;  // first use: free
+        ok = mbar_wait_budget(&tmem_empty_bar[0], acc_parity, p.wait_cycles);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) {
+          if (lane == 0) atomicCAS(status, kStatusOk, kStatusTimeoutMma);
+          break;
+        }
+        tc_fence_after();
+        const bool b_mn = tile.aux ? false : p.b_mn != 0;
+        const int n_inst = tile.aux ? p.aux_n : kGemmTileN;
+        const uint32_t idesc = make_idesc_f16(256, n_inst, FMT, p.a_mn, b_mn ? 1 : 0);
+        const uint32_t a_step = p.a_mn ? 2048u : 32u, b_step = b_mn ? 2048u : 32u;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          ok = mbar_wait_budget(&full_bar[stage], phase, p.wait_cycles);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) {
+            if (lane == 0) atomicCAS(status, kStatusOk, kStatusTimeoutMma);
+            break;
+          }
+          tc_fence_after();
+          const uint32_t a_addr = smem_u32(tiles + stage * kWideStageBytes);
+          const uint32_t b_addr = a_addr + kWideABytes;
+          const uint64_t da0 = p.a_mn ? make_mnmajor_sw128_desc(a_addr, 8192) : make_kmajor_sw128_desc(a_addr);
+          const uint64_t da1 = da0 + uint64_t(16384 >> 4);
+          const uint64_t db0 = b_mn ? make_mnmajor_sw128_desc(b_addr, 8192) : make_kmajor_sw128_desc(b_addr);
+          if (lane == 0) {
+#pragma unroll
+            for (int k = 0; k < kGemmBlockK / 16; ++k)
+              umma_f16_cg<CG>(tmem_base, da0 + uint64_t((a_step * k) >> 4), db0 + uint64_t((b_step * k) >> 4), idesc,
+                              (kb | k) != 0 ? 1u : 0u);
+          }
+          if (kb == 0) {
+            // The second row block's accumulator may still be draining from the previous tile.
+            ok = mbar_wait_budget(&tmem_empty_bar[1], acc_parity, p.wait_cycles);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) {
+              if (lane == 0) atomicCAS(status, kStatusOk, kStatusTimeoutMma);
+              break;
+            }
+            tc_fence_after();
+          }
+          if (lane == 0) {
+#pragma unroll
+            for (int k = 0; k < kGemmBlockK / 16; ++k)
+              umma_f16_cg<CG>(tmem_base + kGemmTileN, da1 + uint64_t((a_step * k) >> 4),
+                              db0 + uint64_t((b_step * k) >> 4), idesc, (kb | k) != 0 ? 1u : 0u);
+            umma_commit_cg<CG>(&empty_bar[stage]);
+          }
+          __syncwarp();
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (ok && lane == 0) umma_commit_cg<CG>(tmem_full_bar);
+        __syncwarp();
+      }
+    }
+  } else if (warp < 10) {
+    // ---------------- epilogue: 8 warps, (lane quadrant) x (column half) ----------------
+    const int quad = warp & 3;
+    const int half = (warp - 2) >> 2;  // 0: columns 0..127 of each row block, 1: columns 128..255
+    long local_tile = 0;
+    bool ok = true;
+    uint32_t empty_addr[2];
+#pragma unroll
+    for (int a = 0; a < 2; ++a) empty_addr[a] = map_to_cta(smem_u32(&tmem_empty_bar[a]), 0);
+    for (long t = group; t < num_tiles && ok; t += num_groups, ++local_tile) {
+      const GemmTile tile = gemm_tile(t, tiles_m, tiles_n, tiles_nt, p.panel);
+      ok = mbar_wait_budget(tmem_full_bar, uint32_t(local_tile) & 1u, p.wait_cycles);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) {
+        if (lane == 0) atomicCAS(status, kStatusOk, kStatusTimeoutEpilogue);
+        break;
+      }
+      tc_fence_after();
+      const int col0 = tile.tn * kGemmTileN;
+      const int n_valid = tile.aux ? 0 : (p.N - col0 < kGemmTileN ? p.N - col0 : kGemmTileN);
+#pragma unroll 1
+      for (int rb = 0; rb < 2; ++rb) {
+        const long row = long(tile.tm) * kWideTileM + rb * 256 + long(cta_rank) * 128 + quad * 32 + lane;
+        const bool row_ok = row < p.M;
+        const uint32_t t_addr = tmem_base + (uint32_t(quad * 32) << 16) + uint32_t(rb) * kGemmTileN;
+        if (tile.aux) {
+          if (half == 0) {
+            float* dst = p.aux_out + (long(tile.batch) * p.M + row) * p.aux_ld;
+            for (int c = 0; c < p.aux_n; c += 16) {
+              float v[16];
+              tmem_ld_32x16(t_addr + c, v);
+              if (row_ok) {
+#pragma unroll
+                for (int i = 0; i < 16; i += 4)
+                  *reinterpret_cast<float4*>(dst + c + i) = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+              }
+            }
+          }
+        } else {
+          const long d_row_off = long(tile.batch) * p.d_batch_stride + row * p.ldd + col0;
+#pragma unroll 1
+          for (int cc = 0; cc < 128; cc += 32) {
+            const int c = half * 128 + cc;
+            if (c >= n_valid) break;  // uniform over the warp
+            float v[32];
+            tmem_ld_32x32(t_addr + c, v);
+            if (!row_ok) continue;
+            const int nv = n_valid - c < 32 ? n_valid - c : 32;
+            if (p.bias != nullptr) {
+              if (p.bias_f32) {
+                const float* b = reinterpret_cast<const float*>(p.bias) + col0 + c;
+#pragma unroll
+                for (int i = 0; i < 32; ++i)
+                  if (i < nv) v[i] += __ldg(b + i);
+              } else {
+                const InT* b = reinterpret_cast<const InT*>(p.bias) + col0 + c;
+#pragma unroll
+                for (int i = 0; i < 32; ++i)
+                  if (i < nv) v[i] += to_float<InT>(b[i]);
+              }
+            }
+            if constexpr (OUT32) {
+              float* dst = reinterpret_cast<float*>(p.d) + d_row_off + c;
+              if (p.sq_accumulate) {
+                if (nv == 32 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+#pragma unroll
+                  for (int i = 0; i < 32; i += 4)
+                    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + i), "f"(v[i] * v[i]),
+                                 "f"(v[i + 1] * v[i + 1]), "f"(v[i + 2] * v[i + 2]), "f"(v[i + 3] * v[i + 3])
+                                 : "memory");
+                } else {
+#pragma unroll
+                  for (int i = 0; i < 32; ++i)
+                    if (i < nv) atomicAdd(dst + i, v[i] * v[i]);
+                }
+              } else if (nv == 32 && (reinterpret_cast<uintptr_t>(dst) & 31) == 0) {
+#pragma unroll
+                for (int i = 0; i < 32; i += 8) {
+                  uint32_t o[8];
+#pragma unroll
+                  for (int j = 0; j < 8; ++j) {
+                    float x = v[i + j];
+                    if (p.accumulate) x += dst[i + j];
+                    o[j] = __float_as_uint(x);
+                  }
+                  st_global_v8(dst + i, o);
+                }
+              } else {
+#pragma unroll
+                for (int i = 0; i < 32; ++i)
+                  if (i < nv) dst[i] = p.accumulate ? dst[i] + v[i] : v[i];
+              }
+            } else {
+              InT* dst = reinterpret_cast<InT*>(p.d) + d_row_off + c;
+              if (nv == 32 && (reinterpret_cast<uintptr_t>(dst) & 31) == 0) {
+#pragma unroll
+                for (int i = 0; i < 32; i += 16) {
+                  union { uint32_t u[8]; InT h[16]; } o;
+                  if (p.accumulate) {
+                    const uint4 lo = *reinterpret_cast<const uint4*>(dst + i);
+                    const uint4 hi = *reinterpret_cast<const uint4*>(dst + i + 8);
+                    o.u[0] = lo.x; o.u[1] = lo.y; o.u[2] = lo.z; o.u[3] = lo.w;
+                    o.u[4] = hi.x; o.u[5] = hi.y; o.u[6] = hi.z; o.u[7] = hi.w;
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) o.h[j] = from_float<InT>(to_float<InT>(o.h[j]) + v[i + j]);
+                  } else {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) o.h[j] = from_float<InT>(v[i + j]);
+                  }
+                  st_global_v8(dst + i, o.u);
+                }
+              } else if (nv == 32 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+#pragma unroll
+                for (int i = 0; i < 32; i += 8) {
+                  union { uint4 u; InT h[8]; } o;
+                  if (p.accumulate) {
+                    o.u = *reinterpret_cast<const uint4*>(dst + i);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) o.h[j] = from_float<InT>(to_float<InT>(o.h[j]) + v[i + j]);
+                  } else {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) o.h[j] = from_float<InT>(v[i + j]);
+                  }
+                  *reinterpret_cast<uint4*>(dst + i) = o.u;
+                }
+              } else {
+#pragma unroll
+                for (int i = 0; i < 32; ++i)
+                  if (i < nv) dst[i] = from_float<InT>(p.accumulate ? to_float<InT>(dst[i]) + v[i] : v[i]);
+              }
+            }
+          }
+        }
+        // This warp's reads of row block `rb` are complete: hand the block back to the MMA warp.
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(empty_addr[rb]);
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // the peer may still be reading this CTA's operands
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_cg<CG>(tmem_base, 512);
+  }
+}
+
+}  // namespace bgn

@@ -34,6 +34,7 @@ struct BgnGemmArgs {
   long a_batch_stride, b_batch_stride, d_batch_stride;
   int sq_accumulate;
   int cta_group;
+  int wide;  // with cta_group 2: 512 x 256 tiles per CTA pair (two row blocks per CTA, one accumulator stage)
   int sm_count;
   int panel;  // tile columns per rasterisation panel; <= 0 picks one from K
   long long wait_cycles;

@@ -117,6 +117,10 @@ def linear(x: Tensor, weight: Tensor, bias: Tensor | None = None, *, layout: str
            tap: ProjectionTap | None = None) -> Tensor:
     """``x @ weight^T + bias`` (``layout="oi"``) or ``x @ weight + bias`` (``layout="io"``)."""
     if gemm_eligible(x, weight) and (bias is None or bias.dtype in (x.dtype, torch.float32)):
+        # A tap only makes sense when a backward pass will follow (grad mode is off inside
+        # ``Function.forward``, so the decision is taken here).
+        if tap is not None and not (torch.is_grad_enabled() and x.requires_grad):
+            tap = None
         return _LinearFn.apply(x, weight, bias, layout, module, tap)
     if layout == "oi":
         return F.linear(x, weight, bias)

@@ -46,13 +46,50 @@ class TraceResult:
         return self._scores
 
 
+def merge_topk_across_ranks(scores: Tensor, indices: Tensor, k: int, *, largest: bool = True, group=None):
+    """Every rank contributes its local top-k (``[Q, k_r]`` scores and *global* row indices,
+    ``k_r`` may differ between ranks); all ranks receive the top-``k`` of the union.  Ties are
+    resolved by rank order, then by the local order, so the result is the same on every rank."""
+    import torch.distributed as dist
+
+    world = dist.get_world_size(group)
+    q = scores.shape[0]
+    fill = float("-inf") if largest else float("inf")
+    pad_s = scores.new_full((q, k), fill, dtype=torch.float32)
+    pad_i = indices.new_full((q, k), -1)
+    pad_s[:, : scores.shape[1]] = scores[:, :k].float()
+    pad_i[:, : indices.shape[1]] = indices[:, :k]
+    all_s = [torch.empty_like(pad_s) for _ in range(world)]
+    all_i = [torch.empty_like(pad_i) for _ in range(world)]
+    dist.all_gather(all_s, pad_s.contiguous(), group=group)
+    dist.all_gather(all_i, pad_i.contiguous(), group=group)
+    cat_s, cat_i = torch.cat(all_s, dim=1), torch.cat(all_i, dim=1)
+    valid = int((cat_i[0] >= 0).sum())
+    top_s, sel = torch.topk(cat_s, min(k, valid), dim=1, largest=largest)
+    return top_s.to(scores.dtype), cat_i.gather(1, sel)
+
+
 class Attributor:
     precondition: Literal["one-sided", "two-sided", "none"]
 
     def __init__(self, index_path, device: str = "cpu", dtype: torch.dtype = torch.float32, unit_norm: bool = False,
                  faiss_cfg: FaissConfig | None = None, inversion_cfg: InversionConfig | None = None,
-                 hessian_path=None, ev_correction: bool = False):
+                 hessian_path=None, ev_correction: bool = False, sharded: bool = False, group=None):
+        """``sharded=True`` (needs an initialised process group): every rank keeps a contiguous
+        slice of the store's rows resident; ``search`` runs on the slice and the per-rank top-k
+        lists are merged across ranks, so every rank returns the global result."""
         self.device, self.dtype, self.unit_norm = device, dtype, unit_norm
+        self.sharded = sharded
+        self.group = group
+        self.row_lo = 0
+        if sharded:
+            import torch.distributed as dist
+
+            if not dist.is_initialized():
+                raise RuntimeError("Attributor(sharded=True) needs torch.distributed to be initialised")
+            if faiss_cfg:
+                raise NotImplementedError("a sharded store uses exact search; omit faiss_cfg")
+            self.shard_rank, self.shard_world = dist.get_rank(group), dist.get_world_size(group)
         self.inversion_cfg = inversion_cfg or InversionConfig()
         self.faiss_index = None
         index_path = Path(index_path)
@@ -90,6 +127,11 @@ class Attributor:
 
         mm = load_gradients(index_path)
         self.N = len(mm)
+        if sharded:
+            from ..hessians.sharded_computation import shard_bounds
+
+            self.row_lo, hi = shard_bounds(self.N, self.shard_rank, self.shard_world)
+            mm = mm[self.row_lo : hi]
         self.store = numpy_to_tensor(np.ascontiguousarray(mm)).to(device=device, dtype=dtype)
         self.inv_norms: Tensor | None = None
         if unit_norm:
@@ -133,7 +175,11 @@ class Attributor:
         else:
             cols = torch.cat([torch.arange(*self.offsets[n], device=self.store.device) for n in use])
             store, q_rows = self.store[:, cols].contiguous(), torch.cat([q[n] for n in use], dim=1)
-        return attribution.topk_scores(store, q_rows.contiguous(), k, largest=not reverse, inv_norms=self.inv_norms)
+        scores, idx = attribution.topk_scores(store, q_rows.contiguous(), min(k, store.shape[0]), largest=not reverse,
+                                              inv_norms=self.inv_norms)
+        if not self.sharded:
+            return scores, idx
+        return merge_topk_across_ranks(scores, idx + self.row_lo, k, largest=not reverse, group=self.group)
 
     @contextmanager
     def trace(self, module: nn.Module, k: int | None, *, modules: set[str] | None = None,

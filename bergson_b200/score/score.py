@@ -59,11 +59,53 @@ def _make_split_hessian(hessians: dict[str, torch.Tensor], modules: list[str], d
     return transform
 
 
+def _gather_queries_ok(score_cfg: ScoreConfig, preprocess_cfg: PreprocessConfig, device, dtype, attribute_tokens) -> bool:
+    """Whether the queries can stay sharded over the ranks and be read through the fused
+    all-gather + score GEMM: CUDA ranks of one NVLink domain, 16-bit scoring, row-wise query
+    preprocessing only (no aggregation over queries, no index-side transform).  Every input is
+    the same on all ranks, so all ranks take the same branch."""
+    import os
+
+    import torch.distributed as dist
+
+    from ..parallel.peer import symmetric_memory_available
+
+    if not (dist.is_initialized() and dist.get_world_size() > 1) or torch.device(device).type != "cuda":
+        return False
+    if os.environ.get("BERGSON_B200_DISABLE_PEER") == "1" or not symmetric_memory_available():
+        return False
+    if dtype not in (torch.bfloat16, torch.float16) or attribute_tokens:
+        return False
+    if preprocess_cfg.aggregation != "none" or preprocess_cfg.normalize_aggregated_grad:
+        return False
+    return not (preprocess_cfg.hessian_path and preprocess_cfg.unit_normalize)
+
+
 def create_scorer(path: Path, data: Dataset, score_cfg: ScoreConfig, preprocess_cfg: PreprocessConfig, device,
-                  dtype, *, attribute_tokens: bool = False, query_range=None, num_queries_total=None) -> Scorer:
+                  dtype, *, attribute_tokens: bool = False, query_range=None, num_queries_total=None,
+                  shard_queries: bool = False) -> Scorer:
     """Load and preprocess the queries (precondition once unless the query store already
-    was, unit-normalise / aggregate unless already done) and set up the writer."""
-    query_grads, recorded = get_query_grads(score_cfg, query_range)
+    was, unit-normalise / aggregate unless already done) and set up the writer.
+
+    ``shard_queries`` (collective: all ranks pass the same value): each rank loads and
+    preprocesses only its slice of the query rows and the scorer reads the other ranks' slices
+    through peer memory inside the score GEMM."""
+    gather_info = None
+    if shard_queries:
+        import torch.distributed as dist
+
+        from ..hessians.sharded_computation import shard_bounds
+
+        with open(Path(score_cfg.query_path) / "info.json") as f:
+            n_all = json.load(f)["num_grads"]
+        base_lo, base_hi = query_range if query_range is not None else (0, n_all)
+        lo, hi = shard_bounds(base_hi - base_lo, dist.get_rank(), dist.get_world_size())
+        gather_info = (base_hi - base_lo, base_lo)
+        query_grads, recorded = get_query_grads(score_cfg, (base_lo + lo, base_lo + hi))
+        if recorded.aggregation != "none":
+            raise ValueError("sharded queries need a query store with one row per query (aggregation='none')")
+    else:
+        query_grads, recorded = get_query_grads(score_cfg, query_range)
     pre = load_preconditioner(
         preprocess_cfg.hessian_path, inversion_cfg=preprocess_cfg.inversion_cfg,
         power=-0.5 if preprocess_cfg.unit_normalize else -1.0, ev_correction=preprocess_cfg.ev_correction,
@@ -91,16 +133,23 @@ def create_scorer(path: Path, data: Dataset, score_cfg: ScoreConfig, preprocess_
     if query_range is not None and score_cfg.score != "individual":
         raise ValueError("query_batch_size requires score='individual': 'nearest' reduces over all queries, "
                          "which per-chunk passes would compute wrongly.")
-    n_q = len(query_grads[score_cfg.modules[0]])
+    n_q = len(query_grads[score_cfg.modules[0]]) if gather_info is None else gather_info[0]
     num_scores = 1 if score_cfg.score == "nearest" else (num_queries_total if num_queries_total is not None else n_q)
     if attribute_tokens:
         writer = MemmapTokenScoreWriter.from_dataset(path, data, num_scores, dtype=dtype)
     else:
         writer = MemmapSequenceScoreWriter(path, len(data), num_scores, dtype=dtype)
+    gathered = None
+    if gather_info is not None:
+        from .scorer import GatheredQueries
+
+        local = torch.cat([query_grads[m].to(device=device, dtype=torch.float32) for m in score_cfg.modules], dim=1)
+        gathered = GatheredQueries(local, gather_info[0], dtype)
     return Scorer(
         query_grads=query_grads, modules=score_cfg.modules, writer=writer, device=device, dtype=dtype,
         unit_normalize=preprocess_cfg.unit_normalize, score_mode=score_cfg.score, attribute_tokens=attribute_tokens,
         index_transform=index_transform, query_offset=query_range[0] if query_range is not None else 0,
+        gathered=gathered,
     )
 
 
@@ -120,10 +169,11 @@ def score_worker(rank: int, local_rank: int, world_size: int, index_cfg: IndexCo
     ranges = [None] if qbs is None or qbs >= num_queries else [
         (lo, min(lo + qbs, num_queries)) for lo in range(0, num_queries, qbs)
     ]
+    shard_queries = _gather_queries_ok(score_cfg, preprocess_cfg, device, dtype, index_cfg.attribute_tokens)
     for qr in ranges:
         scorer = create_scorer(index_cfg.partial_run_path, ds, score_cfg, preprocess_cfg, device=device, dtype=dtype,
                                attribute_tokens=index_cfg.attribute_tokens, query_range=qr,
-                               num_queries_total=num_queries)
+                               num_queries_total=num_queries, shard_queries=shard_queries)
         collect_gradients(model=model, data=ds, processor=processor, cfg=index_cfg, target_modules=target_modules,
                           attention_cfgs=attention_cfgs, batches=batches, scorer=scorer)
         scorer.writer.flush()

@@ -23,19 +23,27 @@ def _status():
     return torch.zeros(1, dtype=torch.int32, device="cuda")
 
 
-@pytest.mark.parametrize("cg", [1, 2])
+MODES = {"single": dict(cta_group=1), "pair": dict(cta_group=2), "wide": dict(cta_group=2, wide=True)}
+
+
+def _gemm(mode, a, b, a_mn, b_mn, out, out_f32, bias, accumulate, aux, sq, st):
+    from bergson_b200.ops import native
+
+    return native.gemm(a, b, a_mn, b_mn, out, out_f32, bias, accumulate, aux, sq_accumulate=sq, wait_cycles=WAIT,
+                       status=st, **MODES[mode])
+
+
+@pytest.mark.parametrize("cg", ["single", "pair", "wide"])
 @pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True), (True, False)])
 @pytest.mark.parametrize("M,N,K", [(256, 256, 64), (300, 520, 200), (1000, 776, 328), (129, 8, 72), (2048, 1280, 1024)])
 def test_gemm_layouts_and_ragged_shapes(cg, a_mn, b_mn, M, N, K):
-    from bergson_b200.ops import native
-
     if (a_mn and M % 8) or (b_mn and N % 8):
         pytest.skip("MN-major operands need a row stride that is a multiple of 8 elements")
     torch.manual_seed(M + N + K)
     a, b, ref = _operands(M, N, K, a_mn, b_mn)
     st = _status()
-    d32, _ = native.gemm(a, b, a_mn, b_mn, None, True, None, False, None, cg, False, WAIT, st)
-    d16, _ = native.gemm(a, b, a_mn, b_mn, None, False, None, False, None, cg, False, WAIT, st)
+    d32, _ = _gemm(cg, a, b, a_mn, b_mn, None, True, None, False, None, False, st)
+    d16, _ = _gemm(cg, a, b, a_mn, b_mn, None, False, None, False, None, False, st)
     torch.cuda.synchronize()
     assert int(st.item()) == 0
     scale = ref.abs().max()
@@ -43,43 +51,39 @@ def test_gemm_layouts_and_ragged_shapes(cg, a_mn, b_mn, M, N, K):
     assert float((d16.float() - ref).abs().max() / scale) < 1e-2
 
 
-@pytest.mark.parametrize("cg", [1, 2])
+@pytest.mark.parametrize("cg", ["single", "pair", "wide"])
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 def test_gemm_bias_accumulate_and_aux_output(cg, dtype):
-    from bergson_b200.ops import native
-
     torch.manual_seed(1)
     M, N, K = 1111, 1024, 520
     a, b, ref = _operands(M, N, K, False, True, dtype)
     bias = torch.randn(N, device="cuda", dtype=dtype)
     p = (torch.randn(32, K, device="cuda") / 4).to(dtype)
     st = _status()
-    d, aux = native.gemm(a, b, False, True, None, True, bias, False, p, cg, False, WAIT, st)
+    d, aux = _gemm(cg, a, b, False, True, None, True, bias, False, p, False, st)
     ref_b = ref + bias.float()
     assert float((d - ref_b).abs().max() / ref_b.abs().max()) < 1e-5
     ref_aux = a.float() @ p.float().T
     assert aux.shape == (M, 32) and float((aux - ref_aux).abs().max() / ref_aux.abs().max()) < 1e-5
     # accumulate into an existing output, in the 16-bit type as well
-    native.gemm(a, b, False, True, d, True, None, True, None, cg, False, WAIT, st)
+    _gemm(cg, a, b, False, True, d, True, None, True, None, False, st)
     assert float((d - (ref_b + ref)).abs().max() / ref.abs().max()) < 1e-5
     d16 = torch.ones(M, N, device="cuda", dtype=dtype)
-    native.gemm(a, b, False, True, d16, False, None, True, None, cg, False, WAIT, st)
+    _gemm(cg, a, b, False, True, d16, False, None, True, None, False, st)
     assert float((d16.float() - (ref + 1)).abs().max() / ref.abs().max()) < 2e-2
     assert int(st.item()) == 0
 
 
-@pytest.mark.parametrize("cg", [1, 2])
+@pytest.mark.parametrize("cg", ["single", "pair", "wide"])
 def test_gemm_batched_and_sum_of_squares(cg):
-    from bergson_b200.ops import native
-
     torch.manual_seed(2)
     nb, M, N, K = 5, 200, 264, 136
     a, b, ref = _operands(M, N, K, True, True, batch=nb)
     st = _status()
-    d, _ = native.gemm(a, b, True, True, None, True, None, False, None, cg, False, WAIT, st)
+    d, _ = _gemm(cg, a, b, True, True, None, True, None, False, None, False, st)
     assert d.shape == (nb, M, N) and float((d - ref).abs().max() / ref.abs().max()) < 1e-5
     sq = torch.zeros(M, N, device="cuda")
-    native.gemm(a, b, True, True, sq, True, None, False, None, cg, True, WAIT, st)
+    _gemm(cg, a, b, True, True, sq, True, None, False, None, True, st)
     want = ref.pow(2).sum(0)
     assert float((sq - want).abs().max() / want.abs().max()) < 1e-5
     assert int(st.item()) == 0
@@ -90,7 +94,7 @@ def test_gemm_is_bitwise_repeatable():
 
     torch.manual_seed(3)
     a, b, _ = _operands(3000, 1536, 2048, False, False)
-    outs = [native.gemm(a, b, False, False, None, False, None, False, None, 2, False, WAIT, _status())[0] for _ in range(3)]
+    outs = [_gemm("wide", a, b, False, False, None, False, None, False, None, False, _status())[0] for _ in range(3)]
     assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
 
 

@@ -62,9 +62,12 @@ def _collect(tmp, name, family, p, fused, tokens=False, dtype="fp32"):
     cfg = IndexConfig(run_path=str(tmp / name), projection_dim=p, token_batch_size=600, store_dtype=dtype,
                       fused_collection=fused, attribute_tokens=tokens)
     cfg.partial_run_path.mkdir(parents=True)
-    c = collect_gradients(model, ds, GradientProcessor(norms, projection_dim=p), cfg,
-                          batches=allocate_batches(ds["length"], 600))
+    batches_run = allocate_batches(ds["length"], 600)
+    c = collect_gradients(model, ds, GradientProcessor(norms, projection_dim=p), cfg, batches=batches_run)
     assert c._fused_enabled == fused
+    if fused:
+        # every in-tree layer went through its tap (projection side outputs of its own GEMMs)
+        assert c._tap_calls == len(batches_run) * len(c.target_info), (c._tap_calls, len(c.target_info))
     torch.cuda.synchronize()
     if tokens:
         from bergson_b200 import TokenGradients
