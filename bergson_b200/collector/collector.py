@@ -401,6 +401,9 @@ class HookCollectorBase(ContextDecorator, ABC):
         self._fwd_hooks.clear()
         return False
 
+    def on_batch_start(self, step: int, num_steps: int) -> None:
+        """Called by the collection loop before batch ``step`` of ``num_steps`` (no-op by default)."""
+
     @abstractmethod
     def setup(self) -> None: ...
 
@@ -727,6 +730,7 @@ class CollectorComputer:
         prof = self._setup_profiler()
         with prof, self.collector:
             for step, indices in enumerate(tqdm(self.batches, desc=f"Computing {desc}", disable=self.rank != 0)):
+                self.collector.on_batch_start(step, len(self.batches))
                 if self.cfg.profile:
                     from torch.profiler import record_function
 

@@ -278,7 +278,7 @@ void row_sumsq(at::Tensor x, at::Tensor out) {
 }
 
 void cov_syrk(at::Tensor x, std::vector<int64_t> dst_ptrs, std::vector<int64_t> row_start,
-              c10::optional<at::Tensor> local, bool full, int64_t num_rows) {
+              c10::optional<at::Tensor> local, bool full, int64_t num_rows, bool local_upper) {
   // x: [T, D] 16-bit; dst_ptrs: device addresses (this GPU's or peer-mapped) of every rank's
   // fp32 row shard; row_start: world + 1 row boundaries.
   TORCH_CHECK(x.is_cuda() && x.dim() == 2 && x.is_contiguous());
@@ -298,7 +298,7 @@ void cov_syrk(at::Tensor x, std::vector<int64_t> dst_ptrs, std::vector<int64_t> 
   const int sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
   // num_rows < 0: use every row of x; num_rows == 0: only push `local`.
   const long T = num_rows < 0 ? x.size(0) : std::min<int64_t>(num_rows, x.size(0));
-  check(bgn_cov_syrk(x.data_ptr(), T, (int)x.size(1), fmt16(x), dst, rs, world, loc, full ? 1 : 0, sms,
+  check(bgn_cov_syrk(x.data_ptr(), T, (int)x.size(1), fmt16(x), dst, rs, world, loc, full ? 1 : 0, local_upper ? 1 : 0, sms,
                      status_ptr(x), stream()), "cov_syrk");
 }
 
@@ -431,7 +431,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("adamw_step", &adamw_step);
   m.def("row_sumsq", &row_sumsq);
   m.def("cov_syrk", &cov_syrk, py::arg("x"), py::arg("dst_ptrs"), py::arg("row_start"), py::arg("local"),
-        py::arg("full") = false, py::arg("num_rows") = -1);
+        py::arg("full") = false, py::arg("num_rows") = -1, py::arg("local_upper") = false);
   m.def("gemm", &gemm, py::arg("a"), py::arg("b"), py::arg("a_mn") = false, py::arg("b_mn") = false,
         py::arg("out") = py::none(), py::arg("out_f32") = false, py::arg("bias") = py::none(),
         py::arg("accumulate") = false, py::arg("aux_p") = py::none(), py::arg("cta_group") = 2,

@@ -40,6 +40,9 @@ struct CovParams {
   int tiles_n;         // 256-column tile columns
   int full;            // 1: every tile is visited (used when the destination must end up
                        // holding complete rows, e.g. the cross-rank reduce-scatter)
+  int local_upper;     // 1: `local` holds valid values only in the tiles that touch the upper
+                       // triangle (it was filled by non-full launches); elements of the other
+                       // tiles are read from their mirror position
 };
 
 __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
@@ -183,10 +186,17 @@ cov_syrk_kernel(const __grid_constant__ CUtensorMap tmap, CovParams p, int* stat
         const int col = tn * kCovBlockN + c;
         if (drow == nullptr || col >= p.D) continue;
         if (fold_local) {
-          const float* lrow = p.local + long(r) * p.D + col;
+          if (!p.local_upper || tn >= tm / 2) {
+            const float* lrow = p.local + long(r) * p.D + col;
 #pragma unroll
-          for (int i = 0; i < 16; ++i)
-            if (col + i < p.D) acc[i] += lrow[i];
+            for (int i = 0; i < 16; ++i)
+              if (col + i < p.D) acc[i] += lrow[i];
+          } else {
+            // mirror: the accumulator is symmetric and only its upper tiles were computed
+#pragma unroll
+            for (int i = 0; i < 16; ++i)
+              if (col + i < p.D) acc[i] += p.local[long(col + i) * p.D + r];
+          }
         }
         if (col + 16 <= p.D && (p.D & 3) == 0) {
 #pragma unroll
@@ -232,7 +242,7 @@ static EncodeTiledFn cov_encode_fn() {
 using namespace bgn;
 
 extern "C" int bgn_cov_syrk(const void* x, long T, int D, int fmt, float* const* dst, const int* row_start,
-                            int world, const float* local, int full, int sm_count, int* status,
+                            int world, const float* local, int full, int local_upper, int sm_count, int* status,
                             cudaStream_t stream) {
   if (D % 8 != 0 || (reinterpret_cast<uintptr_t>(x) & 15) || world < 1 || world > 8)
     return int(cudaErrorInvalidValue);
@@ -262,6 +272,7 @@ extern "C" int bgn_cov_syrk(const void* x, long T, int D, int fmt, float* const*
   p.tiles_m = (D + kCovBlock - 1) / kCovBlock;
   p.tiles_n = (D + kCovBlockN - 1) / kCovBlockN;
   p.full = full ? 1 : 0;
+  p.local_upper = local_upper ? 1 : 0;
   int tiles = 0;
   for (int tm = 0; tm < p.tiles_m; ++tm) tiles += p.full ? p.tiles_n : p.tiles_n - tm / 2;
   const long kb_total = (p.T + kCovBlockK - 1) / kCovBlockK;

@@ -88,7 +88,8 @@ static cudaError_t launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, con
 
 template <int FMT, bool OUT32>
 static cudaError_t launch_gemm_wide(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tp,
-                                    const GemmParams& p, int grid, int* status, cudaStream_t stream) {
+                                    const CUtensorMap& td, const GemmParams& p, int grid, int* status,
+                                    cudaStream_t stream) {
   auto kern = gemm_wide_kernel<FMT, OUT32>;
   static bool attr_set = false;  // one flag per instantiation
   if (!attr_set) {
@@ -108,7 +109,7 @@ static cudaError_t launch_gemm_wide(const CUtensorMap& ta, const CUtensorMap& tb
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, kern, ta, tb, tp, p, status);
+  return cudaLaunchKernelEx(&cfg, kern, ta, tb, tp, td, p, status);
 }
 
 }  // namespace bgn
@@ -183,6 +184,9 @@ extern "C" int bgn_gemm(const BgnGemmArgs* a, int* status, cudaStream_t stream) 
   if (panel < 2) panel = 2;
   if (panel > 16 && a->panel <= 0) panel = 16;
   if (panel > tiles_n) panel = tiles_n;
+  // Keep the aux column in a panel with real columns: alone in a last panel of its own it would
+  // stream every slab of A from memory once more.
+  if (a->aux_n > 0 && panel < tiles_n && tiles_n % panel == 1) ++panel;
   p.panel = int(panel);
   long groups = a->sm_count / cg;
   if (groups < 1) groups = 1;
@@ -191,10 +195,10 @@ extern "C" int bgn_gemm(const BgnGemmArgs* a, int* status, cudaStream_t stream) 
   cudaError_t e;
   const bool bf = a->fmt == 1;
   if (wide) {
-    e = a->out_f32 ? (bf ? launch_gemm_wide<1, true>(ta, tb, tp, p, grid, status, stream)
-                         : launch_gemm_wide<0, true>(ta, tb, tp, p, grid, status, stream))
-                   : (bf ? launch_gemm_wide<1, false>(ta, tb, tp, p, grid, status, stream)
-                         : launch_gemm_wide<0, false>(ta, tb, tp, p, grid, status, stream));
+    e = a->out_f32 ? (bf ? launch_gemm_wide<1, true>(ta, tb, tp, td, p, grid, status, stream)
+                         : launch_gemm_wide<0, true>(ta, tb, tp, td, p, grid, status, stream))
+                   : (bf ? launch_gemm_wide<1, false>(ta, tb, tp, td, p, grid, status, stream)
+                         : launch_gemm_wide<0, false>(ta, tb, tp, td, p, grid, status, stream));
   } else if (cg == 2) {
     e = a->out_f32 ? (bf ? launch_gemm<2, 1, true>(ta, tb, tp, td, p, grid, status, stream)
                          : launch_gemm<2, 0, true>(ta, tb, tp, td, p, grid, status, stream))

@@ -7,8 +7,11 @@
 // is what limits that kernel's tensor-pipe utilisation.  The price is TMEM: the two 128 x 256
 // fp32 accumulators fill all 512 columns, so there is one accumulator stage and the epilogue of
 // a tile overlaps only the first k-block of the next one.  Eight epilogue warps (two per TMEM
-// lane quadrant, each taking half of the columns) and 32-byte stores keep that epilogue short;
-// the two row blocks are released to the MMA warp separately.
+// lane quadrant, each taking half of the columns) keep the drain short: for plain 16-bit outputs
+// they move their accumulator slice through registers into a shared-memory staging slab, hand
+// the row block back to the MMA warp at once, and let TMA stores write the slab to memory while
+// the next tile's MMAs already run.  Other outputs (fp32, accumulate, batched) are stored from
+// registers with 32-byte stores.  The two row blocks are released separately.
 //
 // Warp roles: 0 = A producer, 1 = MMA issuer (leader CTA), 2..9 = epilogue, 10 = B producer.
 // Operand layouts, the aux (projection) tile column, bias, accumulation, the batched
@@ -24,8 +27,10 @@ constexpr int kWideTileM = 512;     // rows per CTA pair
 constexpr int kWideABytes = 2 * 128 * kGemmBlockK * 2;   // two row blocks
 constexpr int kWideBBytes = 128 * kGemmBlockK * 2;
 constexpr int kWideStageBytes = kWideABytes + kWideBBytes;  // 48 KB
-constexpr int kWideStages = 4;
-constexpr int kWideSmemBytes = kWideStages * kWideStageBytes + 1024 + 512;
+constexpr int kWideStages = 3;
+// Output staging: each of the eight epilogue warps owns 32 rows x 128 columns of a 16-bit type.
+constexpr int kWideStagingBytes = 8 * 32 * 128 * 2;  // 64 KB
+constexpr int kWideSmemBytes = kWideStages * kWideStageBytes + kWideStagingBytes + 1024 + 512;
 
 // 32 bytes per thread in one instruction: a full sector per row.
 __device__ __forceinline__ void st_global_v8(void* ptr, const uint32_t (&r)[8]) {
@@ -37,14 +42,16 @@ __device__ __forceinline__ void st_global_v8(void* ptr, const uint32_t (&r)[8]) 
 template <int FMT, bool OUT32>
 __global__ void __launch_bounds__(kWideThreads, 1)
 gemm_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                 const __grid_constant__ CUtensorMap tmap_p, GemmParams p, int* status) {
+                 const __grid_constant__ CUtensorMap tmap_p, const __grid_constant__ CUtensorMap tmap_d, GemmParams p,
+                 int* status) {
   constexpr int CG = 2;
   using InT = typename std::conditional<FMT == 1, __nv_bfloat16, __half>::type;
   constexpr int kStages = kWideStages;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* tiles = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint64_t* full_bar = reinterpret_cast<uint64_t*>(tiles + kStages * kWideStageBytes);
+  uint8_t* staging = tiles + kStages * kWideStageBytes;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(staging + kWideStagingBytes);
   uint64_t* empty_bar = full_bar + kStages;
   uint64_t* tmem_full_bar = empty_bar + kStages;   // [1]
   uint64_t* tmem_empty_bar = tmem_full_bar + 1;    // [2]: one per row block
@@ -74,6 +81,7 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     tma_prefetch_desc(&tmap_a);
     tma_prefetch_desc(&tmap_b);
     if (p.aux_n > 0) tma_prefetch_desc(&tmap_p);
+    if (p.tma_store) tma_prefetch_desc(&tmap_d);
   }
   if (warp == 1) tmem_alloc_cg<CG>(tmem_slot, 512);
   tc_fence_before();
@@ -136,7 +144,11 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       for (long t = group; t < num_tiles && ok; t += num_groups, ++local_tile) {
         const GemmTile tile = gemm_tile(t, tiles_m, tiles_n, tiles_nt, p.panel);
         const uint32_t acc_parity = (uint32_t(local_tile) & 1u) ^ 1u;  // first use: free
+        const bool tracing = p.trace != nullptr && lane == 0 && group == 0;
+        const long long t_begin = tracing ? clock64() : 0;
+        long long full_wait = 0, t_acc1 = 0;
         ok = mbar_wait_budget(&tmem_empty_bar[0], acc_parity, p.wait_cycles);
+        const long long t_acc0 = tracing ? clock64() : 0;
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) {
           if (lane == 0) atomicCAS(status, kStatusOk, kStatusTimeoutMma);
@@ -148,7 +160,9 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         const uint32_t idesc = make_idesc_f16(256, n_inst, FMT, p.a_mn, b_mn ? 1 : 0);
         const uint32_t a_step = p.a_mn ? 2048u : 32u, b_step = b_mn ? 2048u : 32u;
         for (int kb = 0; kb < num_kb; ++kb) {
+          const long long w0 = tracing ? clock64() : 0;
           ok = mbar_wait_budget(&full_bar[stage], phase, p.wait_cycles);
+          if (tracing) full_wait += clock64() - w0;
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) {
             if (lane == 0) atomicCAS(status, kStatusOk, kStatusTimeoutMma);
@@ -175,6 +189,7 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
               break;
             }
             tc_fence_after();
+            if (tracing) t_acc1 = clock64();
           }
           if (lane == 0) {
 #pragma unroll
@@ -190,6 +205,14 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           }
         }
         if (ok && lane == 0) umma_commit_cg<CG>(tmem_full_bar);
+        if (tracing) {
+          long long* tr = p.trace + local_tile * 8;
+          tr[0] = t_begin;
+          tr[1] = t_acc0;
+          tr[2] = clock64();
+          tr[3] = full_wait;
+          tr[7] = t_acc1;
+        }
         __syncwarp();
       }
     }
@@ -204,7 +227,10 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     for (int a = 0; a < 2; ++a) empty_addr[a] = map_to_cta(smem_u32(&tmem_empty_bar[a]), 0);
     for (long t = group; t < num_tiles && ok; t += num_groups, ++local_tile) {
       const GemmTile tile = gemm_tile(t, tiles_m, tiles_n, tiles_nt, p.panel);
+      const bool tracing = p.trace != nullptr && group == 0 && leader && warp == 2 && lane == 0;
+      const long long e0 = tracing ? clock64() : 0;
       ok = mbar_wait_budget(tmem_full_bar, uint32_t(local_tile) & 1u, p.wait_cycles);
+      const long long e1 = tracing ? clock64() : 0;
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) {
         if (lane == 0) atomicCAS(status, kStatusOk, kStatusTimeoutEpilogue);
@@ -231,6 +257,68 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
               }
             }
           }
+        } else if (!OUT32 && p.tma_store) {
+          // This warp's 32 rows x 128 columns go through its private staging slab (two 64-column
+          // slabs in the 128-byte swizzle); TMA stores clip at the matrix edges.
+          uint8_t* stg = staging + (warp - 2) * 8192;
+          if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // earlier stores
+          __syncwarp();
+          const uint32_t stg_row = smem_u32(stg) + uint32_t(lane) * 128u;
+#pragma unroll 1
+          for (int cc = 0; cc < 128; cc += 32) {
+            const int c = half * 128 + cc;
+            if (c >= n_valid) break;  // uniform over the warp
+            float v[32];
+            tmem_ld_32x32(t_addr + c, v);
+            if (p.bias != nullptr) {
+              const int nv = n_valid - c < 32 ? n_valid - c : 32;
+              if (p.bias_f32) {
+                const float* b = reinterpret_cast<const float*>(p.bias) + col0 + c;
+#pragma unroll
+                for (int i = 0; i < 32; ++i)
+                  if (i < nv) v[i] += __ldg(b + i);
+              } else {
+                const InT* b = reinterpret_cast<const InT*>(p.bias) + col0 + c;
+#pragma unroll
+                for (int i = 0; i < 32; ++i)
+                  if (i < nv) v[i] += to_float<InT>(b[i]);
+              }
+            }
+            const uint32_t slab = stg_row + uint32_t(cc >> 6) * 4096u;
+            const uint32_t chunk0 = uint32_t(cc & 63) >> 3;  // 16-byte chunk of the 128-byte row: 0 or 4
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              union { uint4 u; InT h[8]; } o;
+#pragma unroll
+              for (int e = 0; e < 8; ++e) o.h[e] = from_float<InT>(v[j * 8 + e]);
+              const uint32_t addr = slab + (((chunk0 + j) ^ (uint32_t(lane) & 7u)) << 4);
+              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(o.u.x), "r"(o.u.y),
+                           "r"(o.u.z), "r"(o.u.w)
+                           : "memory");
+            }
+          }
+          // The accumulator slice is in shared memory: the row block can go back to the MMA warp
+          // before a single byte has reached global memory.
+          tc_fence_before();
+          fence_proxy_async();
+          __syncwarp();
+          const int row0 = tile.tm * kWideTileM + rb * 256 + int(cta_rank) * 128 + quad * 32;
+          if (lane == 0) {
+            mbar_arrive_cluster(empty_addr[rb]);
+            if (row0 < p.M) {
+              for (int b = 0; b < 2; ++b) {
+                const int c = half * 128 + b * 64;
+                if (c >= n_valid) break;
+                asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
+                                 reinterpret_cast<uint64_t>(&tmap_d)),
+                             "r"(smem_u32(stg) + uint32_t(b) * 4096u), "r"(col0 + c), "r"(row0)
+                             : "memory");
+              }
+            }
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          }
+          if (tracing) p.trace[local_tile * 8 + 5 + rb] = clock64();
+          continue;  // this row block is done (barrier arrival included)
         } else {
           const long d_row_off = long(tile.batch) * p.d_batch_stride + row * p.ldd + col0;
 #pragma unroll 1
@@ -330,10 +418,14 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive_cluster(empty_addr[rb]);
+        if (tracing) p.trace[local_tile * 8 + 5 + rb] = clock64();
       }
+      if (tracing) p.trace[local_tile * 8 + 4] = e1;
+      (void)e0;
     }
   }
 
+  if (warp >= 2 && warp < 10 && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
   tc_fence_before();
   __syncthreads();
   cluster_sync_all();  // the peer may still be reading this CTA's operands

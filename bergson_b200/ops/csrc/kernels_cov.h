@@ -10,6 +10,9 @@ extern "C" {
 // dst pointers may be peer-mapped memory of other GPUs.  With `full` every 128 x 256 tile is
 // visited, so the destinations receive complete rows (cross-rank reduce-scatter of the
 // product and/or of `local`); T == 0 with `local` set is a pure push of `local`.
+// `local_upper`: `local` was itself accumulated by non-full launches (only its upper tiles are
+// valid); the fold reads the remaining elements from their mirror positions.
 int bgn_cov_syrk(const void* x, long T, int D, int fmt, float* const* dst, const int* row_start,
-                 int world, const float* local, int full, int sm_count, int* status, cudaStream_t stream);
+                 int world, const float* local, int full, int local_upper, int sm_count, int* status,
+                 cudaStream_t stream);
 }

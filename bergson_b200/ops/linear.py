@@ -31,9 +31,16 @@ from .functional import use_fused
 _TC_DTYPES = (torch.bfloat16, torch.float16)
 
 
-def _cta_group() -> int:
-    """2 (CTA pairs, the default) or 1 (single-CTA form) from ``BERGSON_B200_GEMM_CTA_GROUP``."""
-    return 1 if os.environ.get("BERGSON_B200_GEMM_CTA_GROUP") == "1" else 2
+def _gemm_form() -> dict:
+    """Keyword arguments selecting the GEMM form: the wide CTA-pair kernel by default;
+    ``BERGSON_B200_GEMM_FORM=pair`` / ``single`` select the 256 x 256 pair tile or the
+    single-CTA kernel (debugging, comparisons)."""
+    form = os.environ.get("BERGSON_B200_GEMM_FORM", "wide")
+    if form == "single":
+        return dict(cta_group=1)
+    if form == "pair":
+        return dict(cta_group=2)
+    return dict(cta_group=2, wide=True)
 
 
 class ProjectionTap(Protocol):
@@ -61,6 +68,34 @@ def gemm_eligible(x: Tensor, weight: Tensor) -> bool:
     )
 
 
+def _aux_fits(rows: int, cols: int, device) -> bool:
+    """Whether the projection side output rides along for free.  It is one more (cheap) tile
+    per 512-row block; the persistent kernel deals tiles round-robin over the CTA pairs, so
+    the extra tiles are free unless they push the tile count over a multiple of the number
+    of pairs, in which case a separate pass over the operand is cheaper."""
+    pairs = max(1, torch.cuda.get_device_properties(device).multi_processor_count // 2)
+    tiles_m, tiles_n = -(-rows // 512), -(-cols // 256)
+    return -(-(tiles_m * (tiles_n + 1)) // pairs) == -(-(tiles_m * tiles_n) // pairs)
+
+
+def _project(x2: Tensor, p: Tensor) -> Tensor:
+    """``x2 @ p^T`` in fp32 as its own pass (16-row operands on the skinny tcgen05 kernel)."""
+    from . import native
+
+    if p.shape[0] == 16 and x2.shape[1] % 8 == 0:
+        return native.proj_right(x2, p)
+    return x2.float() @ p.float().T
+
+
+def _gemm_with_projection(x2: Tensor, w: Tensor, b_mn: bool, bias, p: Tensor | None, out_cols: int, form: dict):
+    from . import native
+
+    if p is None or _aux_fits(x2.shape[0], out_cols, x2.device):
+        return native.gemm(x2, w, False, b_mn, None, False, bias, False, p, **form)
+    y, _ = native.gemm(x2, w, False, b_mn, None, False, bias, False, None, **form)
+    return y, _project(x2, p)
+
+
 class _LinearFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x: Tensor, weight: Tensor, bias: Tensor | None, layout: str, module, tap):
@@ -74,12 +109,11 @@ class _LinearFn(torch.autograd.Function):
         if not x2.is_contiguous():
             x2 = x2.contiguous()
         taps = tap.operands(module, x) if tap is not None else None
-        cg = _cta_group()
-        y, a_proj = native.gemm(x2, weight, False, not oi, None, False, bias, False,
-                                taps[0] if taps is not None else None, cg)
+        form = _gemm_form()
+        y, a_proj = _gemm_with_projection(x2, weight, not oi, bias, taps[0] if taps is not None else None, out_f, form)
         ctx.save_for_backward(x2 if weight.requires_grad else None, weight, taps[1] if taps is not None else None,
                               a_proj if taps is not None else None)
-        ctx.layout, ctx.lead, ctx.cg = layout, lead, cg
+        ctx.layout, ctx.lead, ctx.form = layout, lead, form
         ctx.module, ctx.tap = (module, tap) if taps is not None else (None, None)
         ctx.has_bias = bias is not None
         return y.view(*lead, out_f)
@@ -98,7 +132,8 @@ class _LinearFn(torch.autograd.Function):
         g_proj = None
         if ctx.needs_input_grad[0]:
             # dx = g W (oi: W read as [K = out, N = in]) or g W^T (io: W read as [N = in, K = out]).
-            dx2, g_proj = native.gemm(g2, weight, False, oi, None, False, None, False, p_out, ctx.cg)
+            in_f = weight.shape[1] if oi else weight.shape[0]
+            dx2, g_proj = _gemm_with_projection(g2, weight, oi, None, p_out, in_f, ctx.form)
             dx = dx2.view(*ctx.lead, dx2.shape[1])
         if ctx.tap is not None:
             if g_proj is None or g_proj.numel() == 0:
@@ -107,7 +142,7 @@ class _LinearFn(torch.autograd.Function):
         if ctx.needs_input_grad[1]:
             # dW = g^T x ([out, in]) or x^T g ([in, out]): both operands read along the tokens.
             lhs, rhs = (g2, x2) if oi else (x2, g2)
-            dw, _ = native.gemm(lhs, rhs, True, True, None, False, None, False, None, ctx.cg)
+            dw, _ = native.gemm(lhs, rhs, True, True, None, False, None, False, None, **ctx.form)
         if ctx.has_bias and ctx.needs_input_grad[2]:
             db = g2.sum(0)
         return dx, dw, db, None, None, None

@@ -205,3 +205,34 @@ def test_sharded_attributor_two_gpus(tmp_path):
     for _, s, i in results:
         torch.testing.assert_close(s, s_ref.float().cpu(), atol=2e-3, rtol=1e-2)
         assert (i == i_ref.cpu()).float().mean() > 0.95  # near-ties may swap under fp16 rounding
+
+
+def test_kfac_factors_two_gpus_match_one(tmp_path):
+    """K-FAC covariances on 2 GPUs: the last batch's SYRK launch folds the local accumulators in
+    and adds the rows into their owners' peer memory (GEMM -> reduce-scatter); the assembled
+    factors must equal the 1-GPU factors."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    from bergson_b200.hessians.preconditioner import _load_full
+
+    root = Path(__file__).resolve().parents[1]
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    opts = ["--model", "native:llama-tiny?hidden_size=128&intermediate_size=256&vocab_size=1024&max_position_embeddings=1024",
+            "--precision", "bf16", "--index_cfg.data.dataset", "synthetic:zipf?n=24&len=160&vocab=1024&seed=0&min_len=90",
+            "--method", "kfac", "--use_dataset_labels", "--token_batch_size", "640"]
+    for name, n in (("one", 1), ("two", 2)):
+        out = subprocess.run([sys.executable, "-m", "bergson_b200", "hessian", str(tmp_path / name), *opts,
+                              "--nproc_per_node", str(n)], cwd=root, env=env, capture_output=True, text=True, timeout=600)
+        assert out.returncode == 0, out.stderr[-2000:]
+    for sub in ("activation_sharded", "gradient_sharded"):
+        one = _load_full(tmp_path / "one", sub, "cpu")
+        two = _load_full(tmp_path / "two", sub, "cpu")
+        assert one.keys() == two.keys() and len(one) > 0
+        for k in one:
+            assert one[k].shape == two[k].shape
+            assert float((one[k] - two[k]).norm() / one[k].norm()) < 2e-3, (sub, k)
+            assert float((two[k] - two[k].T).abs().max() / two[k].abs().max()) < 1e-5, (sub, k, "not symmetric")
