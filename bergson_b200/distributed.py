@@ -129,6 +129,11 @@ def launch_distributed_run(process_name: str, worker, const_worker_args: list[An
         assert len(devices) >= local_world, (
             f"CUDA_VISIBLE_DEVICES has {len(devices)} entries ({parent_cvd!r}) but nproc_per_node={local_world}"
         )
+    # Every rank keeps all of the node's GPUs visible and selects its own by index: kernels that
+    # read or add into other ranks' memory over NVLink (symmetric peer heaps) need the peers'
+    # devices to be addressable.  BERGSON_B200_PIN_VISIBLE_DEVICES=1 restores one visible GPU per
+    # child, at the price of the peer-memory paths.
+    pin = os.environ.get("BERGSON_B200_PIN_VISIBLE_DEVICES") == "1"
     if dist_config.nnode > 1:
         master_addr = os.environ.get("MASTER_ADDR", "127.0.0.1")
         master_port = os.environ.get("MASTER_PORT", "29500")
@@ -139,7 +144,7 @@ def launch_distributed_run(process_name: str, worker, const_worker_args: list[An
     children = []
     try:
         for i in range(local_world):
-            if torch.cuda.is_available():
+            if torch.cuda.is_available() and pin:
                 # Inherited through exec, before the child imports torch.
                 os.environ["CUDA_VISIBLE_DEVICES"] = devices[i]
             p = ctx.Process(target=dist_worker,

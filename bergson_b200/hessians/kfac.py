@@ -46,6 +46,7 @@ class _FactorCollector(HookCollectorBase):
         self.S_full: dict[str, Tensor] = {}
         self._final_batch = False
         self._flushed: set[tuple[str, str]] = set()
+        self._flushed_in_gemm: set[tuple[str, str]] = set()
         self._peer = self._make_peer_regions() if self._peer_wanted() else None
 
     # -- peer-memory reduce-scatter ---------------------------------------------------------
@@ -141,6 +142,7 @@ class _FactorCollector(HookCollectorBase):
                 acc.addmm_(xd.mT, xd, alpha=-1.0)
             if flush:
                 self._push(key, x2.contiguous(), acc, local_upper=True)
+                self._flushed_in_gemm.add(key)
             else:
                 attribution.gram_accumulate(acc, x2)
             return
@@ -263,6 +265,9 @@ class _FactorCollector(HookCollectorBase):
         if self._peer is not None:
             heap = self._peer[0]
             heap.barrier()  # every rank's adds have landed
+            n_fused = len(self._flushed_in_gemm)
+            self.logger.info(f"factors reduced through peer memory: {n_fused} inside the last batch's SYRK launches, "
+                             f"{len(self._flushed) - n_fused} pushed at teardown")
             A = self._read_peer_shards("A", [n for n in self.target_info if n in self.A_full])
             S = self._read_peer_shards("S", [n for n in self.target_info if n in self.S_full])
             heap.barrier()  # all ranks have read their shards before the heap is released

@@ -30,7 +30,9 @@ def symmetric_memory_available() -> bool:
         import torch.distributed._symmetric_memory  # noqa: F401
     except Exception:
         return False
-    return torch.cuda.is_available() and dist.is_initialized() and dist.get_backend() != "gloo"
+    # Peers are addressed through their device mappings: every rank must see more than its own GPU.
+    return (torch.cuda.is_available() and dist.is_initialized() and dist.get_backend() != "gloo"
+            and (dist.get_world_size() == 1 or torch.cuda.device_count() > 1))
 
 
 class PeerHeap:

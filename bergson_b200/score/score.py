@@ -170,6 +170,8 @@ def score_worker(rank: int, local_rank: int, world_size: int, index_cfg: IndexCo
         (lo, min(lo + qbs, num_queries)) for lo in range(0, num_queries, qbs)
     ]
     shard_queries = _gather_queries_ok(score_cfg, preprocess_cfg, device, dtype, index_cfg.attribute_tokens)
+    if shard_queries and rank == 0:
+        print(f"score: query rows sharded over {world_size} ranks in peer memory (all-gather fused into the score GEMM)")
     for qr in ranges:
         scorer = create_scorer(index_cfg.partial_run_path, ds, score_cfg, preprocess_cfg, device=device, dtype=dtype,
                                attribute_tokens=index_cfg.attribute_tokens, query_range=qr,

@@ -126,7 +126,7 @@ def test_score_with_sharded_queries_matches_single_gpu(tmp_path):
 
     root = Path(__file__).resolve().parents[1]
     model = ["--model", "native:llama-tiny?hidden_size=128&intermediate_size=256&vocab_size=1024&max_position_embeddings=1024",
-             "--precision", "bf16", "--projection_dim", "16", "--token_batch_size", "640"]
+             "--index_cfg.precision", "bf16", "--projection_dim", "16", "--token_batch_size", "640"]
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
 
     def cli(*args):
@@ -135,11 +135,13 @@ def test_score_with_sharded_queries_matches_single_gpu(tmp_path):
         assert out.returncode == 0, out.stderr[-2000:]
         return out
 
-    cli("build", tmp_path / "query", "--data.dataset", "synthetic:zipf?n=13&len=160&vocab=1024&seed=1&min_len=90", *model,
-        "--nproc_per_node", "1")
+    build_model = [m if m != "--index_cfg.precision" else "--precision" for m in model]
+    cli("build", tmp_path / "query", "--data.dataset", "synthetic:zipf?n=13&len=160&vocab=1024&seed=1&min_len=90",
+        *build_model, "--nproc_per_node", "1")
     data = ["--data.dataset", "synthetic:zipf?n=24&len=160&vocab=1024&seed=0&min_len=90"]
     for name, n in (("one", 1), ("two", 2)):
         out = cli("score", tmp_path / name, *data, *model, "--query_path", tmp_path / "query", "--nproc_per_node", n)
+        assert ("all-gather fused into the score GEMM" in out.stdout) == (n == 2), out.stdout[-500:]
     a, b = load_scores(tmp_path / "one")[:].astype(np.float32), load_scores(tmp_path / "two")[:].astype(np.float32)
     assert a.shape == b.shape == (24, 13) and np.abs(a).max() > 0
     assert np.abs(a - b).max() / np.abs(a).max() < 2e-2
@@ -228,6 +230,9 @@ def test_kfac_factors_two_gpus_match_one(tmp_path):
         out = subprocess.run([sys.executable, "-m", "bergson_b200", "hessian", str(tmp_path / name), *opts,
                               "--nproc_per_node", str(n)], cwd=root, env=env, capture_output=True, text=True, timeout=600)
         assert out.returncode == 0, out.stderr[-2000:]
+        if n == 2:
+            assert "inside the last batch's SYRK launches" in out.stdout + out.stderr
+            assert "reduced through peer memory: 0 inside" not in out.stdout + out.stderr
     for sub in ("activation_sharded", "gradient_sharded"):
         one = _load_full(tmp_path / "one", sub, "cpu")
         two = _load_full(tmp_path / "two", sub, "cpu")
