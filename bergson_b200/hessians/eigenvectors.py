@@ -86,6 +86,20 @@ class LambdaCollector(HookCollectorBase):
         name = assert_type(str, module._name)
         tg = self._rotate("g", name, g, self.eigen_g[name])  # [N, S, O]
         ta = self.transformed_a_cache.pop(name)  # [N, S, I]
+        from ..ops.functional import use_fused
+
+        if (tg.dtype == torch.float32 and tg.dim() == 3 and use_fused(tg, ta) and tg.shape[-1] % 8 == 0
+                and ta.shape[-1] % 8 == 0 and tg.shape[1] > 0):
+            # One batched tensor-core launch: per document (G_n Q_G)^T (A_n Q_A) in TMEM, squared and
+            # added into the [O, I] grid by the epilogue -- the [N, O, I] products are never stored.
+            from ..ops import native
+
+            acc = self.eigenvalue_corrections.get(name)
+            if acc is None:
+                acc = self.eigenvalue_corrections[name] = torch.zeros(tg.shape[-1], ta.shape[-1], device=tg.device)
+            native.gemm(tg.to(torch.bfloat16).contiguous(), ta.to(torch.bfloat16).contiguous(), True, True, acc, True,
+                        None, False, None, 2, sq_accumulate=True)
+            return
         if tg.is_cuda and tg.dtype == torch.float32:
             # Per-document outer products on TF32 tensor cores (fp32 accumulate); the result is
             # squared and summed over documents, so 10-bit operand mantissas are ample.

@@ -166,11 +166,29 @@ class FactoredPreconditioner:
             q_a, q_g, mult = self._assembled(name)
             o, i = q_g.shape[0], q_a.shape[0]
             g = flat.to(q_a.device, torch.float32).view(-1, o, i)
-            g = q_g.T @ (g @ q_a)          # into the eigenbasis
+            g = _left(q_g.T, _right(g, q_a))   # into the eigenbasis
             g = g * mult
-            g = q_g @ (g @ q_a.T)          # and back
+            g = _left(q_g, _right(g, q_a.T))   # and back
             out[name] = g.reshape(flat.shape[0], -1).to(flat.dtype)
         return out
+
+
+def _right(g: Tensor, m: Tensor) -> Tensor:
+    """``g [n, O, I] @ m [I, J]``: one GEMM over all ``n * O`` rows (fp32-accurate tensor-core
+    product on CUDA, see ``ops.attribution.split_matmul``)."""
+    from ..ops.attribution import split_matmul
+
+    n, o, i = g.shape
+    return split_matmul(g.reshape(n * o, i), m.contiguous()).view(n, o, m.shape[1])
+
+
+def _left(m: Tensor, g: Tensor) -> Tensor:
+    """``m [P, O] @ g [n, O, I]`` for every n, as ``(g^T m^T)^T`` so that it is one GEMM too."""
+    from ..ops.attribution import split_matmul
+
+    n, o, i = g.shape
+    gt = g.transpose(1, 2).reshape(n * i, o)
+    return split_matmul(gt, m.T.contiguous()).view(n, i, m.shape[0]).transpose(1, 2)
 
 
 class DiagonalFactoredPreconditioner:

@@ -139,3 +139,24 @@ def rotate(x: Tensor, q: Tensor, q_split: Tensor | None = None) -> Tensor:
         out = native.tn_gemm(x.reshape(-1, a).contiguous(), qs)  # [T, 2b] fp32
         return (out[:, :b] + out[:, b:]).view(*lead, b)
     return x.to(q.dtype) @ q
+
+
+def split_matmul(a: Tensor, b: Tensor) -> Tensor:
+    """``a [M, K] @ b [K, N]`` for fp32 operands at close to fp32 accuracy on the 16-bit tensor
+    cores.  Each operand is written as ``hi + lo`` (bf16 rounding and bf16-rounded residual);
+    ``hi hi + hi lo + lo hi`` is evaluated as *one* GEMM with the three terms laid side by side
+    along the reduction axis (``[ah | ah | al] @ [bh ; bl ; bh]``), accumulated in fp32 by the
+    persistent tcgen05 kernel.  The dropped ``lo lo`` term is ~2^-16 relative.  Falls back to a
+    plain matmul off CUDA or for shapes the kernel does not take."""
+    M, K = a.shape
+    N = b.shape[1]
+    if not (use_fused(a, b) and a.dtype == torch.float32 and b.dtype == torch.float32 and K % 8 == 0 and N % 8 == 0
+            and M > 0):
+        return a @ b
+    ah = a.to(torch.bfloat16)
+    al = (a - ah.float()).to(torch.bfloat16)
+    bh = b.to(torch.bfloat16)
+    bl = (b - bh.float()).to(torch.bfloat16)
+    lhs = torch.cat([ah, ah, al], dim=1).contiguous()          # [M, 3K], K-major
+    rhs = torch.cat([bh, bl, bh], dim=0).contiguous()          # [3K, N], read MN-major
+    return native.gemm(lhs, rhs, False, True, None, True)[0]
