@@ -49,6 +49,8 @@ def parse_args():
     ap.add_argument("--seqs", type=int, default=8, help="sequences per rank per step")
     ap.add_argument("--seq-len", type=int, default=2048)
     ap.add_argument("--small", action="store_true", help="4-layer d1024 stand-in for quick checks (not a bench value)")
+    ap.add_argument("--extra", default="query,ekfac",
+                    help="comma-separated secondary metrics reported under \"extra\" (query, ekfac; empty for none)")
     return ap.parse_args()
 
 
@@ -171,7 +173,8 @@ def run_ours(args, rank, local_rank, world):
         "e2e": {"value": tokens / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": 2 * B * S * 8 + B * 8,
                 "d2h_bytes_per_step": B * row_bytes + 4, "ms_per_step": e2e_s * 1e3 / K},
         "clocks": clocks, "loss_checksum": loss_sum,
-        "store": "fp16 rows, pinned staging ring -> memmap", "model": "llama-32L-d4096" if not args.small else "small",
+        "arm": {"store": "fp16 rows, pinned staging ring -> memmap", "model_impl": "in-tree Llama on the tcgen05 GEMM"},
+        "model": "llama-32L-d4096" if not args.small else "small",
     }
 
 
@@ -262,7 +265,8 @@ def run_reference(args, rank, local_rank, world):
         "value": tokens / (dev_ms / 1e3), "ms_per_step": dev_ms / K, "gpu_launches": None,
         "e2e": {"value": tokens / wall_s, "unit": "tokens/s", "h2d_bytes_per_step": 2 * B * S * 8,
                 "d2h_bytes_per_step": B * row_bytes + 4, "ms_per_step": wall_s * 1e3 / K},
-        "clocks": clocks, "store": "bf16 rows (model dtype)", "model": "hf-llama-32L-d4096" if not args.small else "small",
+        "clocks": clocks, "arm": {"store": "bf16 rows (model dtype)", "model_impl": "transformers LlamaForCausalLM"},
+        "model": "llama-32L-d4096" if not args.small else "small",
     }
 
 
@@ -281,10 +285,17 @@ def main():
 
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-    try:
-        res = (run_reference if args.impl == "reference" else run_ours)(args, rank, local_rank, world)
-    finally:
-        pass
+    res = (run_reference if args.impl == "reference" else run_ours)(args, rank, local_rank, world)
+    extras = None
+    which = tuple(w for w in args.extra.split(",") if w)
+    if which and "unavailable" not in res and not args.small:
+        import gc
+
+        gc.collect()
+        torch.cuda.empty_cache()
+        from benchmarks.extra_metrics import run_extras
+
+        extras = run_extras(args.impl, rank, local_rank, world, which)
     if rank == 0:
         if "unavailable" in res:
             print(json.dumps({"impl": args.impl, "unavailable": res["unavailable"]}))
@@ -296,10 +307,12 @@ def main():
                 "data": "synthetic Zipf(s=1.1) token ids, random-init weights", "impl": args.impl,
                 "config": {"model": res["model"], "global_batch": world * args.seqs, "seq_len": args.seq_len,
                            "parallelism": f"dp{world}", "projection_dim": 16, "normalizer": "adafactor",
-                           "store": res["store"],
+                           "store": "16-bit rows on disk",
                            "l2": "inputs larger than L2 (activations of one step exceed 126 MB many times)"},
-                "e2e": res["e2e"], "gpu_launches": res["gpu_launches"], "clocks": res["clocks"],
+                "e2e": res["e2e"], "gpu_launches": res["gpu_launches"], "clocks": res["clocks"], "arm": res["arm"],
             }
+            if extras is not None:
+                out["extra"] = extras
             print(json.dumps(out))
     if world > 1:
         import torch.distributed as dist

@@ -176,8 +176,114 @@ def bench_linear_gemm(small: bool, iters: int):
     return out
 
 
+def bench_ce_bwd(small: bool, iters: int):
+    from bergson_b200.ops import native
+
+    T, V = (4096, 128256) if small else (16384, 128256)
+    z = torch.randn(T, V, device="cuda", dtype=torch.bfloat16)
+    t = torch.randint(0, V, (T,), device="cuda")
+    _, lse = native.ce_fwd(z, t, -100)
+    dl = torch.ones(T, device="cuda")
+    ms = _time(lambda: native.ce_bwd(z, t, lse, dl, -100), iters)
+    zr = z.clone().requires_grad_(True)
+
+    def ref():
+        zr.grad = None
+        torch.nn.functional.cross_entropy(zr, t, reduction="sum").backward()
+
+    return dict(kernel="ce_bwd", shape=[T, V], ms=ms, torch_ms=_time(ref, iters), bytes=2 * T * V * 2, flops=0)
+
+
+def bench_rmsnorm_bwd(small: bool, iters: int):
+    from bergson_b200.ops import native
+    from bergson_b200.ops.functional import rms_norm_ref
+
+    T, D = (32768, 4096) if small else (131072, 4096)
+    x = torch.randn(T, D, device="cuda", dtype=torch.bfloat16)
+    w = torch.ones(D, device="cuda", dtype=torch.bfloat16)
+    dy = torch.randn_like(x)
+    _, rstd = native.rmsnorm_fwd(x, w, 1e-5)
+    ms = _time(lambda: native.rmsnorm_bwd(dy, x, w, rstd, False), iters)
+    xr = x.clone().requires_grad_(True)
+
+    def ref():
+        xr.grad = None
+        rms_norm_ref(xr, w, 1e-5).backward(dy)
+
+    return dict(kernel="rmsnorm_bwd", shape=[T, D], ms=ms, torch_ms=_time(ref, iters), bytes=3 * T * D * 2, flops=0)
+
+
+def bench_adamw(small: bool, iters: int):
+    from bergson_b200.ops import native
+
+    n = (64 if small else 256) * 1024 * 1024
+    p, m, v = (torch.zeros(n, device="cuda") for _ in range(3))
+    g = torch.randn(n, device="cuda", dtype=torch.bfloat16)
+    pm = torch.zeros(n, device="cuda", dtype=torch.bfloat16)
+    ms = _time(lambda: native.adamw_step(p, m, v, g, pm, 3e-4, 0.9, 0.999, 1e-8, 0.0, 0.01, 1, 1.0), iters)
+    opt = torch.optim.AdamW([torch.nn.Parameter(torch.zeros(n, device="cuda"))], lr=3e-4, fused=True)
+    opt.param_groups[0]["params"][0].grad = g.float()
+    return dict(kernel="adamw_step", shape=[n], ms=ms, torch_ms=_time(opt.step, iters), bytes=n * (6 * 4 + 2 + 2), flops=0)
+
+
+def bench_contract(small: bool, iters: int):
+    """Per-example 16 x S x 16 contraction of the projected operands (deterministic order)."""
+    from bergson_b200.ops import native
+
+    N, S = (8, 2048) if small else (32, 2048)
+    gp = torch.randn(N * S, 16, device="cuda")
+    ap = torch.randn(N * S, 16, device="cuda")
+    acc = torch.zeros(N, 256, device="cuda")
+    ms = _time(lambda: native.proj_contract(gp, ap, acc, N, S, 16, 0), iters)
+    ref = _time(lambda: torch.bmm(gp.view(N, S, 16).mT, ap.view(N, S, 16)), iters)
+    return dict(kernel="proj_contract", shape=[N, S, 16], ms=ms, torch_ms=ref, bytes=2 * N * S * 16 * 4, flops=2 * N * S * 256)
+
+
+def bench_rotary(small: bool, iters: int):
+    from bergson_b200.ops import native
+    from bergson_b200.ops.functional import rotary_ref, rotary_tables
+
+    B, S, H, D = (4, 2048, 32, 128) if small else (8, 2048, 32, 128)
+    x = torch.randn(B, S, H, D, device="cuda", dtype=torch.bfloat16)
+    cos, sin = rotary_tables(S, D, 500000.0, x.device)
+    ms = _time(lambda: native.rotary(x, cos, sin, D, False), iters)
+    return dict(kernel="rotary", shape=[B, S, H, D], ms=ms, torch_ms=_time(lambda: rotary_ref(x, cos, sin, D), iters),
+                bytes=2 * x.numel() * 2, flops=0)
+
+
+def bench_swiglu(small: bool, iters: int):
+    from bergson_b200.ops import native
+
+    T, F_ = (4096, 14336) if small else (16384, 14336)
+    g = torch.randn(T, F_, device="cuda", dtype=torch.bfloat16)
+    u = torch.randn_like(g)
+    dy = torch.randn_like(g)
+    ms = _time(lambda: native.swiglu_bwd(dy, g, u), iters)
+    ref = _time(lambda: torch.nn.functional.silu(g) * u, iters)
+    return dict(kernel="swiglu_bwd", shape=[T, F_], ms=ms, torch_ms=ref, bytes=5 * T * F_ * 2, flops=0,
+                note="torch_ms is the forward silu(g) * u composition (3 tensor passes), for scale only")
+
+
+def bench_gemm_case(small: bool, iters: int):
+    """One Linear forward and one input-gradient product on the wide GEMM (profiling case)."""
+    from bergson_b200.ops import native
+
+    M, N, K = (8192, 4096, 4096) if small else (16384, 4096, 4096)
+    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    bk = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
+    bm = torch.randn(K, N, device="cuda", dtype=torch.bfloat16)
+    d = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+    ms = _time(lambda: native.gemm(a, bk, False, False, d, False, None, False, None, 2, wide=True), iters)
+    ms2 = _time(lambda: native.gemm(a, bm, False, True, d, False, None, False, None, 2, wide=True), iters)
+    ref = _time(lambda: torch.matmul(a, bk.T, out=d), iters)
+    return dict(kernel="gemm_wide", shape=[M, N, K], ms=ms, ms_dgrad=ms2, torch_ms=ref, bytes=(M * K + N * K + M * N) * 2,
+                flops=2 * M * N * K)
+
+
 BENCHES = {"proj_right": bench_proj_right, "proj_left_outer": bench_proj_left_outer, "cov_syrk": bench_cov_syrk,
-           "tn_gemm": bench_tn_gemm, "ce_fwd": bench_ce, "rmsnorm_fwd": bench_rmsnorm, "linear_gemm": bench_linear_gemm}
+           "tn_gemm": bench_tn_gemm, "ce_fwd": bench_ce, "rmsnorm_fwd": bench_rmsnorm, "linear_gemm": bench_linear_gemm, "ce_bwd": bench_ce_bwd,
+           "rmsnorm_bwd": bench_rmsnorm_bwd, "adamw": bench_adamw, "proj_contract": bench_contract, "rotary": bench_rotary,
+           "swiglu_bwd": bench_swiglu, "gemm_case": bench_gemm_case}
 
 
 def main():

@@ -1,10 +1,12 @@
-"""TrackStar pipeline: value Hessian -> query Hessian -> mix -> query build -> score
-(reference ``bergson/cli/trackstar.py:43-176``)."""
+"""TrackStar pipeline: gradient-similarity attribution with the gradients of both sides
+whitened by a mixture of the training ("value") and query autocorrelation Hessians.
+
+Outputs under the run directory: ``value_hessian/``, ``query_hessian/``, ``mixed_hessian/``
+(the latter two only when ``mix_hessians``), ``query/`` (preconditioned query gradients) and
+``scores/``.  With ``resume`` a step whose output directory exists is not repeated.
+"""
 
 from __future__ import annotations
-
-from copy import deepcopy
-from pathlib import Path
 
 from ..build import build
 from ..config.config import HessianConfig, IndexConfig, TrackstarConfig
@@ -13,20 +15,12 @@ from ..distributed import parent_barrier
 from ..hessians.hessian_approximations import approximate_hessians
 from ..process_grads import mix_autocorrelation_matrices
 from ..score.score import score_dataset
-from ..utils.worker_utils import validate_run_path
+from .steps import Step, StepRunner, derive
 
 
-def _limit_split_for_hess(cfg: IndexConfig, n: int | None) -> None:
-    """Restrict the split to its first ``n`` rows for Hessian fitting."""
-    if n is not None:
-        cfg.data.split = f"{cfg.data.split.split('[')[0]}[:{n}]"
-
-
-def _step_complete(path: str, resume: bool) -> bool:
-    if resume and Path(path).exists():
-        print(f"  Skipping (output exists at {path})")
-        return True
-    return False
+def _head_of_split(split: str, n: int | None) -> str:
+    """``split`` restricted to its first ``n`` rows (any earlier slice is replaced)."""
+    return split if n is None else f"{split.partition('[')[0]}[:{n}]"
 
 
 def trackstar(index_cfg: IndexConfig, trackstar_cfg: TrackstarConfig):
@@ -35,65 +29,55 @@ def trackstar(index_cfg: IndexConfig, trackstar_cfg: TrackstarConfig):
     if index_cfg.projection_dim == 0:
         raise ValueError("Trackstar scores via compressed random-projected gradients and requires a nonzero "
                          "index_cfg.projection_dim; got 0.")
-    run = index_cfg.run_path
-    value_h, query_h, mixed_h = f"{run}/value_hessian", f"{run}/query_hessian", f"{run}/mixed_hessian"
-    query_path, scores_path = f"{run}/query", f"{run}/scores"
-    resume = trackstar_cfg.resume
-    hess_cfg = HessianConfig(method="autocorrelation")
+    root = index_cfg.run_path
+    out = {k: f"{root}/{k}" for k in ("value_hessian", "query_hessian", "mixed_hessian", "query", "scores")}
+    tc = trackstar_cfg
+    runner = StepRunner(resume=tc.resume, protocol="exists")
+    autocorr = HessianConfig(method="autocorrelation")
+    mixing = tc.mix_hessians
+    # Every later step whitens with the mixed Hessian, or with the value Hessian alone.
+    tc.preprocess_cfg.hessian_path = out["mixed_hessian"] if mixing else out["value_hessian"]
 
-    def validate(cfg: IndexConfig):
-        if not (resume and cfg.partial_run_path.exists()):
-            validate_run_path(cfg)
+    def fit_autocorrelation(where: str, data):
+        def action():
+            cfg = derive(index_cfg, run_path=where, data=data)
+            cfg.data.split = _head_of_split(cfg.data.split, tc.stats_sample_size)
+            runner.check_run_path(cfg)
+            save_run_config(Hessian(hessian_cfg=autocorr, index_cfg=cfg), cfg.partial_run_path)
+            approximate_hessians(cfg, autocorr)
+        return action
 
-    print("Step 1/5: Computing hessians on value dataset...")
-    if not _step_complete(value_h, resume):
-        c = deepcopy(index_cfg)
-        c.run_path = value_h
-        _limit_split_for_hess(c, trackstar_cfg.stats_sample_size)
-        validate(c)
-        save_run_config(Hessian(hessian_cfg=hess_cfg, index_cfg=c), c.partial_run_path)
-        approximate_hessians(c, hess_cfg)
+    def mix():
+        if index_cfg.distributed._node_rank == 0:
+            k = tc.target_downweight_components
+            save_run_config(Mix(query_path=out["query_hessian"], index_path=out["value_hessian"],
+                                output_path=out["mixed_hessian"], target_downweight_components=k), out["mixed_hessian"])
+            mix_autocorrelation_matrices(out["query_hessian"], out["value_hessian"], out["mixed_hessian"], k)
+        parent_barrier(index_cfg.distributed)
 
-    if not trackstar_cfg.mix_hessians:
-        print("Steps 2-3/5: Skipped (mix_hessians=false); using the value hessian.")
-        pre_path = value_h
-    else:
-        print("Step 2/5: Computing hessians on query dataset...")
-        if not _step_complete(query_h, resume):
-            c = deepcopy(index_cfg)
-            c.run_path, c.data = query_h, deepcopy(trackstar_cfg.query)
-            _limit_split_for_hess(c, trackstar_cfg.stats_sample_size)
-            validate(c)
-            save_run_config(Hessian(hessian_cfg=hess_cfg, index_cfg=c), c.partial_run_path)
-            approximate_hessians(c, hess_cfg)
-        print("Step 3/5: Mixing hessians...")
-        if not _step_complete(mixed_h, resume) and index_cfg.distributed._node_rank == 0:
-            k = trackstar_cfg.target_downweight_components
-            save_run_config(Mix(query_path=query_h, index_path=value_h, output_path=mixed_h,
-                                target_downweight_components=k), mixed_h)
-            mix_autocorrelation_matrices(query_h, value_h, mixed_h, k)
-        pre_path = mixed_h
-    parent_barrier(index_cfg.distributed)
-    trackstar_cfg.preprocess_cfg.hessian_path = pre_path
+    def build_query():
+        cfg = derive(index_cfg, run_path=out["query"], data=tc.query)
+        if tc.preprocess_cfg.aggregation != "none" and cfg.attribute_tokens:
+            print("  aggregated queries are per sequence: token attribution is switched off on the query side")
+            cfg.attribute_tokens = False
+        runner.check_run_path(cfg)
+        save_run_config(Build(cfg, tc.preprocess_cfg), cfg.partial_run_path)
+        build(cfg, tc.preprocess_cfg)
 
-    print("Step 4/5: Building query gradient index...")
-    if not _step_complete(query_path, resume):
-        c = deepcopy(index_cfg)
-        c.run_path, c.data = query_path, deepcopy(trackstar_cfg.query)
-        if trackstar_cfg.preprocess_cfg.aggregation != "none" and c.attribute_tokens:
-            print("Query aggregation is not compatible with query-side token attribution; "
-                  "query gradients are collected per sequence.")
-            c.attribute_tokens = False
-        validate(c)
-        save_run_config(Build(c, trackstar_cfg.preprocess_cfg), c.partial_run_path)
-        build(c, trackstar_cfg.preprocess_cfg)
+    def score():
+        cfg = derive(index_cfg, run_path=out["scores"])
+        tc.score_cfg.query_path, tc.score_cfg.higher_is_better = out["query"], True
+        runner.check_run_path(cfg)
+        save_run_config(Score(tc.score_cfg, cfg, tc.preprocess_cfg), cfg.partial_run_path)
+        score_dataset(cfg, tc.score_cfg, tc.preprocess_cfg)
 
-    print("Step 5/5: Scoring value dataset...")
-    if not _step_complete(scores_path, resume):
-        c = deepcopy(index_cfg)
-        c.run_path = scores_path
-        trackstar_cfg.score_cfg.query_path = query_path
-        trackstar_cfg.score_cfg.higher_is_better = True
-        validate(c)
-        save_run_config(Score(trackstar_cfg.score_cfg, c, trackstar_cfg.preprocess_cfg), c.partial_run_path)
-        score_dataset(c, trackstar_cfg.score_cfg, trackstar_cfg.preprocess_cfg)
+    note = "mix_hessians=false: the value Hessian is used alone"
+    return runner.run([
+        Step("autocorrelation Hessian of the value data", out["value_hessian"],
+             fit_autocorrelation(out["value_hessian"], index_cfg.data)),
+        Step("autocorrelation Hessian of the query data", out["query_hessian"],
+             fit_autocorrelation(out["query_hessian"], tc.query), enabled=mixing, skip_note=note),
+        Step("mixture of the two Hessians", out["mixed_hessian"], mix, enabled=mixing, skip_note=note),
+        Step("query gradient index", out["query"], build_query),
+        Step("value data scored against the queries", out["scores"], score),
+    ])

@@ -13,6 +13,7 @@ from __future__ import annotations
 
 import gc
 import os
+from contextlib import nullcontext
 from dataclasses import dataclass
 
 import torch
@@ -26,6 +27,10 @@ from ..collector.collector import HookCollectorBase
 from ..utils.logger import get_logger
 from ..utils.utils import assert_type, get_device
 from .sharded_computation import ShardedMul, shard_bounds
+
+
+# Factors decomposed concurrently per rank (one host thread and one stream each).
+EIGH_CONCURRENCY = int(os.environ.get("BERGSON_B200_EIGH_CONCURRENCY", "6"))
 
 
 def fair_distribute_by_cost(key_dimensions: dict[str, int], world_size: int) -> list[list[str]]:
@@ -175,17 +180,46 @@ def compute_eigendecomposition(covariance_path: str, total_processed) -> dict[st
 
     vecs: dict[str, Tensor] = {}
     vals: dict[str, Tensor] = {}
-    for key in fair_distribute_by_cost(dims, world)[rank]:
-        m = _compute_full_matrix(key, covariance_path, rank, world).to(torch.float64) / total
-        m = (m + m.T) / 2
-        if not torch.isfinite(m).all():
-            raise ValueError(f"Covariance matrix for {key} contains NaNs or Infs. Consider using fp32.")
-        try:
-            w, q = torch.linalg.eigh(m)
-        except Exception as e:
-            raise RuntimeError(f"Eigendecomposition failed for {key}") from e
-        vecs[key] = q.to(out_dtype).cpu().contiguous()
-        vals[key] = w.to(out_dtype).cpu().contiguous()
+
+    def decompose(key: str, stream) -> None:
+        ctx = torch.cuda.stream(stream) if stream is not None else nullcontext()
+        with ctx:
+            m = _compute_full_matrix(key, covariance_path, rank, world).to(torch.float64) / total
+            m = (m + m.T) / 2
+            if not torch.isfinite(m).all():
+                raise ValueError(f"Covariance matrix for {key} contains NaNs or Infs. Consider using fp32.")
+            try:
+                w, q = torch.linalg.eigh(m)
+            except Exception as e:
+                raise RuntimeError(f"Eigendecomposition failed for {key}") from e
+            vecs[key] = q.to(out_dtype).cpu().contiguous()
+            vals[key] = w.to(out_dtype).cpu().contiguous()
+
+    mine = fair_distribute_by_cost(dims, world)[rank]
+    if torch.device(device).type == "cuda" and len(mine) > 1:
+        # A dense symmetric eigensolver of a few thousand rows cannot fill the GPU on its own (long
+        # chains of small kernels with host round trips in between): several factors are
+        # decomposed at once, each on its own stream from its own host thread.
+        from concurrent.futures import ThreadPoolExecutor
+
+        workers = min(EIGH_CONCURRENCY, len(mine))
+        main = torch.cuda.current_stream()
+        streams = [torch.cuda.Stream() for _ in range(workers)]
+        for st in streams:
+            st.wait_stream(main)
+
+        def work(i: int) -> None:
+            torch.cuda.set_device(torch.device(device))
+            for key in mine[i::workers]:
+                decompose(key, streams[i])
+
+        with ThreadPoolExecutor(max_workers=workers) as pool:
+            list(pool.map(work, range(workers)))
+        for st in streams:
+            main.wait_stream(st)
+    else:
+        for key in mine:
+            decompose(key, None)
 
     vecs = _gather_and_shard_along_dim_0(vecs, {k: (m, m) for k, m in dims.items()}, out_dtype, rank, world, device)
     vals = _gather_and_shard_along_dim_0(vals, {k: (m,) for k, m in dims.items()}, out_dtype, rank, world, device)

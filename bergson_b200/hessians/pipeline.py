@@ -1,38 +1,27 @@
-"""EK-FAC influence pipeline: query build -> factor fit -> inverse-Hessian apply -> score
-(reference ``bergson/hessians/pipeline.py:46-150``)."""
+"""EK-FAC influence pipeline.
+
+Four steps under one run directory, each restartable (``.part`` / promote protocol):
+
+====================  ===================================================================
+``query/``            gradient(s) of the query set at full resolution (projection 0),
+                      aggregated as ``query_aggregation`` says
+``hessian/<method>``  Kronecker factors of the training set, their eigendecomposition and
+                      (EK-FAC) the corrected eigenvalues
+``<method>_query/``   the query gradient(s) multiplied by the inverse of that Hessian
+``scores/``           inner products of every training example's gradient with them
+====================  ===================================================================
+"""
 
 from __future__ import annotations
 
-import time
-from contextlib import contextmanager
-from copy import deepcopy
-
 from ..build import build
+from ..cli.steps import Step, StepRunner, derive
 from ..config.config import HessianConfig, HessianPipelineConfig, IndexConfig, PreprocessConfig, ScoreConfig
 from ..config.config_io import save_run_config
 from ..distributed import launch_distributed_run
 from ..score.score import score_dataset
-from ..utils.step_state import prepare_step
-from ..utils.worker_utils import validate_run_path
 from .apply_hessian import EkfacConfig, apply_worker
 from .hessian_approximations import approximate_hessians
-
-
-def _step_complete(path: str, resume: bool) -> bool:
-    if prepare_step(path, resume=resume):
-        return False
-    print(f"  Skipping (already complete at {path})")
-    return True
-
-
-@contextmanager
-def _timed(label: str, durations: dict[str, float]):
-    t0 = time.perf_counter()
-    try:
-        yield
-    finally:
-        durations[label] = time.perf_counter() - t0
-        print(f"  [{label}] took {durations[label]:.1f}s")
 
 
 def hessian_pipeline(index_cfg: IndexConfig, hessian_cfg: HessianConfig, score_cfg: ScoreConfig,
@@ -42,57 +31,46 @@ def hessian_pipeline(index_cfg: IndexConfig, hessian_cfg: HessianConfig, score_c
     if preprocess_cfg.unit_normalize:
         raise ValueError("preprocess_cfg.unit_normalize (cosine similarity) is not supported with "
                          "Kronecker-factored Hessians.")
-    run, method = index_cfg.run_path, hessian_cfg.method
-    query_path, hessian_path = f"{run}/query", f"{run}/hessian"
-    transformed, scores_path = f"{run}/{method}_query", f"{run}/scores"
-    resume = hessian_pipeline_cfg.resume
-    durations: dict[str, float] = {}
+    root, method = index_cfg.run_path, hessian_cfg.method
+    out = {"query": f"{root}/query", "hessian": f"{root}/hessian", "ivhp": f"{root}/{method}_query",
+           "scores": f"{root}/scores"}
+    factors = f"{out['hessian']}/{method}"
+    runner = StepRunner(resume=hessian_pipeline_cfg.resume, protocol="promote")
 
-    def validate(cfg: IndexConfig):
-        if not (resume and cfg.partial_run_path.exists()):
-            validate_run_path(cfg)
+    def build_query():
+        cfg = derive(index_cfg, run_path=out["query"], data=hessian_pipeline_cfg.query, projection_dim=0)
+        runner.check_run_path(cfg)
+        pre = PreprocessConfig(aggregation=hessian_pipeline_cfg.query_aggregation)
+        save_run_config(Build(cfg, pre), cfg.partial_run_path)
+        build(cfg, pre)
 
-    agg = hessian_pipeline_cfg.query_aggregation
-    print(f"Step 1/4: Building query gradient(s) (aggregation={agg})...")
-    if not _step_complete(query_path, resume):
-        with _timed("step1_build_query", durations):
-            qcfg = deepcopy(index_cfg)
-            qcfg.run_path, qcfg.data, qcfg.projection_dim = query_path, hessian_pipeline_cfg.query, 0
-            validate(qcfg)
-            qpre = PreprocessConfig(aggregation=agg)
-            save_run_config(Build(qcfg, qpre), qcfg.partial_run_path)
-            build(qcfg, qpre)
+    def fit_factors():
+        cfg = derive(index_cfg, run_path=factors)
+        runner.check_run_path(cfg)
+        approximate_hessians(cfg, hessian_cfg)
 
-    print(f"Step 2/4: Fitting {method} factors on training data...")
-    if not _step_complete(hessian_path, resume):
-        with _timed("step2_fit_hessian", durations):
-            hcfg = deepcopy(index_cfg)
-            hcfg.run_path = f"{hessian_path}/{method}"
-            validate(hcfg)
-            approximate_hessians(hcfg, hessian_cfg)
+    def apply_inverse():
+        ecfg = EkfacConfig(hessian_method_path=factors, gradient_path=out["query"], run_path=out["ivhp"],
+                           ev_correction=hessian_cfg.ev_correction, projection_dim=index_cfg.projection_dim,
+                           projection_type=index_cfg.projection_type)
+        launch_distributed_run("apply_hessian", apply_worker, [ecfg, hessian_pipeline_cfg.inversion_cfg],
+                               index_cfg.distributed)
 
-    print(f"Step 3/4: Applying {method} inverse Hessian to the query gradient(s)...")
-    if not _step_complete(transformed, resume):
-        with _timed("step3_apply", durations):
-            ecfg = EkfacConfig(
-                hessian_method_path=f"{hessian_path}/{method}", gradient_path=query_path, run_path=transformed,
-                ev_correction=hessian_cfg.ev_correction, projection_dim=index_cfg.projection_dim,
-                projection_type=index_cfg.projection_type,
-            )
-            launch_distributed_run("apply_hessian", apply_worker, [ecfg, hessian_pipeline_cfg.inversion_cfg],
-                                   index_cfg.distributed)
+    def score():
+        cfg = derive(index_cfg, run_path=out["scores"])
+        score_cfg.query_path, score_cfg.higher_is_better = out["ivhp"], True
+        runner.check_run_path(cfg)
+        save_run_config(Score(score_cfg, cfg, preprocess_cfg), cfg.partial_run_path)
+        score_dataset(cfg, score_cfg, preprocess_cfg)
 
-    print("Step 4/4: Scoring training data against transformed query...")
-    if not _step_complete(scores_path, resume):
-        with _timed("step4_score", durations):
-            scfg = deepcopy(index_cfg)
-            scfg.run_path = scores_path
-            score_cfg.query_path = transformed
-            score_cfg.higher_is_better = True
-            validate(scfg)
-            save_run_config(Score(score_cfg, scfg, preprocess_cfg), scfg.partial_run_path)
-            score_dataset(scfg, score_cfg, preprocess_cfg)
-    print(f"Done! Scores saved to: {scores_path}")
-    if durations:
-        print(f"Step timings (s): {durations} | total {sum(durations.values()):.1f}s")
-    return durations
+    timings = runner.run([
+        Step(f"query gradient(s), aggregation={hessian_pipeline_cfg.query_aggregation}", out["query"], build_query,
+             key="step1_build_query"),
+        Step(f"{method} factors of the training data", out["hessian"], fit_factors, key="step2_fit_hessian"),
+        Step(f"inverse {method} Hessian applied to the query gradient(s)", out["ivhp"], apply_inverse, key="step3_apply"),
+        Step("training data scored against the transformed query", out["scores"], score, key="step4_score"),
+    ])
+    print(f"EK-FAC pipeline finished; scores at {out['scores']}")
+    if timings:
+        print(f"seconds per step: {timings} (total {sum(timings.values()):.1f})")
+    return timings

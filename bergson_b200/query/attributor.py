@@ -145,6 +145,43 @@ class Attributor:
                 print("Warning: zero-norm rows in the index; their cosine scores are set to 0")
             self.inv_norms = torch.where(bad, torch.zeros_like(inv), inv)
 
+    @classmethod
+    def from_rows(cls, rows: Tensor, grad_sizes: dict[str, int], *, unit_norm: bool = False, sharded: bool = False,
+                  row_offset: int = 0, total_rows: int | None = None, group=None,
+                  processor: GradientProcessor | None = None) -> "Attributor":
+        """An attributor over rows that are already on a device (``[n, sum(grad_sizes)]``, module
+        blocks in ``grad_sizes`` order), without a store on disk.  With ``sharded`` the tensor is
+        this rank's slice ``[row_offset, row_offset + n)`` of a store of ``total_rows`` rows."""
+        self = cls.__new__(cls)
+        self.device, self.dtype, self.unit_norm = str(rows.device), rows.dtype, unit_norm
+        self.sharded, self.group, self.row_lo = sharded, group, row_offset
+        self.inversion_cfg = InversionConfig()
+        self.faiss_index = None
+        self.processor = processor or GradientProcessor()
+        self.precondition, self.preconditioner = "none", None
+        self.ordered_modules = list(grad_sizes)
+        self.offsets = column_offsets(grad_sizes)
+        self.store = rows.contiguous()
+        self.N = total_rows if total_rows is not None else rows.shape[0]
+        self.inv_norms = None
+        if sharded:
+            import torch.distributed as dist
+
+            self.shard_rank, self.shard_world = dist.get_rank(group), dist.get_world_size(group)
+        if unit_norm:
+            from ..ops.functional import use_fused
+
+            if use_fused(self.store):
+                from ..ops import native
+
+                sq = torch.zeros(self.store.shape[0], device=self.store.device, dtype=torch.float32)
+                native.row_sumsq(self.store, sq)
+            else:
+                sq = self.store.float().pow(2).sum(1)
+            inv = sq.rsqrt()
+            self.inv_norms = torch.where(torch.isfinite(inv), inv, torch.zeros_like(inv))
+        return self
+
     @property
     def grads(self) -> dict[str, Tensor]:
         """Per-module views of the resident store (unit-normalised rows under ``unit_norm``)."""
