@@ -26,16 +26,24 @@ _DTYPES = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32,
 
 
 def validate_run_path(index_cfg: IndexConfig):
-    """Refuse to overwrite an existing run unless ``overwrite`` (rank 0 only)."""
-    if index_cfg.distributed.rank != 0:
-        return
-    for path in (Path(index_cfg.run_path), Path(index_cfg.partial_run_path)):
-        if not path.exists():
-            continue
-        if index_cfg.overwrite:
-            shutil.rmtree(path)
-        else:
-            raise FileExistsError(f"Run path {path} already exists. Use --overwrite to overwrite it.")
+    """Refuse to overwrite an existing run unless ``overwrite``.  The check runs on global rank
+    0 only; with several nodes the other nodes' parents wait for it at a barrier, so that none
+    of them can create the (shared) partial directory before it has been checked."""
+    multi_node = index_cfg.distributed.nnode > 1
+    try:
+        if index_cfg.distributed.rank == 0:
+            for path in (Path(index_cfg.run_path), Path(index_cfg.partial_run_path)):
+                if not path.exists():
+                    continue
+                if index_cfg.overwrite:
+                    shutil.rmtree(path)
+                else:
+                    raise FileExistsError(f"Run path {path} already exists. Use --overwrite to overwrite it.")
+    finally:
+        if multi_node:
+            from ..distributed import parent_barrier
+
+            parent_barrier(index_cfg.distributed)
 
 
 def create_processor(model, cfg: IndexConfig, target_modules: set[str] | None = None) -> GradientProcessor:
