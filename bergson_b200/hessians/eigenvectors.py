@@ -203,6 +203,9 @@ def compute_eigendecomposition(covariance_path: str, total_processed) -> dict[st
         from concurrent.futures import ThreadPoolExecutor
 
         workers = min(EIGH_CONCURRENCY, len(mine))
+        # torch loads its dense linear-algebra backend lazily and not thread-safely: trigger that
+        # from this thread before the workers start.
+        torch.linalg.eigh(torch.eye(2, device=device, dtype=torch.float64))
         main = torch.cuda.current_stream()
         streams = [torch.cuda.Stream() for _ in range(workers)]
         for st in streams:

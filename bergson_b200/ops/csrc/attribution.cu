@@ -319,33 +319,39 @@ constexpr int kContractChunk = 64;  // tokens staged per step and group
 template <int P>
 __global__ void __launch_bounds__(kContractThreads)
 proj_contract_kernel(const float* __restrict__ g_proj, const float* __restrict__ a_proj, float* __restrict__ acc,
-                     int S, int ldp, long ld, long col_off) {
+                     float* __restrict__ partials, int* __restrict__ counters, int S, int ldp, long ld, long col_off) {
+  // grid = (examples, splits): CTA (n, k) contracts the k-th slice of example n's tokens into a
+  // p x p partial; the last CTA of an example to finish adds the partials up in slice order (so
+  // the result does not depend on which CTA that was) and writes the block.
   constexpr int kOut = P * P;
-  constexpr int kGroups = kOut >= kContractThreads ? 1 : (kContractThreads / kOut > 4 ? 4 : kContractThreads / kOut);  // token groups
+  constexpr int kGroups = kOut >= kContractThreads ? 1 : (kContractThreads / kOut > 4 ? 4 : kContractThreads / kOut);
   constexpr int kPerThread = kOut >= kContractThreads ? kOut / kContractThreads : 1;
   __shared__ float gs[kGroups][kContractChunk][P + 1];
   __shared__ float as[kGroups][kContractChunk][P + 1];
   __shared__ float red[kGroups][kOut >= kContractThreads ? 1 : kOut];
-  const int n = blockIdx.x;
+  __shared__ int is_last;
+  const int n = blockIdx.x, split = blockIdx.y, splits = gridDim.y;
   const int tid = threadIdx.x;
   const int grp = kOut >= kContractThreads ? 0 : tid / kOut;
   const int o0 = kOut >= kContractThreads ? tid * kPerThread : tid % kOut;
+  const int per_split = (S + splits - 1) / splits;
+  const int s_begin = split * per_split;
+  const int s_end = s_begin + per_split < S ? s_begin + per_split : S;
   const float* g0 = g_proj + long(n) * S * ldp;
   const float* a0 = a_proj + long(n) * S * ldp;
   float sum[kPerThread];
 #pragma unroll
   for (int q = 0; q < kPerThread; ++q) sum[q] = 0.f;
-  // Token range of this group, walked in chunks that the whole CTA stages together.
-  const int per_group = (S + kGroups - 1) / kGroups;
+  const int span = s_end > s_begin ? s_end - s_begin : 0;
+  const int per_group = (span + kGroups - 1) / kGroups;
   for (int base = 0; base < per_group; base += kContractChunk) {
-    // cooperative load: every thread copies elements of every group's chunk
     for (int e = tid; e < kGroups * kContractChunk * P; e += kContractThreads) {
       const int gq = e / (kContractChunk * P);
       const int r = (e / P) % kContractChunk;
       const int c = e % P;
       const int s_local = base + r;
-      const int s = gq * per_group + s_local;
-      const bool ok = s_local < per_group && s < S;
+      const int s = s_begin + gq * per_group + s_local;
+      const bool ok = s_local < per_group && s < s_end;
       gs[gq][r][c] = ok ? g0[long(s) * ldp + c] : 0.f;
       as[gq][r][c] = ok ? a0[long(s) * ldp + c] : 0.f;
     }
@@ -362,19 +368,37 @@ proj_contract_kernel(const float* __restrict__ g_proj, const float* __restrict__
     }
     __syncthreads();
   }
-  float* dst = acc + long(n) * ld + col_off;
+  // this CTA's partial, groups added in fixed order
+  float* part = partials + (long(n) * splits + split) * kOut;
   if constexpr (kOut >= kContractThreads) {
 #pragma unroll
-    for (int q = 0; q < kPerThread; ++q) dst[o0 + q] = sum[0 + q];
+    for (int q = 0; q < kPerThread; ++q) part[o0 + q] = sum[q];
   } else {
     if (grp < kGroups) red[grp][o0] = sum[0];
     __syncthreads();
     if (tid < kOut) {
       float t = 0.f;
 #pragma unroll
-      for (int gq = 0; gq < kGroups; ++gq) t += red[gq][tid];  // fixed order
-      dst[tid] = t;
+      for (int gq = 0; gq < kGroups; ++gq) t += red[gq][tid];
+      part[tid] = t;
     }
+  }
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    const int ticket = atomicAdd(&counters[n], 1);
+    is_last = ticket == splits - 1;
+    if (is_last) counters[n] = 0;  // ready for the next launch
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  float* dst = acc + long(n) * ld + col_off;
+  const float* all = partials + long(n) * splits * kOut;
+  for (int o = tid; o < kOut; o += kContractThreads) {
+    float t = 0.f;
+    for (int k = 0; k < splits; ++k) t += __ldcg(all + long(k) * kOut + o);  // slice order
+    dst[o] = t;
   }
 }
 
@@ -393,14 +417,20 @@ __global__ void proj_token_rows_kernel(const float* __restrict__ g_proj, const f
 
 }  // namespace bgn
 
-extern "C" int bgn_proj_contract(const float* g_proj, const float* a_proj, float* acc, int N, int S, int p, int ldp,
-                                 long ld, long col_off, cudaStream_t stream) {
-  if (N <= 0 || S <= 0 || ldp < p) return int(cudaErrorInvalidValue);
+extern "C" int bgn_proj_contract_splits(int S) {
+  int splits = (S + 255) / 256;
+  return splits < 1 ? 1 : (splits > 16 ? 16 : splits);
+}
+
+extern "C" int bgn_proj_contract(const float* g_proj, const float* a_proj, float* acc, float* partials, int* counters,
+                                 int N, int S, int p, int ldp, long ld, long col_off, cudaStream_t stream) {
+  if (N <= 0 || S <= 0 || ldp < p || !partials || !counters) return int(cudaErrorInvalidValue);
+  const dim3 grid(N, bgn_proj_contract_splits(S));
   switch (p) {
-    case 8: proj_contract_kernel<8><<<N, kContractThreads, 0, stream>>>(g_proj, a_proj, acc, S, ldp, ld, col_off); break;
-    case 16: proj_contract_kernel<16><<<N, kContractThreads, 0, stream>>>(g_proj, a_proj, acc, S, ldp, ld, col_off); break;
-    case 32: proj_contract_kernel<32><<<N, kContractThreads, 0, stream>>>(g_proj, a_proj, acc, S, ldp, ld, col_off); break;
-    case 64: proj_contract_kernel<64><<<N, kContractThreads, 0, stream>>>(g_proj, a_proj, acc, S, ldp, ld, col_off); break;
+    case 8: proj_contract_kernel<8><<<grid, kContractThreads, 0, stream>>>(g_proj, a_proj, acc, partials, counters, S, ldp, ld, col_off); break;
+    case 16: proj_contract_kernel<16><<<grid, kContractThreads, 0, stream>>>(g_proj, a_proj, acc, partials, counters, S, ldp, ld, col_off); break;
+    case 32: proj_contract_kernel<32><<<grid, kContractThreads, 0, stream>>>(g_proj, a_proj, acc, partials, counters, S, ldp, ld, col_off); break;
+    case 64: proj_contract_kernel<64><<<grid, kContractThreads, 0, stream>>>(g_proj, a_proj, acc, partials, counters, S, ldp, ld, col_off); break;
     default: return int(cudaErrorInvalidValue);
   }
   return int(cudaGetLastError());

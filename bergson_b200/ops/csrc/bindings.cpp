@@ -49,6 +49,21 @@ at::Tensor status_tensor(int device) {
   return it->second;
 }
 
+// Arrival counters of the contraction kernel: zero between launches (the kernel resets them), so
+// one buffer per device serves every call issued on one stream.
+at::Tensor contract_counters(int device, int64_t n) {
+  static std::mutex mu;
+  static std::map<int, at::Tensor> bufs;
+  std::lock_guard<std::mutex> lock(mu);
+  auto it = bufs.find(device);
+  if (it == bufs.end() || it->second.numel() < n) {
+    auto t = at::zeros({std::max<int64_t>(n, 256)}, at::TensorOptions().dtype(at::kInt).device(at::kCUDA, device));
+    if (it == bufs.end()) it = bufs.emplace(device, t).first;
+    else it->second = t;
+  }
+  return it->second;
+}
+
 int* status_ptr(const at::Tensor& like) { return status_tensor(like.get_device()).data_ptr<int>(); }
 
 }  // namespace
@@ -383,8 +398,12 @@ void proj_contract(at::Tensor g_proj, at::Tensor a_proj, at::Tensor acc, int64_t
   TORCH_CHECK(acc.is_cuda() && acc.scalar_type() == at::kFloat && acc.dim() == 2 && acc.stride(1) == 1 &&
               acc.size(0) >= n && col_off + p * p <= acc.size(1));
   c10::cuda::CUDAGuard guard(acc.device());
-  check(bgn_proj_contract(g_proj.data_ptr<float>(), a_proj.data_ptr<float>(), acc.data_ptr<float>(), (int)n, (int)s,
-                          (int)p, (int)g_proj.size(1), acc.stride(0), col_off, stream()), "proj_contract");
+  const int splits = bgn_proj_contract_splits((int)s);
+  auto partials = at::empty({n * splits * p * p}, acc.options());
+  auto counters = contract_counters(acc.get_device(), n);
+  check(bgn_proj_contract(g_proj.data_ptr<float>(), a_proj.data_ptr<float>(), acc.data_ptr<float>(),
+                          partials.data_ptr<float>(), counters.data_ptr<int>(), (int)n, (int)s, (int)p,
+                          (int)g_proj.size(1), acc.stride(0), col_off, stream()), "proj_contract");
 }
 
 void proj_token_rows(at::Tensor g_proj, at::Tensor a_proj, at::Tensor token_index, at::Tensor out, int64_t p,

@@ -266,6 +266,45 @@ __global__ void rotary_kernel(const T* __restrict__ x, const float* __restrict__
   }
 }
 
+// Vectorised form: one thread per 16-byte packet of the first half of the rotated prefix (it also
+// handles the matching packet of the second half) or per pass-through packet.  Needs the packet
+// width to divide rot / 2 and D - rot.
+template <typename T>
+__global__ void rotary_vec_kernel(const T* __restrict__ x, const float* __restrict__ cosT,
+                                  const float* __restrict__ sinT, T* __restrict__ y, long total, int S, int H, int D,
+                                  int rot, float sign) {
+  constexpr int V = Vec<T>::N;
+  const int half = rot >> 1;
+  const int rot_packets = half / V, pass_packets = (D - rot) / V;
+  const int per_head = rot_packets + pass_packets;
+  for (long idx = blockIdx.x * long(blockDim.x) + threadIdx.x; idx < total; idx += long(gridDim.x) * blockDim.x) {
+    const long head = idx / per_head;
+    const int k = int(idx - head * per_head);
+    const T* xp = x + head * D;
+    T* yp = y + head * D;
+    if (k < rot_packets) {
+      const int i = k * V;
+      const int s = int((head / H) % S);
+      const Vec<T> a = load_vec(xp + i), b = load_vec(xp + i + half);
+      const float* cp = cosT + long(s) * half + i;
+      const float* sp = sinT + long(s) * half + i;
+      Vec<T> oa, ob;
+#pragma unroll
+      for (int j = 0; j < V; ++j) {
+        const float c = __ldg(cp + j), sn = __ldg(sp + j) * sign;
+        const float av = to_float<T>(a.v[j]), bv = to_float<T>(b.v[j]);
+        oa.v[j] = from_float<T>(av * c - bv * sn);
+        ob.v[j] = from_float<T>(bv * c + av * sn);
+      }
+      store_vec(yp + i, oa);
+      store_vec(yp + i + half, ob);
+    } else {
+      const int i = rot + (k - rot_packets) * V;
+      store_vec(yp + i, load_vec(xp + i));
+    }
+  }
+}
+
 // ---- activations ----------------------------------------------------------------------
 
 __device__ __forceinline__ float sigmoidf_(float x) { return 1.f / (1.f + __expf(-x)); }
@@ -528,7 +567,15 @@ extern "C" int bgn_rotary(const void* x, const float* cosT, const float* sinT, v
   const long heads = B * S * H;
   const long total = heads * (D - rot / 2);
   BGN_DISPATCH(type, {
-    rotary_kernel<T><<<grid_for(total, 256), 256, 0, st>>>((const T*)x, cosT, sinT, (T*)y, total, S, H, D, rot, inverse ? -1.f : 1.f);
+    constexpr int V = Vec<T>::N;
+    const bool aligned = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 15) == 0;
+    if (aligned && (rot / 2) % V == 0 && (D - rot) % V == 0 && D % V == 0) {
+      const long packets = heads * ((rot / 2) / V + (D - rot) / V);
+      rotary_vec_kernel<T><<<grid_for(packets, 256), 256, 0, st>>>((const T*)x, cosT, sinT, (T*)y, packets, S, H, D, rot,
+                                                                   inverse ? -1.f : 1.f);
+    } else {
+      rotary_kernel<T><<<grid_for(total, 256), 256, 0, st>>>((const T*)x, cosT, sinT, (T*)y, total, S, H, D, rot, inverse ? -1.f : 1.f);
+    }
   });
   return int(cudaGetLastError());
 }

@@ -33,10 +33,13 @@ int bgn_tn_gemm_gathered(const void* a, const void* const* b, int world, float* 
                          long ldc, int fmt, int* status, cudaStream_t stream);
 
 // acc[n, col_off + i*p + j] = sum_s g_proj[n*S + s, i] * a_proj[n*S + s, j]  (overwrites; fixed
-// summation order).  g_proj / a_proj: fp32 [N*S, ldp] with p <= ldp meaningful columns;
-// p in {8, 16, 32, 64}.
-int bgn_proj_contract(const float* g_proj, const float* a_proj, float* acc, int N, int S, int p, int ldp,
-                      long ld, long col_off, cudaStream_t stream);
+// summation order: bitwise repeatable).  g_proj / a_proj: fp32 [N*S, ldp] with p <= ldp
+// meaningful columns; p in {8, 16, 32, 64}.  Scratch: `partials` holds
+// N * bgn_proj_contract_splits(S) * p * p floats (any contents), `counters` N ints that are zero
+// on entry and are left zero.
+int bgn_proj_contract_splits(int S);
+int bgn_proj_contract(const float* g_proj, const float* a_proj, float* acc, float* partials, int* counters,
+                      int N, int S, int p, int ldp, long ld, long col_off, cudaStream_t stream);
 
 // out[r, col_off + i*p + j] = g_proj[t, i] * a_proj[t, j] with t = token_index[r], r < rows.
 int bgn_proj_token_rows(const float* g_proj, const float* a_proj, const long* token_index, float* out,
