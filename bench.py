@@ -284,7 +284,10 @@ def main():
         import torch.distributed as dist
 
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+        from datetime import timedelta
+
+        # A short collective timeout: if one rank of a run fails, the others give up in minutes.
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank), timeout=timedelta(minutes=4))
     res = (run_reference if args.impl == "reference" else run_ours)(args, rank, local_rank, world)
     extras = None
     which = tuple(w for w in args.extra.split(",") if w)

@@ -97,26 +97,35 @@ def query_reference(rank: int, local_rank: int, world: int) -> dict:
     c = QUERY_CFG
     dev = torch.device("cuda", local_rank)
     base = Path("/dev/shm") if Path("/dev/shm").is_dir() else Path(tempfile.gettempdir())
-    tmp = base / f"ref_query_store_{rank}"
-    shutil.rmtree(tmp, ignore_errors=True)
-    tmp.mkdir(parents=True)
+    # One store shared by all ranks: the reference's create_index is collective (rank 0 creates the
+    # file, a barrier, every rank maps it), and its Attributor has no sharding -- each rank loads
+    # the whole store onto its own GPU and answers the same queries.
+    tmp = base / "ref_query_store"
+    if rank == 0:
+        shutil.rmtree(tmp, ignore_errors=True)
+        tmp.mkdir(parents=True)
+    _sync(dev)
     try:
         sizes = {f"m{i}": 256 for i in range(c["dim"] // 256)}
         mm = create_index(tmp, c["rows"], sizes, np.float16)
-        g = torch.Generator(device=dev).manual_seed(1234)
-        for lo in range(0, c["rows"], 8192):
-            n = min(8192, c["rows"] - lo)
-            mm[lo : lo + n] = torch.randn(n, c["dim"], device=dev, dtype=torch.float16, generator=g).cpu().numpy()
-        mm.flush()
+        if rank == 0:
+            g = torch.Generator(device=dev).manual_seed(1234)
+            for lo in range(0, c["rows"], 8192):
+                n = min(8192, c["rows"] - lo)
+                mm[lo : lo + n] = torch.randn(n, c["dim"], device=dev, dtype=torch.float16, generator=g).cpu().numpy()
+            mm.flush()
+            GradientProcessor(projection_dim=16).save(tmp)
         del mm
-        GradientProcessor(projection_dim=16).save(tmp)
+        _sync(dev)
         attr = Attributor(tmp, device=str(dev), dtype=torch.float16, unit_norm=True)
         gq = torch.Generator(device=dev).manual_seed(99)
         q = torch.randn(c["queries"], c["dim"], device=dev, dtype=torch.float16, generator=gq)
         queries = {n: q[:, i * 256 : (i + 1) * 256].contiguous() for i, n in enumerate(sizes)}
         ms = _timed(lambda: attr.search(queries, c["k"]), dev)
     finally:
-        shutil.rmtree(tmp, ignore_errors=True)
+        _sync(dev)
+        if rank == 0:
+            shutil.rmtree(tmp, ignore_errors=True)
     return {"metric": "query_scores_per_s", "value": c["rows"] * c["queries"] / (ms / 1e3), "unit": "scores/s",
             "ms_per_search": ms, "higher_is_better": True, "scaling": "strong", "config": dict(c, store="fp16, resident",
                                                                                                  scoring="cosine, top-k")}
