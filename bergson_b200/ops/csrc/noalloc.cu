@@ -22,6 +22,13 @@ int fail(int code, const char* fmt, long a = 0, long b = 0) {
   return code;
 }
 
+// Records "<what>: <CUDA error name> (<code>): <CUDA error text>".
+int fail_cuda(int code, const char* what) {
+  std::snprintf(g_error, sizeof(g_error), "%s: %s (%d): %s", what, cudaGetErrorName(cudaError_t(code)), code,
+                cudaGetErrorString(cudaError_t(code)));
+  return code;
+}
+
 __global__ void sum_partials_kernel(const float* __restrict__ partials, int n_partial, int d,
                                     float* __restrict__ dw) {
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
@@ -62,13 +69,18 @@ extern "C" int bgn_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void
     return fail(int(cudaErrorInvalidValue), "hidden size %ld exceeds the built-in scratch (max %ld)", d,
                 long(kBgnNoAllocMaxD));
   if (rows <= 0) return fail(int(cudaErrorInvalidValue), "rows must be positive (got %ld)", rows);
+  if (type < 0 || type > 2)
+    return fail(int(cudaErrorInvalidValue), "element type %ld is not one of 0 (fp16), 1 (bf16), 2 (fp32)", type);
+  const int vec = type == 2 ? 4 : 8;  // elements per 16-byte packet
+  if (d % vec)
+    return fail(int(cudaErrorInvalidValue), "hidden size %ld is not a multiple of the 16-byte packet (%ld elements)", d, vec);
   float* scratch = nullptr;
   if (int rc = scratch_for_current_device(&scratch)) return rc;
   const int n_partial = int(rows < kBgnNoAllocPartials ? rows : kBgnNoAllocPartials);
   int rc = bgn_rmsnorm_bwd(dy, x, w, rstd, dx, scratch, n_partial, rows, d, type, stream);
-  if (rc != 0) return fail(rc, "rmsnorm backward launch failed (%ld); d must be a multiple of the vector width", rc);
+  if (rc != 0) return fail_cuda(rc, "rmsnorm backward launch failed");
   sum_partials_kernel<<<(d + 255) / 256, 256, 0, stream>>>(scratch, n_partial, d, dw);
   cudaError_t e = cudaGetLastError();
-  if (e != cudaSuccess) return fail(int(e), "partial-sum launch failed (%ld)", long(e));
+  if (e != cudaSuccess) return fail_cuda(int(e), "partial-sum launch failed");
   return 0;
 }

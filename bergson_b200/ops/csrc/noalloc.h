@@ -2,9 +2,8 @@
 //
 // This entry point has no counterpart in the reference implementation.  It exists for
 // hosts that drive the kernels from a context where cudaMalloc / cudaFree (or torch's
-// caching allocator) must not run: inside code that is later captured, under a memory
-// budget fixed at start-up, or from a thin C caller that owns only its input and output
-// buffers.  The weight-gradient partial sums that `bgn_rmsnorm_bwd` expects the caller to
+// caching allocator) must not run: under a memory budget fixed at start-up, or from a
+// thin C caller that owns only its input and output buffers.  The weight-gradient partial sums that `bgn_rmsnorm_bwd` expects the caller to
 // provide as scratch live here in a fixed device array that belongs to the library.
 #pragma once
 
@@ -21,12 +20,12 @@ enum { kBgnNoAllocMaxD = 8192, kBgnNoAllocPartials = 296 };
 // y = rmsnorm(x) * w given dy.  Same math as bgn_rmsnorm_bwd followed by a column sum of
 // its partials.  Returns 0 on success, a cudaError_t value on a CUDA failure, and
 // cudaErrorInvalidValue when d exceeds kBgnNoAllocMaxD, d is not a multiple of the 16-byte
-// vector width, or a pointer is null; bgn_noalloc_last_error() then describes the reason.
+// packet (8 elements for 16-bit types, 4 for fp32), type is not 0..2, rows is not positive or a
+// pointer is null; bgn_noalloc_last_error() then names which, or gives the CUDA error's text.
 //
 // * Allocates nothing: no cudaMalloc, cudaFree or allocating library call.
 // * The first call on each device resolves the device address of the scratch array
-//   (cudaGetSymbolAddress with that device current).  Make that first call before starting
-//   a stream capture on the device.
+//   (cudaGetSymbolAddress with that device current); later calls only launch kernels.
 // * All calls on a device share the scratch, which keeps the previous call's contents;
 //   every call rewrites the part it reads, so nothing needs clearing between calls, but
 //   two calls that overlap on the GPU (different streams) race on it.  Serialise them.
