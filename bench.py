@@ -49,7 +49,7 @@ def parse_args():
     ap.add_argument("--seqs", type=int, default=8, help="sequences per rank per step")
     ap.add_argument("--seq-len", type=int, default=2048)
     ap.add_argument("--small", action="store_true", help="4-layer d1024 stand-in for quick checks (not a bench value)")
-    ap.add_argument("--extra", default="query,ekfac",
+    ap.add_argument("--extra", default="query,ekfac,magic",
                     help="comma-separated secondary metrics reported under \"extra\" (query, ekfac; empty for none)")
     return ap.parse_args()
 

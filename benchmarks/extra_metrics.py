@@ -10,6 +10,13 @@ device with CUDA events after a warm-up, maximum over ranks.
   across ranks.  Reference: its ``Attributor`` holds the whole store on each rank's GPU.
 * ``ekfac``: K-FAC covariances, eigendecomposition and eigenvalue correction for a random-init
   GPT-NeoX 12L d768 on 256 sequences x 1024 synthetic tokens (bf16 compute, fp32 factors).
+* ``magic``: one meta-step of the twice-differentiable trainer for a random-init GPT-2 12L d768
+  (bf16 parameters, AdamW lr 3e-4) on a global batch of 64 sequences x 512 synthetic tokens,
+  data-parallel over the ranks: the step replayed with its graph, then the vector-Jacobian
+  product that carries cotangents of the new parameters and optimizer state back to the old
+  state and to the 64 data weights.  The plain in-place training step is timed as well.
+  The reference's trainer imports ``torchopt``, which is not installed; its arm runs with the
+  stand-in under ``baseline/shims/torchopt`` (plain tensor operations, no accelerated op).
 """
 
 from __future__ import annotations
@@ -23,6 +30,10 @@ QUERY_CFG = dict(rows=65536, dim=57344, queries=1024, k=100)
 EKFAC_SPEC = dict(model_type="gpt_neox", vocab_size=50304, hidden_size=768, intermediate_size=3072, num_hidden_layers=12,
                   num_attention_heads=12, rotary_pct=0.25, max_position_embeddings=2048)
 EKFAC_CFG = dict(docs=256, seq_len=1024, token_batch=16384)
+MAGIC_SPEC = dict(vocab_size=50257, n_positions=1024, n_embd=768, n_layer=12, n_head=12)
+# Betas, eps, eps_root and weight decay are the reference TrainingConfig's defaults; eps_root > 0
+# keeps d sqrt(v) finite for rows that never received a gradient.
+MAGIC_CFG = dict(batch=64, seq_len=512, lr=3e-4, betas=(0.95, 0.975), eps=1e-8, eps_root=1e-8, weight_decay=0.01)
 
 
 def _max_over_ranks(x: float, device) -> float:
@@ -250,11 +261,119 @@ def ekfac_reference(rank: int, local_rank: int, world: int) -> dict:
             shutil.rmtree(tmp, ignore_errors=True)
 
 
+# --------------------------------------------------------------------------- MAGIC
+
+
+def _magic_data(vocab: int):
+    """Four global batches of synthetic Zipf tokens (the same ids for both arms)."""
+    import numpy as np
+    from datasets import Dataset
+
+    n, length = MAGIC_CFG["batch"] * 4, MAGIC_CFG["seq_len"]
+    rng = np.random.default_rng(0)
+    ids = np.minimum(rng.zipf(1.1, size=(n, length)), vocab) - 1
+    return Dataset.from_dict({"input_ids": ids.tolist(), "length": [length] * n})
+
+
+def _magic_run(trainer, state, data, dev, world: int) -> dict:
+    """Times ``Trainer.step`` in place and a traced step plus its VJP (the same calls for both
+    packages: their trainers expose the same interface)."""
+    import torch
+
+    holder = {"s": state, "loss": 0.0}
+
+    def train_step():
+        holder["s"] = trainer.step(holder["s"], data[0], inplace=True)
+
+    train_ms = _timed(train_step, dev, warmup=2, iters=4)
+
+    def meta_step():
+        st = holder["s"]
+        st.detach_()
+        st.requires_grad = True
+        data.requires_grad = True
+        before = st.differentiable_tensors()
+        after = trainer.step(st, data[1], trace=True).differentiable_tensors()
+        cot = [torch.full_like(t, 1e-3) for t in after]
+        grads = torch.autograd.grad(after, before + [data.weights], grad_outputs=cot, allow_unused=True)
+        holder["loss"] = float(grads[-1].float().abs().sum())  # device -> host read of the weight gradient
+        st.requires_grad = False
+        data.requires_grad = False
+
+    torch.cuda.reset_peak_memory_stats(dev)
+    meta_ms = _timed(meta_step, dev, warmup=1, iters=3)
+    tokens = MAGIC_CFG["batch"] * MAGIC_CFG["seq_len"]
+    return {"metric": "magic_meta_step_s", "value": meta_ms / 1e3, "unit": "s", "higher_is_better": False,
+            "scaling": "strong", "train_step_s": train_ms / 1e3, "meta_over_train": meta_ms / train_ms,
+            "meta_tokens_per_s": tokens / (meta_ms / 1e3), "weight_grad_abs_sum": holder["loss"],
+            "peak_mem_gb": torch.cuda.max_memory_allocated(dev) / 1e9,
+            "config": {"model": "gpt2-12L-d768 random init", "global_batch": MAGIC_CFG["batch"],
+                       "seq_len": MAGIC_CFG["seq_len"], "dtype": "bf16", "optimizer": "adamw",
+                       "parallelism": f"dp{world}"}}
+
+
+def magic_ours(rank: int, local_rank: int, world: int) -> dict:
+    import torch
+
+    from bergson_b200.magic import optim
+    from bergson_b200.magic.data_stream import DataStream
+    from bergson_b200.magic.trainer import Trainer
+    from bergson_b200.models import build_model
+    from bergson_b200.models.registry import PRESETS, args_from_dict
+
+    dev = torch.device("cuda", local_rank)
+    s = MAGIC_SPEC
+    spec = dict(PRESETS["gpt2"], vocab_size=s["vocab_size"], hidden_size=s["n_embd"], num_hidden_layers=s["n_layer"],
+                num_attention_heads=s["n_head"], max_position_embeddings=s["n_positions"])
+    model = build_model(args_from_dict(spec), dtype=torch.bfloat16, device=dev, init_on_device=True)
+    model.requires_grad_(True)
+    model.eval()
+    c = MAGIC_CFG
+    opt = optim.adamw(lambda step: c["lr"], betas=c["betas"], eps=c["eps"], eps_root=c["eps_root"],
+                      weight_decay=c["weight_decay"])
+    trainer, state = Trainer.initialize(model, opt)
+    data = DataStream(_magic_data(s["vocab_size"]), c["batch"], device=dev)
+    return _magic_run(trainer, state, data, dev, world)
+
+
+def magic_reference(rank: int, local_rank: int, world: int) -> dict:
+    from functools import partial
+
+    import torch
+    import torchopt
+    from transformers import AutoModelForCausalLM, GPT2Config
+
+    from bergson.magic.data_stream import DataStream
+    from bergson.magic.trainer import Trainer
+    from bergson.utils import weighted_causal_lm_ce
+
+    dev = torch.device("cuda", local_rank)
+    s = MAGIC_SPEC
+    # What the reference's prepare_trainer builds: eager attention, dropout off in eval mode,
+    # the weighted cross-entropy as the model's loss function.
+    hf = GPT2Config(vocab_size=s["vocab_size"], n_positions=s["n_positions"], n_embd=s["n_embd"], n_layer=s["n_layer"],
+                    n_head=s["n_head"], attn_implementation="eager")
+    torch.manual_seed(0)
+    with torch.device(dev):
+        model = AutoModelForCausalLM.from_config(hf, dtype=torch.bfloat16)
+    model.loss_function = partial(weighted_causal_lm_ce, reduction="mean")
+    model.requires_grad_(True)
+    model.eval()
+    c = MAGIC_CFG
+    opt = torchopt.adamw(lambda step: c["lr"], betas=c["betas"], eps=c["eps"], eps_root=c["eps_root"],
+                         weight_decay=c["weight_decay"])
+    trainer, state = Trainer.initialize(model, opt)
+    data = DataStream(_magic_data(s["vocab_size"]), c["batch"], device=dev)
+    out = _magic_run(trainer, state, data, dev, world)
+    out["torchopt"] = getattr(torchopt, "__version__", "?")
+    return out
+
+
 def run_extras(impl: str, rank: int, local_rank: int, world: int, which=("query", "ekfac")) -> dict:
     """``{"query": {...}, "ekfac": {...}}``; a metric that fails reports its error instead of
     taking the headline down with it."""
-    table = {"ours": {"query": query_ours, "ekfac": ekfac_ours},
-             "reference": {"query": query_reference, "ekfac": ekfac_reference}}[impl]
+    table = {"ours": {"query": query_ours, "ekfac": ekfac_ours, "magic": magic_ours},
+             "reference": {"query": query_reference, "ekfac": ekfac_reference, "magic": magic_reference}}[impl]
     out = {}
     for name in which:
         try:

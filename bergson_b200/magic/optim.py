@@ -14,8 +14,11 @@ gradients, parameters and optimizer state to any order:
   (a, b, c = 3.4445, -4.7750, 2.0315), lr ratio ``0.2 sqrt(max(A, B))``, decoupled
   weight decay; other params: AdamW.
 
-On CUDA, the non-traced (``inplace=True``) AdamW step over fp32 state runs in the fused
-``adamw_step`` kernel.
+On CUDA, the non-traced (``inplace=True``) AdamW step runs as one multi-tensor kernel launch
+(``GradientTransformation.step_inplace``: moments, bias correction, weight decay and the
+parameter write in a single pass, with an optional device-side gradient coefficient so that
+global-norm clipping needs no pass of its own); ``global_norm_coef`` computes that
+coefficient with one multi-tensor reduction.
 """
 
 from __future__ import annotations
@@ -40,6 +43,43 @@ NS_STEPS = 5
 class GradientTransformation:
     init: Callable[[Params], OptState]
     update: Callable[..., tuple[Params, OptState]]
+    # Optional fused in-place step ``(grads, state, params, coef) -> (params, state) | None``;
+    # None means "not applicable to these tensors", and the caller uses ``update``.
+    step_inplace: Callable[..., tuple[Params, OptState] | None] | None = None
+
+
+_FUSED_DTYPES = (torch.float32, torch.bfloat16, torch.float16)
+
+
+def _native():
+    from ..ops import native
+
+    return native if native.available() else None
+
+
+def _fusable(tensors: list[Tensor]) -> bool:
+    """One CUDA device, one element type the kernels take, contiguous, outside autograd."""
+    if not tensors or _native() is None:
+        return False
+    first = tensors[0]
+    return first.is_cuda and first.dtype in _FUSED_DTYPES and all(
+        t.device == first.device and t.dtype == first.dtype and t.is_contiguous() and not t.requires_grad
+        for t in tensors)
+
+
+def global_norm_coef(grads: list[Tensor], max_norm: float, *, reduce=None) -> Tensor | None:
+    """``min(1, max_norm / (||grads||_2 + 1e-6))`` as a device scalar, from one multi-tensor
+    sum-of-squares launch (partials added in a fixed order).  ``reduce`` (e.g. an all-reduce
+    over ranks holding shards) is applied to the squared norm first.  None when the tensors
+    are not eligible for the kernel."""
+    if not _fusable(grads):
+        return None
+    out = torch.empty(2, device=grads[0].device, dtype=torch.float32)
+    _native().multi_sumsq(grads, out, False, 0.0 if reduce is not None else float(max_norm))
+    if reduce is None:
+        return out[1:2]
+    sq = reduce(out[0:1])
+    return (max_norm / (sq.sqrt() + 1e-6)).clamp(max=1.0)
 
 
 def apply_updates(params: Params, updates: Params, *, inplace: bool = False) -> Params:
@@ -168,6 +208,17 @@ def adamw(lr: Schedule | float, betas=(0.9, 0.999), eps: float = 1e-8, eps_root:
         updates.update(dict(zip(keys, direction)))
         return updates, {"mu": state["mu"], "nu": state["nu"], "count": count}
 
+    def step_inplace(grads: Params, state: OptState, params: Params, coef: Tensor | None = None):
+        keys = [k for k in params if grads.get(k) is not None]
+        ps, gs = [params[k] for k in keys], [grads[k] for k in keys]
+        mus, nus = [state["mu"][k] for k in keys], [state["nu"][k] for k in keys]
+        if not (_fusable(ps + gs) and all(t.dtype == torch.float32 and t.is_contiguous() for t in mus + nus)):
+            return None
+        t = int(state["count"]) + 1
+        _native().adamw_multi(ps, mus, nus, gs, _lr_of(lr, state["count"]), b1, b2, eps, eps_root, weight_decay, t,
+                              1.0, coef)
+        return dict(params), {"mu": state["mu"], "nu": state["nu"], "count": state["count"] + 1}
+
     def update(grads: Params, state: OptState, *, params: Params, inplace: bool = False):
         if inplace and not any(g is not None and g.requires_grad for g in grads.values()):
             return update_foreach(grads, state, params)
@@ -187,7 +238,7 @@ def adamw(lr: Schedule | float, betas=(0.9, 0.999), eps: float = 1e-8, eps_root:
             updates[k] = -step_lr * d
         return updates, {"mu": mu, "nu": nu, "count": count}
 
-    return GradientTransformation(init, update)
+    return GradientTransformation(init, update, step_inplace)
 
 
 # --------------------------------------------------------------------------- #

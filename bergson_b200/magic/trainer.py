@@ -139,7 +139,15 @@ class TrainerState:
     def to(self, device) -> "TrainerState":
         """Snapshot on ``device`` (always a copy, so later in-place steps cannot touch it)."""
         mv = lambda t: t.to(device, copy=True) if isinstance(t, torch.Tensor) else t  # noqa: E731
-        return TrainerState({k: mv(p) for k, p in self.params.items()}, tree_map(mv, self.opt_state),
+
+        def mv_opt(t):
+            # Integer leaves (the step count) stay on the host: the schedule and the bias
+            # correction read them every step, and a device copy would cost a sync each time.
+            if isinstance(t, torch.Tensor) and not t.is_floating_point():
+                return t.to("cpu", copy=True)
+            return mv(t)
+
+        return TrainerState({k: mv(p) for k, p in self.params.items()}, tree_map(mv_opt, self.opt_state),
                             {k: mv(b) for k, b in self.buffers.items()}, self.batch_index,
                             self.cuda_rng_state.clone(), self.cpu_rng_state.clone())
 
@@ -284,7 +292,19 @@ class Trainer:
             else:
                 for g in grads.values():
                     dist.all_reduce(g, op=dist.ReduceOp.AVG)
-        if max_grad_norm:
+        coef = None
+        fused_step = inplace and not trace and self.optimizer.step_inplace is not None
+        if max_grad_norm and fused_step:
+            # One multi-tensor reduction; the coefficient is applied inside the optimizer kernel.
+            reduce = _all_reduce_ if fsdp and dist.is_initialized() else None
+            coef = optim.global_norm_coef(list(grads.values()), max_grad_norm, reduce=reduce)
+        if fused_step and (coef is not None or not max_grad_norm):
+            stepped = self.optimizer.step_inplace(grads, state.opt_state, state.params, coef)
+            if stepped is not None:
+                return TrainerState(stepped[0], stepped[1], state.buffers, state.batch_index + 1)
+        if max_grad_norm and coef is not None:
+            torch._foreach_mul_(list(grads.values()), coef.to(next(iter(grads.values())).dtype))
+        elif max_grad_norm:
             sq = sum(g.float().pow(2).sum() for g in grads.values())
             if fsdp and dist.is_initialized():
                 sq = all_reduce_sum(sq) if trace else _all_reduce_(sq)

@@ -4,6 +4,9 @@
 #include <c10/cuda/CUDAGuard.h>
 #include <torch/extension.h>
 
+#include <array>
+#include <cstring>
+
 #include <map>
 #include <mutex>
 
@@ -284,6 +287,63 @@ void adamw_step(at::Tensor p, at::Tensor m, at::Tensor v, at::Tensor g, c10::opt
                        (float)grad_scale, type_code(g), mt, stream()), "adamw_step");
 }
 
+// Device copy of a pointer table for the multi-tensor kernels: six 8-byte words per entry.
+// The host side is pinned so that the copy is asynchronous; the caching host allocator keeps
+// the pinned block alive until the copy has run.
+static at::Tensor upload_table(const std::vector<std::array<int64_t, 6>>& rows, const at::Device& device) {
+  auto host = at::empty({(int64_t)rows.size(), 6}, at::TensorOptions().dtype(at::kLong).pinned_memory(true));
+  std::memcpy(host.data_ptr<int64_t>(), rows.data(), rows.size() * sizeof(rows[0]));
+  return host.to(device, /*non_blocking=*/true);
+}
+
+void adamw_multi(std::vector<at::Tensor> ps, std::vector<at::Tensor> ms, std::vector<at::Tensor> vs,
+                 std::vector<at::Tensor> gs, double lr, double b1, double b2, double eps, double eps_root, double wd,
+                 int64_t step, double grad_scale, c10::optional<at::Tensor> coef) {
+  const size_t n = ps.size();
+  TORCH_CHECK(n > 0 && ms.size() == n && vs.size() == n && gs.size() == n, "adamw_multi: list lengths differ");
+  std::vector<std::array<int64_t, 6>> rows(n);
+  int64_t max_n = 0;
+  for (size_t i = 0; i < n; ++i) {
+    CHECK_CUDA_CONTIG(ps[i]); CHECK_CUDA_CONTIG(ms[i]); CHECK_CUDA_CONTIG(vs[i]); CHECK_CUDA_CONTIG(gs[i]);
+    TORCH_CHECK(ps[i].scalar_type() == ps[0].scalar_type() && gs[i].scalar_type() == ps[0].scalar_type(),
+                "adamw_multi: parameters and gradients must share one element type");
+    TORCH_CHECK(ms[i].scalar_type() == at::kFloat && vs[i].scalar_type() == at::kFloat, "adamw_multi: fp32 moments");
+    TORCH_CHECK(ms[i].numel() == ps[i].numel() && vs[i].numel() == ps[i].numel() && gs[i].numel() == ps[i].numel());
+    TORCH_CHECK(ps[i].device() == ps[0].device());
+    rows[i] = {(int64_t)ps[i].data_ptr(), (int64_t)ms[i].data_ptr(), (int64_t)vs[i].data_ptr(),
+               (int64_t)gs[i].data_ptr(), ps[i].numel(), 0};
+    max_n = std::max<int64_t>(max_n, ps[i].numel());
+  }
+  c10::cuda::CUDAGuard guard(ps[0].device());
+  const float* cf = nullptr;
+  if (coef.has_value()) {
+    TORCH_CHECK(coef->is_cuda() && coef->scalar_type() == at::kFloat && coef->numel() >= 1);
+    cf = coef->data_ptr<float>();
+  }
+  auto table = upload_table(rows, ps[0].device());
+  const float bc1 = 1.f - (float)std::pow(b1, (double)step), bc2 = 1.f - (float)std::pow(b2, (double)step);
+  check(bgn_adamw_multi(table.data_ptr(), (int)n, max_n, (float)lr, (float)b1, (float)b2, (float)eps, (float)eps_root,
+                        (float)wd, bc1, bc2, (float)grad_scale, cf, type_code(ps[0]), stream()), "adamw_multi");
+}
+
+// out[0] (+)= sum of squares of every tensor in `xs`; with max_norm > 0 also
+// out[1] = min(1, max_norm / (sqrt(out[0]) + 1e-6)).  `out` is fp32 with at least two elements.
+void multi_sumsq(std::vector<at::Tensor> xs, at::Tensor out, bool accumulate, double max_norm) {
+  const size_t n = xs.size();
+  TORCH_CHECK(n > 0 && out.is_cuda() && out.scalar_type() == at::kFloat && out.numel() >= 2 && out.is_contiguous());
+  std::vector<std::array<int64_t, 6>> rows(n);
+  for (size_t i = 0; i < n; ++i) {
+    CHECK_CUDA_CONTIG(xs[i]);
+    TORCH_CHECK(xs[i].scalar_type() == xs[0].scalar_type() && xs[i].device() == out.device());
+    rows[i] = {0, 0, 0, (int64_t)xs[i].data_ptr(), xs[i].numel(), 0};
+  }
+  c10::cuda::CUDAGuard guard(out.device());
+  auto table = upload_table(rows, out.device());
+  auto partials = at::empty({(int64_t)n * bgn_multi_sumsq_blocks()}, out.options());
+  check(bgn_multi_sumsq(table.data_ptr(), (int)n, partials.data_ptr<float>(), out.data_ptr<float>(), accumulate,
+                        (float)max_norm, type_code(xs[0]), stream()), "multi_sumsq");
+}
+
 void row_sumsq(at::Tensor x, at::Tensor out) {
   TORCH_CHECK(x.is_cuda() && x.dim() == 2 && x.stride(1) == 1 && out.scalar_type() == at::kFloat &&
               out.numel() == x.size(0));
@@ -448,6 +508,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("tn_gemm_gathered", &tn_gemm_gathered);
   m.def("finalize_rows", &finalize_rows);
   m.def("adamw_step", &adamw_step);
+  m.def("adamw_multi", &adamw_multi, py::arg("params"), py::arg("mu"), py::arg("nu"), py::arg("grads"), py::arg("lr"),
+        py::arg("b1"), py::arg("b2"), py::arg("eps"), py::arg("eps_root"), py::arg("weight_decay"), py::arg("step"),
+        py::arg("grad_scale") = 1.0, py::arg("coef") = py::none());
+  m.def("multi_sumsq", &multi_sumsq, py::arg("tensors"), py::arg("out"), py::arg("accumulate") = false,
+        py::arg("max_norm") = 0.0);
   m.def("row_sumsq", &row_sumsq);
   m.def("cov_syrk", &cov_syrk, py::arg("x"), py::arg("dst_ptrs"), py::arg("row_start"), py::arg("local"),
         py::arg("full") = false, py::arg("num_rows") = -1, py::arg("local_upper") = false);

@@ -483,6 +483,100 @@ __global__ void adamw_kernel(float* __restrict__ p, float* __restrict__ m, float
   }
 }
 
+// One launch for a whole list of tensors: blockIdx.y selects the table entry, the blocks of
+// that row stride over its elements (four at a time when size and addresses allow).
+// p and g share the element type T; m and v are fp32.  `coef` (optional, device scalar)
+// scales every gradient, e.g. a global-norm clipping coefficient computed on the device.
+struct AdamEntry {
+  void* p;
+  float* m;
+  float* v;
+  const void* g;
+  long n;
+  long reserved;
+};
+
+template <typename T>
+__device__ __forceinline__ void adamw_one(T& p, float& m, float& v, T g, float gs, float lr, float b1, float b2,
+                                          float eps, float eps_root, float wd, float bc1, float bc2) {
+  const float gi = to_float<T>(g) * gs;
+  m = b1 * m + (1.f - b1) * gi;
+  v = b2 * v + (1.f - b2) * gi * gi;
+  const float pf = to_float<T>(p);
+  const float upd = (m / bc1) / (sqrtf(v / bc2 + eps_root) + eps) + wd * pf;
+  p = from_float<T>(pf - lr * upd);
+}
+
+template <typename T>
+__global__ void adamw_multi_kernel(const AdamEntry* __restrict__ table, float lr, float b1, float b2, float eps,
+                                   float eps_root, float wd, float bc1, float bc2, float gscale,
+                                   const float* __restrict__ coef) {
+  const AdamEntry e = table[blockIdx.y];
+  const float gs = coef ? gscale * coef[0] : gscale;
+  T* p = static_cast<T*>(e.p);
+  const T* g = static_cast<const T*>(e.g);
+  struct alignas(4 * sizeof(T)) Pack { T v[4]; };
+  const bool vec = (e.n & 3) == 0 &&
+                   ((reinterpret_cast<uintptr_t>(e.m) | reinterpret_cast<uintptr_t>(e.v)) & 15) == 0 &&
+                   ((reinterpret_cast<uintptr_t>(e.p) | reinterpret_cast<uintptr_t>(e.g)) & (4 * sizeof(T) - 1)) == 0;
+  const long tid = blockIdx.x * long(blockDim.x) + threadIdx.x, stride = long(gridDim.x) * blockDim.x;
+  if (vec) {
+    for (long i = tid; i < (e.n >> 2); i += stride) {
+      float4 m4 = reinterpret_cast<float4*>(e.m)[i], v4 = reinterpret_cast<float4*>(e.v)[i];
+      Pack pp = reinterpret_cast<Pack*>(p)[i];
+      const Pack gp = reinterpret_cast<const Pack*>(g)[i];
+      adamw_one<T>(pp.v[0], m4.x, v4.x, gp.v[0], gs, lr, b1, b2, eps, eps_root, wd, bc1, bc2);
+      adamw_one<T>(pp.v[1], m4.y, v4.y, gp.v[1], gs, lr, b1, b2, eps, eps_root, wd, bc1, bc2);
+      adamw_one<T>(pp.v[2], m4.z, v4.z, gp.v[2], gs, lr, b1, b2, eps, eps_root, wd, bc1, bc2);
+      adamw_one<T>(pp.v[3], m4.w, v4.w, gp.v[3], gs, lr, b1, b2, eps, eps_root, wd, bc1, bc2);
+      reinterpret_cast<float4*>(e.m)[i] = m4;
+      reinterpret_cast<float4*>(e.v)[i] = v4;
+      reinterpret_cast<Pack*>(p)[i] = pp;
+    }
+  } else {
+    for (long i = tid; i < e.n; i += stride) {
+      float mi = e.m[i], vi = e.v[i];
+      T pi = p[i];
+      adamw_one<T>(pi, mi, vi, g[i], gs, lr, b1, b2, eps, eps_root, wd, bc1, bc2);
+      e.m[i] = mi;
+      e.v[i] = vi;
+      p[i] = pi;
+    }
+  }
+}
+
+// Sum of squares over a list of tensors (entries reuse AdamEntry: g = data, n = elements).
+// Every block writes one partial; `multi_sumsq_finish` adds them in a fixed order, so the
+// result does not depend on scheduling.
+template <typename T>
+__global__ void multi_sumsq_kernel(const AdamEntry* __restrict__ table, float* __restrict__ partials) {
+  __shared__ float red[32];
+  const AdamEntry e = table[blockIdx.y];
+  const T* g = static_cast<const T*>(e.g);
+  float ss = 0.f;
+  for (long i = blockIdx.x * long(blockDim.x) + threadIdx.x; i < e.n; i += long(gridDim.x) * blockDim.x) {
+    const float f = to_float<T>(g[i]);
+    ss = fmaf(f, f, ss);
+  }
+  ss = block_sum(ss, red);
+  if (threadIdx.x == 0) partials[blockIdx.y * long(gridDim.x) + blockIdx.x] = ss;
+}
+
+// out[0] = sum(partials) (+ out[0] when `accumulate`); out[1] = min(1, max_norm / (sqrt(out[0]) + 1e-6))
+// when max_norm > 0.
+__global__ void multi_sumsq_finish_kernel(const float* __restrict__ partials, long n, float* __restrict__ out,
+                                          int accumulate, float max_norm) {
+  __shared__ float red[32];
+  float ss = 0.f;
+  for (long i = threadIdx.x; i < n; i += blockDim.x) ss += partials[i];
+  ss = block_sum(ss, red);
+  if (threadIdx.x == 0) {
+    const float total = accumulate ? out[0] + ss : ss;
+    out[0] = total;
+    if (max_norm > 0.f) out[1] = fminf(1.f, max_norm / (sqrtf(total) + 1e-6f));
+  }
+}
+
 template <typename T>
 __global__ void row_sumsq_kernel(const T* __restrict__ x, float* __restrict__ out, long d, long ldx) {
   __shared__ float red[32];
@@ -643,6 +737,34 @@ extern "C" int bgn_adamw_step(float* p, float* m, float* v, const void* g, void*
   else if (g_type == 2 && model_type == 0) ADAM_LAUNCH(float, __half);
   else return int(cudaErrorInvalidValue);
 #undef ADAM_LAUNCH
+  return int(cudaGetLastError());
+}
+
+extern "C" int bgn_adamw_multi(const void* table, int n_tensors, long max_n, float lr, float b1, float b2,
+                               float eps, float eps_root, float wd, float bc1, float bc2, float gscale,
+                               const float* coef, int type, cudaStream_t st) {
+  if (n_tensors <= 0) return 0;
+  if (n_tensors > 65535) return int(cudaErrorInvalidValue);
+  // About eight 4-element packets per thread for the largest tensor, at most 128 blocks per
+  // tensor; blocks of shorter tensors run out of work early and retire.
+  long per_row = (max_n / 4 + 256 * 8 - 1) / (256 * 8);
+  per_row = per_row < 1 ? 1 : (per_row > 128 ? 128 : per_row);
+  const dim3 grid((unsigned)per_row, (unsigned)n_tensors);
+  BGN_DISPATCH(type, {
+    adamw_multi_kernel<T><<<grid, 256, 0, st>>>((const AdamEntry*)table, lr, b1, b2, eps, eps_root, wd, bc1, bc2,
+                                                gscale, coef);
+  });
+  return int(cudaGetLastError());
+}
+
+extern "C" int bgn_multi_sumsq_blocks(void) { return 16; }
+
+extern "C" int bgn_multi_sumsq(const void* table, int n_tensors, float* partials, float* out, int accumulate,
+                               float max_norm, int type, cudaStream_t st) {
+  if (n_tensors <= 0 || n_tensors > 65535) return int(cudaErrorInvalidValue);
+  const dim3 grid(16, (unsigned)n_tensors);
+  BGN_DISPATCH(type, { multi_sumsq_kernel<T><<<grid, 256, 0, st>>>((const AdamEntry*)table, partials); });
+  multi_sumsq_finish_kernel<<<1, 1024, 0, st>>>(partials, 16L * n_tensors, out, accumulate, max_norm);
   return int(cudaGetLastError());
 }
 

@@ -81,6 +81,20 @@ int bgn_ce_bwd(const void* logits, const long* targets, const float* lse, const 
 int bgn_adamw_step(float* p, float* m, float* v, const void* g, void* p_model, long n, float lr,
                    float b1, float b2, float eps, float eps_root, float wd, float bc1, float bc2,
                    float grad_scale, int g_type, int model_type, cudaStream_t stream);
+// AdamW over a list of tensors in one launch.  `table` is a device array of n_tensors entries of
+// six 8-byte words {p, m, v, g, n, unused}: p and g of element type `type`, m and v fp32, all
+// updated in place; max_n is the largest n.  `coef` (device scalar, may be null) multiplies
+// every gradient together with gscale.
+int bgn_adamw_multi(const void* table, int n_tensors, long max_n, float lr, float b1, float b2, float eps,
+                    float eps_root, float wd, float bc1, float bc2, float gscale, const float* coef,
+                    int type, cudaStream_t stream);
+// Sum of squares over a list of tensors (table entries as above, only g and n are read) into
+// out[0] (added to it when `accumulate`); with max_norm > 0, out[1] = min(1, max_norm /
+// (sqrt(out[0]) + 1e-6)).  `partials` holds bgn_multi_sumsq_blocks() * n_tensors floats; the
+// partials are added in a fixed order.
+int bgn_multi_sumsq_blocks(void);
+int bgn_multi_sumsq(const void* table, int n_tensors, float* partials, float* out, int accumulate,
+                    float max_norm, int type, cudaStream_t stream);
 // out[r] += sum_k x[r, k]^2  (x 16-bit or fp32).
 int bgn_row_sumsq(const void* x, float* out, long rows, long d, long ldx, int type,
                   cudaStream_t stream);

@@ -1,0 +1,109 @@
+"""MAGIC's in-place training step on the GPU: the multi-tensor AdamW kernel and the fused
+global-norm clipping coefficient against fp32 PyTorch, and the trainer taking that path."""
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def native():
+    from bergson_b200.ops import native
+
+    assert native.available()
+    return native
+
+
+def _adamw_reference(p, m, v, g, lr, b1, b2, eps, eps_root, wd, step, coef=1.0):
+    g = g.float() * coef
+    m = b1 * m + (1 - b1) * g
+    v = b2 * v + (1 - b2) * g * g
+    upd = (m / (1 - b1**step)) / ((v / (1 - b2**step) + eps_root).sqrt() + eps) + wd * p.float()
+    return p.float() - lr * upd, m, v
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16, torch.float16])
+def test_adamw_multi_matches_fp32_reference(native, dtype):
+    torch.manual_seed(0)
+    # Aligned and ragged sizes, a scalar-like tensor, and an offset view whose address is not
+    # a multiple of 16 bytes (all in one launch).
+    sizes = [4096 * 33, 1000, 7, 1, 128 * 1024 + 4]
+    ps = [torch.randn(n, device="cuda").to(dtype) for n in sizes]
+    base = torch.randn(1025, device="cuda").to(dtype)
+    ps.append(base[1:])
+    first = base[0].clone()
+    gs = [torch.randn_like(p) for p in ps[:-1]] + [torch.randn(1025, device="cuda").to(dtype)[1:]]
+    ms = [torch.randn(p.numel(), device="cuda") * 0.1 for p in ps]
+    vs = [torch.rand(p.numel(), device="cuda") * 0.1 for p in ps]
+    coef = torch.tensor([0.37], device="cuda")
+    hp = dict(lr=1e-2, b1=0.9, b2=0.95, eps=1e-8, eps_root=1e-12, wd=0.1)
+    for step in (1, 2):
+        want = [_adamw_reference(p, m, v, g, step=step, coef=0.37, **hp) for p, m, v, g in zip(ps, ms, vs, gs)]
+        native.adamw_multi(ps, ms, vs, gs, hp["lr"], hp["b1"], hp["b2"], hp["eps"], hp["eps_root"], hp["wd"], step,
+                           1.0, coef)
+        for (p_ref, m_ref, v_ref), p, m, v in zip(want, ps, ms, vs):
+            torch.testing.assert_close(m, m_ref, atol=1e-6, rtol=1e-5)
+            torch.testing.assert_close(v, v_ref, atol=1e-6, rtol=1e-5)
+            if dtype == torch.float32:
+                torch.testing.assert_close(p, p_ref, atol=1e-6, rtol=1e-5)
+            else:  # one rounding of the fp32 result to the 16-bit type
+                torch.testing.assert_close(p, p_ref.to(dtype), atol=0, rtol=2**-7)
+    assert torch.equal(base[0], first)  # the element before the offset view is left alone
+
+
+def test_multi_sumsq_and_clip_coefficient(native):
+    torch.manual_seed(1)
+    xs = [torch.randn(n, device="cuda", dtype=torch.bfloat16) for n in (5, 4096 * 17, 1, 333)]
+    out = torch.zeros(2, device="cuda")
+    native.multi_sumsq(xs, out, False, 1.5)
+    sq = sum(x.float().pow(2).sum() for x in xs)
+    torch.testing.assert_close(out[0], sq, rtol=1e-5, atol=0)
+    torch.testing.assert_close(out[1], (1.5 / (sq.sqrt() + 1e-6)).clamp(max=1.0), rtol=1e-5, atol=0)
+    again = torch.zeros(2, device="cuda")
+    native.multi_sumsq(xs, again, False, 1.5)
+    assert torch.equal(out, again)  # fixed summation order
+    native.multi_sumsq(xs, again, True, 0.0)
+    torch.testing.assert_close(again[0], 2 * sq, rtol=1e-5, atol=0)
+    small = [torch.full((4,), 0.1, device="cuda")]
+    native.multi_sumsq(small, out, False, 10.0)
+    assert out[1].item() == 1.0  # no clipping below the threshold
+
+
+def _tiny_trainer(max_grad_norm):
+    from bergson_b200.magic import optim
+    from bergson_b200.magic.data_stream import DataStream
+    from bergson_b200.magic.trainer import Trainer
+
+    from .helpers import tiny_dataset, tiny_model
+
+    torch.manual_seed(0)
+    model = tiny_model("llama", dtype=torch.float32, num_hidden_layers=2).to("cuda")
+    model.requires_grad_(True)
+    model.eval()
+    opt = optim.adamw(lambda i: 1e-3 * (1 + i), betas=(0.9, 0.95), weight_decay=0.01)
+    trainer, state = Trainer.initialize(model, opt)
+    data = DataStream(tiny_dataset(n=8, length=16, ragged=False), 4, device="cuda")
+    with torch.no_grad():
+        batch = {k: (v.detach() if isinstance(v, torch.Tensor) else v) for k, v in data[0].items()}
+    return trainer, state, batch, max_grad_norm
+
+
+@pytest.mark.parametrize("max_grad_norm", [None, 0.05])
+def test_trainer_inplace_step_uses_the_fused_kernel_and_matches_functional(monkeypatch, native, max_grad_norm):
+    from bergson_b200.magic import optim
+
+    trainer, state, batch, clip = _tiny_trainer(max_grad_norm)
+    want = state.to("cuda")
+    calls = []
+    real = native.adamw_multi
+    monkeypatch.setattr(native, "adamw_multi", lambda *a, **k: (calls.append(len(a[0])), real(*a, **k))[1])
+    for _ in range(3):
+        state = trainer.step(state, batch, inplace=True, max_grad_norm=clip)
+        want = trainer.step(want, batch, inplace=False, max_grad_norm=clip)
+    assert len(calls) == 3 and calls[0] == len(state.params)
+    assert int(state.opt_state["count"]) == 3 and state.opt_state["count"].device.type == "cpu"
+    for k in state.params:
+        torch.testing.assert_close(state.params[k], want.params[k], atol=2e-6, rtol=1e-4)
+        torch.testing.assert_close(state.opt_state["nu"][k], want.opt_state["nu"][k], atol=1e-10, rtol=1e-4)
+    assert optim.global_norm_coef([torch.ones(3)], 1.0) is None  # CPU tensors: not eligible
