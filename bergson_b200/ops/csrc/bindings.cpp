@@ -12,6 +12,7 @@
 
 #include "kernels.h"
 #include "kernels_cov.h"
+#include "kernels_peer.h"
 #include "kernels_gemm.h"
 
 namespace {
@@ -383,7 +384,9 @@ void cov_syrk(at::Tensor x, std::vector<int64_t> dst_ptrs, std::vector<int64_t> 
 std::vector<at::Tensor> gemm(at::Tensor a, at::Tensor b, bool a_mn, bool b_mn, c10::optional<at::Tensor> out,
                              bool out_f32, c10::optional<at::Tensor> bias, bool accumulate,
                              c10::optional<at::Tensor> aux_p, int64_t cta_group, bool sq_accumulate,
-                             int64_t wait_cycles, c10::optional<at::Tensor> status, int64_t panel, c10::optional<at::Tensor> trace, bool no_tma_store, bool wide) {
+                             int64_t wait_cycles, c10::optional<at::Tensor> status, int64_t panel, c10::optional<at::Tensor> trace, bool no_tma_store, bool wide,
+                             std::vector<int64_t> a_peer_ptrs, std::vector<int64_t> d_peer_ptrs, int64_t d_rows_per_rank,
+                             int64_t d_slot) {
   TORCH_CHECK(a.is_cuda() && b.is_cuda() && a.scalar_type() == b.scalar_type(), "gemm: CUDA operands of one dtype");
   TORCH_CHECK((a.dim() == 2 || a.dim() == 3) && a.dim() == b.dim() && a.stride(-1) == 1 && b.stride(-1) == 1,
               "gemm: 2-D or 3-D operands with contiguous last dimension");
@@ -392,7 +395,14 @@ std::vector<at::Tensor> gemm(at::Tensor a, at::Tensor b, bool a_mn, bool b_mn, c
   const bool batched = a.dim() == 3;
   const int64_t nb = batched ? a.size(0) : 1;
   if (batched) { TORCH_CHECK(b.size(0) == nb, "gemm: batch sizes differ"); }
-  const int64_t M = a_mn ? a.size(-1) : a.size(-2), K = a_mn ? a.size(-2) : a.size(-1);
+  // With a_peer_ptrs, `a` is this rank's [rows, K] block (shape, dtype and row stride of every
+  // rank's block) and the product runs over the concatenation of all ranks' blocks.
+  const int64_t gather_world = (int64_t)a_peer_ptrs.size(), scatter_world = (int64_t)d_peer_ptrs.size();
+  TORCH_CHECK(gather_world <= 8 && scatter_world <= 8, "gemm: at most 8 peers");
+  if (gather_world || scatter_world) {
+    TORCH_CHECK(!batched && !a_mn && !out_f32 && !accumulate && !sq_accumulate, "gemm: peer forms take a K-major 2-D A and write 16-bit outputs");
+  }
+  const int64_t M = (a_mn ? a.size(-1) : a.size(-2)) * (gather_world ? gather_world : 1), K = a_mn ? a.size(-2) : a.size(-1);
   const int64_t N = b_mn ? b.size(-1) : b.size(-2), Kb = b_mn ? b.size(-2) : b.size(-1);
   TORCH_CHECK(K == Kb, "gemm: reduction lengths differ (", K, " vs ", Kb, ")");
   const auto out_type = out_f32 ? at::kFloat : a.scalar_type();
@@ -406,6 +416,8 @@ std::vector<at::Tensor> gemm(at::Tensor a, at::Tensor b, bool a_mn, bool b_mn, c
       TORCH_CHECK(d.dim() == a.dim() && d.size(-2) == M && d.size(-1) == N && (!batched || d.size(0) == nb),
                   "gemm: output shape mismatch");
     }
+  } else if (scatter_world) {
+    d = at::empty({0, N}, a.options().dtype(out_type));  // results go to the peers' buffers
   } else {
     TORCH_CHECK(!accumulate && !sq_accumulate, "gemm: accumulation needs an output tensor");
     d = batched ? at::empty({nb, M, N}, a.options().dtype(out_type)) : at::empty({M, N}, a.options().dtype(out_type));
@@ -413,7 +425,17 @@ std::vector<at::Tensor> gemm(at::Tensor a, at::Tensor b, bool a_mn, bool b_mn, c
   BgnGemmArgs g = {};
   g.a = a.data_ptr(); g.b = b.data_ptr(); g.d = d.data_ptr();
   g.M = (int)M; g.N = (int)N; g.K = (int)K;
-  g.lda = a.stride(-2); g.ldb = b.stride(-2); g.ldd = d.stride(-2);
+  g.lda = a.stride(-2); g.ldb = b.stride(-2); g.ldd = scatter_world ? N : d.stride(-2);
+  if (gather_world) {
+    g.gather_world = (int)gather_world; g.gather_rows = (int)a.size(0);
+    for (int64_t r = 0; r < gather_world; ++r) g.a_peers[r] = reinterpret_cast<const void*>(a_peer_ptrs[r]);
+  }
+  if (scatter_world) {
+    TORCH_CHECK(d_rows_per_rank > 0 && d_rows_per_rank * scatter_world >= M && d_slot >= 0 && d_slot < scatter_world,
+                "gemm: scatter needs rows_per_rank * world >= M and a slot below world");
+    g.scatter_world = (int)scatter_world; g.scatter_rows = (int)d_rows_per_rank; g.scatter_slot = (int)d_slot;
+    for (int64_t r = 0; r < scatter_world; ++r) g.d_peers[r] = reinterpret_cast<void*>(d_peer_ptrs[r]);
+  }
   g.a_mn = a_mn; g.b_mn = b_mn; g.fmt = fmt; g.out_f32 = out_f32;
   at::Tensor bias_c;
   if (bias.has_value()) {
@@ -449,6 +471,49 @@ std::vector<at::Tensor> gemm(at::Tensor a, at::Tensor b, bool a_mn, bool b_mn, c
   int* st = status.has_value() ? status->data_ptr<int>() : status_ptr(a);
   check(bgn_gemm(&g, st, stream()), "gemm");
   return {d, aux_out};
+}
+
+// ---- peer-memory helpers -------------------------------------------------------------------
+
+void peer_barrier(std::vector<int64_t> flag_ptrs, int64_t rank, int64_t epoch, int64_t budget_cycles,
+                  c10::optional<at::Tensor> status) {
+  const int64_t world = (int64_t)flag_ptrs.size();
+  TORCH_CHECK(world >= 1 && world <= kPeerMax && rank >= 0 && rank < world, "peer_barrier: 1..8 ranks");
+  PeerFlagTable table = {};
+  for (int64_t r = 0; r < world; ++r) table.flags[r] = reinterpret_cast<unsigned*>(flag_ptrs[r]);
+  int* st = status.has_value() ? status->data_ptr<int>() : status_ptr_current();
+  check(bgn_peer_barrier(&table, (int)rank, (int)world, (unsigned)epoch, budget_cycles, st, stream()), "peer_barrier");
+}
+
+// out = residual + sum over slots; `slots` is a [world, rows, cols] view of this rank's slot region.
+at::Tensor slot_reduce(at::Tensor slots, c10::optional<at::Tensor> residual, c10::optional<at::Tensor> out) {
+  CHECK_CUDA_CONTIG(slots);
+  TORCH_CHECK(slots.dim() == 3, "slot_reduce: [world, rows, cols]");
+  c10::cuda::CUDAGuard guard(slots.device());
+  at::Tensor o = out.has_value() ? *out : at::empty({slots.size(1), slots.size(2)}, slots.options());
+  CHECK_CUDA_CONTIG(o);
+  TORCH_CHECK(o.numel() == slots.size(1) * slots.size(2) && o.scalar_type() == slots.scalar_type());
+  const void* res = nullptr;
+  if (residual.has_value()) {
+    CHECK_CUDA_CONTIG((*residual));
+    TORCH_CHECK(residual->numel() == o.numel() && residual->scalar_type() == slots.scalar_type());
+    res = residual->data_ptr();
+  }
+  check(bgn_slot_reduce(slots.data_ptr(), (int)slots.size(0), o.numel(), res, o.data_ptr(), fmt16(slots), stream()),
+        "slot_reduce");
+  return o;
+}
+
+// Row block o of src [world * rows, cols] goes to peer o's slot region at slot `slot`.
+void peer_push(at::Tensor src, std::vector<int64_t> dst_ptrs, int64_t slot) {
+  TORCH_CHECK(src.is_cuda() && src.dim() == 2 && src.stride(1) == 1 && src.element_size() == 2, "peer_push: 16-bit 2-D source");
+  const int64_t world = (int64_t)dst_ptrs.size();
+  TORCH_CHECK(world >= 1 && world <= kPeerMax && src.size(0) % world == 0 && slot >= 0 && slot < world);
+  c10::cuda::CUDAGuard guard(src.device());
+  PeerPtrTable table = {};
+  for (int64_t r = 0; r < world; ++r) table.ptrs[r] = reinterpret_cast<void*>(dst_ptrs[r]);
+  check(bgn_peer_push(src.data_ptr(), src.stride(0), &table, (int)slot, src.size(0) / world, src.size(1), (int)world,
+                      stream()), "peer_push");
 }
 
 void proj_contract(at::Tensor g_proj, at::Tensor a_proj, at::Tensor acc, int64_t n, int64_t s, int64_t p, int64_t col_off) {
@@ -514,12 +579,17 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("multi_sumsq", &multi_sumsq, py::arg("tensors"), py::arg("out"), py::arg("accumulate") = false,
         py::arg("max_norm") = 0.0);
   m.def("row_sumsq", &row_sumsq);
+  m.def("peer_barrier", &peer_barrier, py::arg("flag_ptrs"), py::arg("rank"), py::arg("epoch"),
+        py::arg("budget_cycles") = 0, py::arg("status") = py::none());
+  m.def("slot_reduce", &slot_reduce, py::arg("slots"), py::arg("residual") = py::none(), py::arg("out") = py::none());
+  m.def("peer_push", &peer_push, py::arg("src"), py::arg("dst_ptrs"), py::arg("slot"));
   m.def("cov_syrk", &cov_syrk, py::arg("x"), py::arg("dst_ptrs"), py::arg("row_start"), py::arg("local"),
         py::arg("full") = false, py::arg("num_rows") = -1, py::arg("local_upper") = false);
   m.def("gemm", &gemm, py::arg("a"), py::arg("b"), py::arg("a_mn") = false, py::arg("b_mn") = false,
         py::arg("out") = py::none(), py::arg("out_f32") = false, py::arg("bias") = py::none(),
         py::arg("accumulate") = false, py::arg("aux_p") = py::none(), py::arg("cta_group") = 2,
-        py::arg("sq_accumulate") = false, py::arg("wait_cycles") = 0, py::arg("status") = py::none(), py::arg("panel") = 0, py::arg("trace") = py::none(), py::arg("no_tma_store") = false, py::arg("wide") = false);
+        py::arg("sq_accumulate") = false, py::arg("wait_cycles") = 0, py::arg("status") = py::none(), py::arg("panel") = 0, py::arg("trace") = py::none(), py::arg("no_tma_store") = false, py::arg("wide") = false, py::arg("a_peer_ptrs") = std::vector<int64_t>{}, py::arg("d_peer_ptrs") = std::vector<int64_t>{},
+        py::arg("d_rows_per_rank") = 0, py::arg("d_slot") = 0);
   m.def("proj_contract", &proj_contract);
   m.def("proj_token_rows", &proj_token_rows);
   m.def("wait_probe", &wait_probe);

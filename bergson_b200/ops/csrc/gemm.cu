@@ -63,7 +63,8 @@ static bool gemm_tmap_blocked(CUtensorMap* map, const void* base, int fmt, uint6
 
 template <int CG, int FMT, bool OUT32>
 static cudaError_t launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tp, const CUtensorMap& td,
-                               const GemmParams& p, int grid, int* status, cudaStream_t stream) {
+                               const GemmPeerMaps& peers, const GemmParams& p, int grid, int* status,
+                               cudaStream_t stream) {
   auto kern = gemm_kernel<CG, FMT, OUT32>;
   static bool attr_set = false;  // one flag per instantiation
   if (!attr_set) {
@@ -83,7 +84,7 @@ static cudaError_t launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, con
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, kern, ta, tb, tp, td, p, status);
+  return cudaLaunchKernelEx(&cfg, kern, ta, tb, tp, td, peers, p, status);
 }
 
 template <int FMT, bool OUT32>
@@ -122,12 +123,31 @@ extern "C" int bgn_gemm(const BgnGemmArgs* a, int* status, cudaStream_t stream) 
   if (a->aux_n < 0 || a->aux_n > 64 || a->aux_n % 16) return int(cudaErrorInvalidValue);
   if (a->sq_accumulate && !a->out_f32) return int(cudaErrorInvalidValue);
   CUtensorMap ta, tb, tp;
+  static GemmPeerMaps no_peers;  // zero-initialised placeholder when A is not gathered
+  GemmPeerMaps gathered;
+  const bool gather = a->gather_world > 0, scatter = a->scatter_world > 0;
+  if (gather || scatter) {
+    if (a->batch != 1 || a->a_mn || a->out_f32 || a->accumulate || a->sq_accumulate) return int(cudaErrorInvalidValue);
+    if (gather && (a->gather_world > kGemmMaxPeers || a->gather_rows % 128 ||
+                   long(a->gather_world) * a->gather_rows != a->M))
+      return int(cudaErrorInvalidValue);
+    if (scatter && (a->scatter_world > kGemmMaxPeers || a->scatter_rows <= 0 || a->scatter_slot < 0 ||
+                    a->scatter_slot >= a->scatter_world || long(a->scatter_world) * a->scatter_rows < a->M))
+      return int(cudaErrorInvalidValue);
+  }
   const uint64_t B = uint64_t(a->batch);
   // A: K-major [M, K] (box 64 k x 128 rows) or MN-major [K, M] (64 m x 64 k slabs; one blocked
   // load when M is a multiple of 64, else one load per slab).
   const bool a_blocked = a->a_mn && a->M % 64 == 0;
   const bool b_blocked = a->b_mn && a->N % 64 == 0;
-  const bool ok_a = !a->a_mn ? gemm_tmap(&ta, a->a, a->fmt, a->K, a->M, B, a->lda, a->a_batch_stride, 128)
+  if (gather) {
+    for (int r = 0; r < a->gather_world; ++r)
+      if (!gemm_tmap(&gathered.a[r], a->a_peers[r], a->fmt, a->K, a->gather_rows, 1, a->lda, 0, 128))
+        return int(cudaErrorInvalidPitchValue);
+  }
+  const void* a_base = gather ? a->a_peers[0] : a->a;
+  const uint64_t a_rows = gather ? uint64_t(a->gather_rows) : uint64_t(a->M);
+  const bool ok_a = !a->a_mn ? gemm_tmap(&ta, a_base, a->fmt, a->K, a_rows, B, a->lda, a->a_batch_stride, 128)
                     : a_blocked ? gemm_tmap_blocked(&ta, a->a, a->fmt, a->M, a->K, B, a->lda, a->a_batch_stride, 2)
                                 : gemm_tmap(&ta, a->a, a->fmt, a->M, a->K, B, a->lda, a->a_batch_stride, 64);
   const bool ok_b = !a->b_mn ? gemm_tmap(&tb, a->b, a->fmt, a->K, a->N, B, a->ldb, a->b_batch_stride, kGemmTileN / cg)
@@ -157,7 +177,11 @@ extern "C" int bgn_gemm(const BgnGemmArgs* a, int* status, cudaStream_t stream) 
   // (box 64 columns x 32 rows); anything else is written from registers.
   CUtensorMap td = ta;
   p.tma_store = 0;
-  if (!a->out_f32 && !a->accumulate && a->batch == 1 && !a->no_tma_store) {
+  p.a_gather_rows = gather ? a->gather_rows : 0;
+  p.d_scatter_rows = scatter ? a->scatter_rows : 0;
+  p.d_slot = scatter ? a->scatter_slot : 0;
+  for (int r = 0; r < kGemmMaxPeers; ++r) p.d_peers[r] = scatter && r < a->scatter_world ? a->d_peers[r] : nullptr;
+  if (!a->out_f32 && !a->accumulate && a->batch == 1 && !a->no_tma_store && !scatter) {
     EncodeTiledFn enc = gemm_encode_fn();
     if (enc && (reinterpret_cast<uintptr_t>(a->d) & 15) == 0 && a->ldd % 8 == 0) {
       cuuint64_t dims[2] = {cuuint64_t(a->N), cuuint64_t(a->M)};
@@ -173,7 +197,7 @@ extern "C" int bgn_gemm(const BgnGemmArgs* a, int* status, cudaStream_t stream) 
   p.a_blocked = a_blocked ? 1 : 0;
   p.b_blocked = b_blocked ? 1 : 0;
 
-  const bool wide = cg == 2 && a->wide;
+  const bool wide = cg == 2 && a->wide && !gather && !scatter;
   const int tile_m = wide ? kWideTileM : 128 * cg;
   const long tiles_m = (a->M + tile_m - 1) / tile_m;
   const long tiles_n = (a->N + kGemmTileN - 1) / kGemmTileN + (a->aux_n > 0 ? 1 : 0);
@@ -194,21 +218,22 @@ extern "C" int bgn_gemm(const BgnGemmArgs* a, int* status, cudaStream_t stream) 
   const int grid = int(groups) * cg;
   cudaError_t e;
   const bool bf = a->fmt == 1;
+  const GemmPeerMaps& pm = gather ? gathered : no_peers;
   if (wide) {
     e = a->out_f32 ? (bf ? launch_gemm_wide<1, true>(ta, tb, tp, td, p, grid, status, stream)
                          : launch_gemm_wide<0, true>(ta, tb, tp, td, p, grid, status, stream))
                    : (bf ? launch_gemm_wide<1, false>(ta, tb, tp, td, p, grid, status, stream)
                          : launch_gemm_wide<0, false>(ta, tb, tp, td, p, grid, status, stream));
   } else if (cg == 2) {
-    e = a->out_f32 ? (bf ? launch_gemm<2, 1, true>(ta, tb, tp, td, p, grid, status, stream)
-                         : launch_gemm<2, 0, true>(ta, tb, tp, td, p, grid, status, stream))
-                   : (bf ? launch_gemm<2, 1, false>(ta, tb, tp, td, p, grid, status, stream)
-                         : launch_gemm<2, 0, false>(ta, tb, tp, td, p, grid, status, stream));
+    e = a->out_f32 ? (bf ? launch_gemm<2, 1, true>(ta, tb, tp, td, pm, p, grid, status, stream)
+                         : launch_gemm<2, 0, true>(ta, tb, tp, td, pm, p, grid, status, stream))
+                   : (bf ? launch_gemm<2, 1, false>(ta, tb, tp, td, pm, p, grid, status, stream)
+                         : launch_gemm<2, 0, false>(ta, tb, tp, td, pm, p, grid, status, stream));
   } else {
-    e = a->out_f32 ? (bf ? launch_gemm<1, 1, true>(ta, tb, tp, td, p, grid, status, stream)
-                         : launch_gemm<1, 0, true>(ta, tb, tp, td, p, grid, status, stream))
-                   : (bf ? launch_gemm<1, 1, false>(ta, tb, tp, td, p, grid, status, stream)
-                         : launch_gemm<1, 0, false>(ta, tb, tp, td, p, grid, status, stream));
+    e = a->out_f32 ? (bf ? launch_gemm<1, 1, true>(ta, tb, tp, td, pm, p, grid, status, stream)
+                         : launch_gemm<1, 0, true>(ta, tb, tp, td, pm, p, grid, status, stream))
+                   : (bf ? launch_gemm<1, 1, false>(ta, tb, tp, td, pm, p, grid, status, stream)
+                         : launch_gemm<1, 0, false>(ta, tb, tp, td, pm, p, grid, status, stream));
   }
   return int(e);
 }

@@ -35,6 +35,8 @@ constexpr int kGemmBlockK = 64;
 constexpr int kGemmTileN = 256;
 constexpr int kGemmThreadsV2 = 224;
 
+constexpr int kGemmMaxPeers = 8;
+
 struct GemmParams {
   int M, N, K;
   int a_mn, b_mn;      // 1: operand stored MN-major
@@ -56,6 +58,19 @@ struct GemmParams {
   int tma_store;       // 16-bit output written through shared-memory staging and TMA stores
   long long wait_cycles;
   long long* trace;    // optional: per-tile timestamps of CTA group 0 (8 values per tile); null in production
+  // Peer-memory forms (pair / single-CTA kernel only).
+  int a_gather_rows;   // > 0: rows [r * a_gather_rows, (r + 1) * a_gather_rows) of A live in rank r's
+                       // buffer and are loaded through that rank's tensor map (all-gather -> GEMM)
+  int d_scatter_rows;  // > 0: output rows [o * d_scatter_rows, ...) are stored into rank o's buffer
+                       // d_peers[o], at row d_slot * d_scatter_rows + local row (GEMM -> the push
+                       // half of a reduce-scatter; the owner adds the slots afterwards)
+  int d_slot;
+  void* d_peers[kGemmMaxPeers];
+};
+
+// One tensor map per rank for a row-gathered A operand.
+struct GemmPeerMaps {
+  CUtensorMap a[kGemmMaxPeers];
 };
 
 template <int CG>
@@ -245,8 +260,8 @@ __device__ __forceinline__ GemmTile gemm_tile(long t, int tiles_m, int tiles_n, 
 template <int CG, int FMT, bool OUT32>
 __global__ void __launch_bounds__(kGemmThreadsV2, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-            const __grid_constant__ CUtensorMap tmap_p, const __grid_constant__ CUtensorMap tmap_d, GemmParams p,
-            int* status) {
+            const __grid_constant__ CUtensorMap tmap_p, const __grid_constant__ CUtensorMap tmap_d,
+            const __grid_constant__ GemmPeerMaps peers, GemmParams p, int* status) {
   using S = GemmSmemV2<CG>;
   using InT = typename std::conditional<FMT == 1, __nv_bfloat16, __half>::type;
   constexpr int kStages = S::kStages;
@@ -322,7 +337,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
           if constexpr (CG == 2) bar = map_to_cta(bar, 0);
           const int k0 = kb * kGemmBlockK;
           if (is_a) {
-            load_operand<CG>(a_dst, &tmap_a, bar, p.a_mn != 0, p.a_blocked != 0, 128, m0, k0, tile.batch, three_d);
+            const CUtensorMap* ma = &tmap_a;
+            int m_src = m0;
+            if (p.a_gather_rows > 0) {  // this CTA's 128 rows sit in one rank's buffer
+              const int src = m0 / p.a_gather_rows;
+              ma = &peers.a[src];
+              m_src = m0 - src * p.a_gather_rows;
+            }
+            load_operand<CG>(a_dst, ma, bar, p.a_mn != 0, p.a_blocked != 0, 128, m_src, k0, tile.batch, three_d);
           } else {
             load_operand<CG>(a_dst + S::kABytes, mb, bar, b_mn, p.b_blocked != 0, b_rows, n0, k0, tile.batch,
                              three_d && !tile.aux);
@@ -520,7 +542,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
       } else {
         const int col0 = tile.tn * kGemmTileN;
         const int n_valid = p.N - col0 < kGemmTileN ? p.N - col0 : kGemmTileN;
-        const long d_row_off = long(tile.batch) * p.d_batch_stride + row * p.ldd + col0;
+        long d_row_off = long(tile.batch) * p.d_batch_stride + row * p.ldd + col0;
+        void* d_base = p.d;
+        if (p.d_scatter_rows > 0 && row_ok) {
+          const int owner = int(row / p.d_scatter_rows);
+          d_base = p.d_peers[owner];
+          d_row_off = (long(p.d_slot) * p.d_scatter_rows + (row - long(owner) * p.d_scatter_rows)) * p.ldd + col0;
+        }
 #pragma unroll 1
         for (int c = 0; c < kGemmTileN; c += 32) {
           if (c >= n_valid) break;  // uniform over the CTA
@@ -542,7 +570,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             }
           }
           if constexpr (OUT32) {
-            float* dst = reinterpret_cast<float*>(p.d) + d_row_off + c;
+            float* dst = reinterpret_cast<float*>(d_base) + d_row_off + c;
             if (p.sq_accumulate) {
               if (nv == 32 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
 #pragma unroll
@@ -571,7 +599,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                 if (i < nv) dst[i] = p.accumulate ? dst[i] + v[i] : v[i];
             }
           } else {
-            InT* dst = reinterpret_cast<InT*>(p.d) + d_row_off + c;
+            InT* dst = reinterpret_cast<InT*>(d_base) + d_row_off + c;
             if (nv == 32 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
 #pragma unroll
               for (int i = 0; i < 32; i += 8) {

@@ -40,6 +40,17 @@ struct BgnGemmArgs {
   long long wait_cycles;
   int no_tma_store;  // 1: write 16-bit outputs from registers instead of through TMA stores
   long long* trace;  // optional device buffer for per-tile timestamps of the first CTA group (debugging aid)
+  // Peer-memory forms (pair / single-CTA kernel; K-major A, 16-bit output, batch 1).
+  // gather_world > 0: A is the concatenation over ranks of [gather_rows, K] blocks at a_peers[r]
+  //   (row stride lda; gather_rows a multiple of 128; M must equal gather_world * gather_rows);
+  //   every rank's block is read through its own tensor map with plain (non-multicast) TMA loads.
+  // scatter_world > 0: output rows [o * scatter_rows, (o + 1) * scatter_rows) are stored into
+  //   d_peers[o] at row scatter_slot * scatter_rows + local row (row stride ldd); `d` is unused.
+  //   The stores are complete on the peers only after a cross-rank barrier that follows the kernel.
+  int gather_world, gather_rows;
+  const void* a_peers[8];
+  int scatter_world, scatter_rows, scatter_slot;
+  void* d_peers[8];
 };
 
 int bgn_gemm(const BgnGemmArgs* args, int* status, cudaStream_t stream);

@@ -228,22 +228,39 @@ def gelu(x: Tensor, approximate: str = "none") -> Tensor:
 # --------------------------------------------------------------------------- #
 
 
+_CAUSAL_BIAS: dict = {}
+
+
+def _causal_bias(S: int, dtype: torch.dtype, device) -> Tensor:
+    """``[S, S]`` additive mask: 0 on and below the diagonal, -inf above (cached per shape)."""
+    key = (S, dtype, str(device))
+    bias = _CAUSAL_BIAS.get(key)
+    if bias is None:
+        if len(_CAUSAL_BIAS) > 16:
+            _CAUSAL_BIAS.clear()
+        bias = torch.full((S, S), float("-inf"), dtype=dtype, device=device).triu_(1)
+        _CAUSAL_BIAS[key] = bias
+    return bias
+
+
 def causal_attention(q: Tensor, k: Tensor, v: Tensor, scale: float | None = None) -> Tensor:
     """q: [B, Hq, S, D]; k, v: [B, Hkv, S, D] (Hq a multiple of Hkv). Causal."""
     B, Hq, S, D = q.shape
     Hkv = k.shape[1]
     scale = scale if scale is not None else 1.0 / math.sqrt(D)
     if _composable() or not q.is_cuda:
-        # Explicit softmax(QK^T)V: differentiable to any order on every backend.
+        # Explicit softmax(QK^T)V: differentiable to any order on every backend.  Three passes
+        # over the [B, H, S, S] scores instead of six: the scale goes onto q, the causal mask
+        # is the additive input of the batched product, and the softmax reads and writes the
+        # tensors' own dtype (its arithmetic is fp32 inside the kernel for 16-bit inputs).
         if Hkv != Hq:
             rep = Hq // Hkv
             k = k.repeat_interleave(rep, dim=1)
             v = v.repeat_interleave(rep, dim=1)
-        att = torch.matmul(q, k.transpose(-1, -2)) * scale
-        mask = torch.ones(S, S, dtype=torch.bool, device=q.device).tril()
-        att = att.masked_fill(~mask, float("-inf"))
-        att = torch.softmax(att if att.dtype == torch.float64 else att.float(), dim=-1).to(q.dtype)
-        return torch.matmul(att, v)
+        bias = _causal_bias(S, q.dtype, q.device)
+        att = torch.baddbmm(bias, (q * scale).reshape(B * Hq, S, D), k.reshape(B * Hq, S, D).transpose(1, 2))
+        att = torch.softmax(att, dim=-1)
+        return torch.bmm(att, v.reshape(B * Hq, S, D)).view(B, Hq, S, D)
     return F.scaled_dot_product_attention(
         q, k, v, is_causal=True, scale=scale, enable_gqa=(Hkv != Hq)
     )

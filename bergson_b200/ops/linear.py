@@ -5,8 +5,13 @@
 ``Conv1D`` weight ``[in, out]``).  On CUDA with 16-bit tensors the forward product, the
 input-gradient product ``g @ W`` and the weight-gradient product ``g^T x`` all run on
 ``native.gemm``, which reads the weight in place in whichever orientation the product
-needs (no transposed copies).  Everywhere else, and inside ``ops.composable()``, the
-call is ``F.linear`` / ``addmm`` and stays differentiable to any order.
+needs (no transposed copies).  Inside ``ops.composable()`` (graphs that will be
+differentiated again, as in MAGIC's traced step) the products run on the same kernel through
+``_GemmFn``, whose backward is written with ``_GemmFn`` itself: the derivative of a matrix
+product is two matrix products, so the family is closed under differentiation and every
+order of derivative stays on the tensor cores.  A weight whose output size is not a multiple
+of 8 (GPT-2's 50257-row vocabulary) is zero-padded to the next multiple for the product and
+the result sliced back.  Everywhere else the call is ``F.linear`` / ``addmm``.
 
 A *tap* lets a gradient collector ride on the same passes over the data: when the
 module carries a tap that accepts the call, the forward GEMM also emits
@@ -26,7 +31,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 from torch import Tensor
 
-from .functional import use_fused
+from .functional import _composable, use_fused
 
 _TC_DTYPES = (torch.bfloat16, torch.float16)
 
@@ -55,6 +60,15 @@ class ProjectionTap(Protocol):
         ``[tokens, p16]``); ``lead_shape`` is the shape of ``x`` without its last dimension."""
 
 
+def _kernel_ready(x: Tensor, weight: Tensor) -> bool:
+    """CUDA 16-bit operands and a loaded extension (whether or not composable mode is on)."""
+    if not (x.is_cuda and weight.is_cuda and x.dtype in _TC_DTYPES and weight.dtype == x.dtype and x.numel() > 0):
+        return False
+    from . import native
+
+    return native.available()
+
+
 def gemm_eligible(x: Tensor, weight: Tensor) -> bool:
     return (
         x.dtype in _TC_DTYPES
@@ -66,6 +80,68 @@ def gemm_eligible(x: Tensor, weight: Tensor) -> bool:
         and x.numel() > 0
         and use_fused(x, weight)
     )
+
+
+def _operand_ok(t: Tensor) -> bool:
+    """What a tensor map over a 2-D operand needs: unit inner stride, rows and base on 16 bytes."""
+    return t.dim() == 2 and t.stride(1) == 1 and t.stride(0) % 8 == 0 and t.data_ptr() % 16 == 0 and t.shape[1] % 8 == 0
+
+
+def _as_operand(t: Tensor) -> Tensor:
+    return t if _operand_ok(t) else t.contiguous()
+
+
+class _GemmFn(torch.autograd.Function):
+    """``d = A B`` in the kernel's storage convention: ``a`` holds A as ``[M, K]`` (``a_mn``
+    False) or ``[K, M]`` (True); ``b`` holds B as ``[N, K]`` (``b_mn`` False) or ``[K, N]``
+    (True); ``bias`` ``[N]`` is optional.  The backward calls ``_GemmFn`` again, so a graph
+    built with ``create_graph=True`` can itself be differentiated."""
+
+    @staticmethod
+    def forward(ctx, a: Tensor, b: Tensor, a_mn: bool, b_mn: bool, bias: Tensor | None):
+        from . import native
+
+        a, b = _as_operand(a), _as_operand(b)
+        ctx.save_for_backward(a, b)
+        ctx.layout = (a_mn, b_mn)
+        ctx.has_bias = bias is not None
+        d, _ = native.gemm(a, b, a_mn, b_mn, None, False, bias, False, None, **_gemm_form())
+        return d
+
+    @staticmethod
+    def backward(ctx, g: Tensor):
+        a, b = ctx.saved_tensors
+        a_mn, b_mn = ctx.layout
+        g = _as_operand(g)
+        da = db = dbias = None
+        if ctx.needs_input_grad[0]:
+            # [M, K] = g B, or in A's transposed storage [K, M] = B^T g^T.
+            da = _GemmFn.apply(b, g, not b_mn, False, None) if a_mn else _GemmFn.apply(g, b, False, not b_mn, None)
+        if ctx.needs_input_grad[1]:
+            # [N, K] = g^T A, or in B's transposed storage [K, N] = A^T g.
+            db = _GemmFn.apply(a, g, not a_mn, True, None) if b_mn else _GemmFn.apply(g, a, True, not a_mn, None)
+        if ctx.has_bias and ctx.needs_input_grad[4]:
+            dbias = g.sum(0)
+        return da, db, None, None, dbias
+
+
+def _composable_linear(x: Tensor, weight: Tensor, bias: Tensor | None, layout: str) -> Tensor | None:
+    """The any-order-differentiable product on the kernel, or None when the shapes do not fit."""
+    oi = layout == "oi"
+    in_f = weight.shape[1] if oi else weight.shape[0]
+    out_f = weight.shape[0] if oi else weight.shape[1]
+    if weight.dim() != 2 or in_f % 8 or x.shape[-1] != in_f:
+        return None
+    pad = -out_f % 8
+    if pad and not oi:
+        return None
+    if bias is not None and bias.dtype not in (x.dtype, torch.float32):
+        return None
+    w = F.pad(weight, (0, 0, 0, pad)) if pad else weight
+    bb = F.pad(bias, (0, pad)) if (pad and bias is not None) else bias
+    y = _GemmFn.apply(x.reshape(-1, in_f), w, False, not oi, bb)
+    y = y.view(*x.shape[:-1], out_f + pad)
+    return y[..., :out_f] if pad else y
 
 
 def _aux_fits(rows: int, cols: int, device) -> bool:
@@ -151,6 +227,11 @@ class _LinearFn(torch.autograd.Function):
 def linear(x: Tensor, weight: Tensor, bias: Tensor | None = None, *, layout: str = "oi", module=None,
            tap: ProjectionTap | None = None) -> Tensor:
     """``x @ weight^T + bias`` (``layout="oi"``) or ``x @ weight + bias`` (``layout="io"``)."""
+    if _kernel_ready(x, weight) and (_composable() or weight.dim() == 2 and weight.shape[0] % 8 and layout == "oi"):
+        # Graphs that will be differentiated again, and weights that need padding.
+        y = _composable_linear(x, weight, bias, layout)
+        if y is not None:
+            return y
     if gemm_eligible(x, weight) and (bias is None or bias.dtype in (x.dtype, torch.float32)):
         # A tap only makes sense when a backward pass will follow (grad mode is off inside
         # ``Function.forward``, so the decision is taken here).

@@ -110,3 +110,62 @@ def test_wait_probe_times_out_and_returns():
     assert 100_000 <= int(waited.item()) < 50_000_000
     x = torch.ones(8, device="cuda")
     assert float(x.sum()) == 8.0
+
+
+def _second_order(fn, a, b, probe_a):
+    """Value, first derivatives and a second derivative (d/da, d/db of <dL/db, probe>) of
+    ``L = sum(fn(a, b) * cot)``: enough to exercise the backward of the backward."""
+    y = fn(a, b)
+    cot = torch.linspace(-1, 1, y.numel(), device=y.device, dtype=y.dtype).view_as(y)
+    ga, gb = torch.autograd.grad((y * cot).sum(), (a, b), create_graph=True)
+    inner = (ga * probe_a).sum() + (gb * gb).sum() * 1e-3
+    gga, ggb = torch.autograd.grad(inner, (a, b))
+    return y, ga, gb, gga, ggb
+
+
+@pytest.mark.parametrize("a_mn", [False, True])
+@pytest.mark.parametrize("b_mn", [False, True])
+def test_gemm_function_is_closed_under_differentiation(a_mn, b_mn):
+    from bergson_b200.ops.linear import _GemmFn
+
+    torch.manual_seed(0)
+    M, N, K = 264, 136, 200
+    a = (torch.randn((K, M) if a_mn else (M, K), device="cuda") * 0.5).to(torch.bfloat16).requires_grad_(True)
+    b = (torch.randn((K, N) if b_mn else (N, K), device="cuda") * 0.5).to(torch.bfloat16).requires_grad_(True)
+    probe = torch.randn_like(a)
+
+    def ours(a, b):
+        return _GemmFn.apply(a, b, a_mn, b_mn, None)
+
+    def ref(a, b):
+        A = a.T if a_mn else a
+        B = b if b_mn else b.T
+        return A @ B
+
+    got = _second_order(ours, a, b, probe)
+    a64, b64 = a.detach().double().requires_grad_(True), b.detach().double().requires_grad_(True)
+    want = _second_order(ref, a64, b64, probe.double())
+    for g, w in zip(got, want):
+        scale = w.abs().max().item() + 1e-6
+        assert (g.double() - w).abs().max().item() <= 2e-2 * scale
+
+
+def test_linear_pads_odd_output_sizes_and_stays_twice_differentiable():
+    from bergson_b200 import ops
+    from bergson_b200.ops.linear import linear
+
+    torch.manual_seed(0)
+    x = (torch.randn(4, 40, 64, device="cuda") * 0.5).to(torch.bfloat16).requires_grad_(True)
+    w = (torch.randn(1003, 64, device="cuda") * 0.2).to(torch.bfloat16).requires_grad_(True)  # 1003 % 8 != 0
+    y = linear(x, w)
+    assert y.shape == (4, 40, 1003)
+    torch.testing.assert_close(y.float(), x.float() @ w.float().T, atol=3e-2, rtol=3e-2)
+    with ops.composable():
+        y2 = linear(x, w)
+        (gx,) = torch.autograd.grad(y2.float().pow(2).sum(), x, create_graph=True)
+        (gw,) = torch.autograd.grad(gx.float().pow(2).sum(), w)
+    x64, w64 = x.detach().double().requires_grad_(True), w.detach().double().requires_grad_(True)
+    (gx64,) = torch.autograd.grad((x64 @ w64.T).pow(2).sum(), x64, create_graph=True)
+    (gw64,) = torch.autograd.grad(gx64.pow(2).sum(), w64)
+    assert (gx.double() - gx64).abs().max() <= 3e-2 * gx64.abs().max()
+    assert (gw.double() - gw64).abs().max() <= 5e-2 * gw64.abs().max()
