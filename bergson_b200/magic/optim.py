@@ -46,6 +46,9 @@ class GradientTransformation:
     # Optional fused in-place step ``(grads, state, params, coef) -> (params, state) | None``;
     # None means "not applicable to these tensors", and the caller uses ``update``.
     step_inplace: Callable[..., tuple[Params, OptState] | None] | None = None
+    # Optional fused out-of-place step that stays in the autograd graph (one launch forward,
+    # one for its vector-Jacobian product): ``(grads, state, params) -> (params, state) | None``.
+    step_traced: Callable[..., tuple[Params, OptState] | None] | None = None
 
 
 _FUSED_DTYPES = (torch.float32, torch.bfloat16, torch.float16)
@@ -65,6 +68,31 @@ def _fusable(tensors: list[Tensor]) -> bool:
     return first.is_cuda and first.dtype in _FUSED_DTYPES and all(
         t.device == first.device and t.dtype == first.dtype and t.is_contiguous() and not t.requires_grad
         for t in tensors)
+
+
+class _AdamWStepFn(torch.autograd.Function):
+    """``(p, g, mu, nu) -> (p', mu', nu')`` for a whole parameter list in one launch; the
+    backward is the step's vector-Jacobian product, also one launch.  Differentiable once:
+    that is what a metagradient needs from the optimizer (the second-order terms live in the
+    graph of ``g``)."""
+
+    @staticmethod
+    def forward(ctx, hp: tuple, n: int, *tensors: Tensor):
+        ps, gs, ms, vs = (list(tensors[i * n : (i + 1) * n]) for i in range(4))
+        po, mo, vo = _native().adamw_traced_fwd(ps, gs, ms, vs, *hp)
+        ctx.save_for_backward(*gs, *ms, *vs)
+        ctx.hp, ctx.n = hp, n
+        return (*po, *mo, *vo)
+
+    @staticmethod
+    @torch.autograd.function.once_differentiable
+    def backward(ctx, *cots):
+        n = ctx.n
+        saved = ctx.saved_tensors
+        gs, ms, vs = list(saved[:n]), list(saved[n : 2 * n]), list(saved[2 * n :])
+        cp, cm, cv = list(cots[:n]), list(cots[n : 2 * n]), list(cots[2 * n :])
+        dp, dg, dm, dv = _native().adamw_traced_bwd(gs, ms, vs, cp, cm, cv, *ctx.hp)
+        return (None, None, *dp, *dg, *dm, *dv)
 
 
 def global_norm_coef(grads: list[Tensor], max_norm: float, *, reduce=None) -> Tensor | None:
@@ -219,6 +247,23 @@ def adamw(lr: Schedule | float, betas=(0.9, 0.999), eps: float = 1e-8, eps_root:
                               1.0, coef)
         return dict(params), {"mu": state["mu"], "nu": state["nu"], "count": state["count"] + 1}
 
+    def step_traced(grads: Params, state: OptState, params: Params):
+        keys = [k for k in params if grads.get(k) is not None]
+        ps, gs = [params[k] for k in keys], [grads[k] for k in keys]
+        mus, nus = [state["mu"][k] for k in keys], [state["nu"][k] for k in keys]
+        first = ps[0] if ps else None
+        if (first is None or _native() is None or not first.is_cuda or first.dtype not in _FUSED_DTYPES
+                or not all(t.device == first.device and t.dtype == first.dtype for t in ps + gs)
+                or not all(t.dtype == torch.float32 and t.device == first.device for t in mus + nus)):
+            return None
+        hp = (_lr_of(lr, state["count"]), b1, b2, eps, eps_root, weight_decay, int(state["count"]) + 1)
+        n = len(keys)
+        out = _AdamWStepFn.apply(hp, n, *(t.contiguous() for t in ps + gs + mus + nus))
+        new_params, mu, nu = dict(params), dict(state["mu"]), dict(state["nu"])
+        for i, k in enumerate(keys):
+            new_params[k], mu[k], nu[k] = out[i], out[n + i], out[2 * n + i]
+        return new_params, {"mu": mu, "nu": nu, "count": state["count"] + 1}
+
     def update(grads: Params, state: OptState, *, params: Params, inplace: bool = False):
         if inplace and not any(g is not None and g.requires_grad for g in grads.values()):
             return update_foreach(grads, state, params)
@@ -238,7 +283,7 @@ def adamw(lr: Schedule | float, betas=(0.9, 0.999), eps: float = 1e-8, eps_root:
             updates[k] = -step_lr * d
         return updates, {"mu": mu, "nu": nu, "count": count}
 
-    return GradientTransformation(init, update, step_inplace)
+    return GradientTransformation(init, update, step_inplace, step_traced)
 
 
 # --------------------------------------------------------------------------- #

@@ -314,6 +314,10 @@ class Trainer:
             else:
                 for g in grads.values():
                     g.mul_(coef.to(g.dtype))
+        if not inplace and self.optimizer.step_traced is not None:
+            stepped = self.optimizer.step_traced(grads, state.opt_state, state.params)
+            if stepped is not None:
+                return TrainerState(stepped[0], stepped[1], state.buffers, state.batch_index + 1)
         updates, new_opt = self.optimizer.update(grads, state.opt_state, params=state.params, inplace=inplace)
         new_params = optim.apply_updates(state.params, updates, inplace=inplace)
         return TrainerState(new_params, new_opt, state.buffers, state.batch_index + 1)

@@ -46,6 +46,21 @@ class LlamaAttention(nn.Module):
         out = self.o_proj(o.transpose(1, 2).reshape(B, S, -1))
         return reduce_from_group(out, self.tp_group) if self.tp_group is not None else out
 
+    def forward_seq_parallel(self, h: Tensor, residual: Tensor, cos: Tensor, sin: Tensor, sp, lead) -> Tensor:
+        """``residual + o_proj(attention(...))`` on token shards ``[T / W, d]``: q/k/v gather the
+        tokens inside their GEMMs, o_proj reduce-scatters from its epilogue."""
+        from ..parallel.sequence_parallel import Published, gather_linear, scatter_linear
+
+        B, S = lead
+        pub = Published(sp, h)
+        q = gather_linear(pub, self.q_proj, lead).view(B, S, self.num_heads, self.head_dim)
+        k = gather_linear(pub, self.k_proj, lead).view(B, S, self.kv_heads, self.head_dim)
+        v = gather_linear(pub, self.v_proj, lead).view(B, S, self.kv_heads, self.head_dim)
+        q = ops.rotary(q, cos, sin, self.head_dim)
+        k = ops.rotary(k, cos, sin, self.head_dim)
+        o = ops.causal_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2))
+        return scatter_linear(o.transpose(1, 2).reshape(B * S, -1), self.o_proj, sp, lead, residual)
+
 
 class LlamaMLP(nn.Module):
     def __init__(self, cfg: ModelArgs):
@@ -64,6 +79,13 @@ class LlamaMLP(nn.Module):
         x = copy_to_group(x, self.tp_group)
         return reduce_from_group(self.down_proj(ops.swiglu(self.gate_proj(x), self.up_proj(x))), self.tp_group)
 
+    def forward_seq_parallel(self, h: Tensor, residual: Tensor, sp, lead) -> Tensor:
+        from ..parallel.sequence_parallel import Published, gather_linear, scatter_linear
+
+        pub = Published(sp, h)
+        a = ops.swiglu(gather_linear(pub, self.gate_proj, lead), gather_linear(pub, self.up_proj, lead))
+        return scatter_linear(a, self.down_proj, sp, lead, residual)
+
 
 class LlamaDecoderLayer(nn.Module):
     def __init__(self, cfg: ModelArgs):
@@ -76,6 +98,11 @@ class LlamaDecoderLayer(nn.Module):
     def forward(self, x: Tensor, cos: Tensor, sin: Tensor) -> Tensor:
         x = x + self.self_attn(self.input_layernorm(x), cos, sin)
         return x + self.mlp(self.post_attention_layernorm(x))
+
+    def forward_seq_parallel(self, x: Tensor, cos: Tensor, sin: Tensor, sp, lead) -> Tensor:
+        """The block on a token shard ``[T / W, d]`` (norms and residuals are per token)."""
+        x = self.self_attn.forward_seq_parallel(self.input_layernorm(x), x, cos, sin, sp, lead)
+        return self.mlp.forward_seq_parallel(self.post_attention_layernorm(x), x, sp, lead)
 
 
 class LlamaModel(Backbone):
@@ -112,3 +139,52 @@ class LlamaForCausalLM(NativeCausalLM):
         for layer in m.layers:
             x = maybe_checkpoint(self, layer, x, cos, sin)
         return m.norm(x)
+
+    def _seq_parallel_for(self, input_ids: Tensor):
+        """The sequence-parallel context when this call can take the fused tensor-parallel path:
+        16-bit CUDA weights, a token count that splits into 128-row blocks per rank, frozen
+        sharded weights, and no hook-based collector on the sharded projections."""
+        sp = getattr(self, "_seq_parallel", None)
+        from ..ops.functional import _composable
+
+        if sp is None or self.gradient_checkpointing or _composable():
+            return None
+        w = self.model.layers[0].self_attn.q_proj.weight
+        if not (w.is_cuda and sp.fits(input_ids.numel(), self.config.hidden_size, w.dtype)):
+            return None
+        from ..parallel.sequence_parallel import hooks_compatible
+
+        sharded = [m for layer in self.model.layers for m in (
+            layer.self_attn.q_proj, layer.self_attn.k_proj, layer.self_attn.v_proj, layer.self_attn.o_proj,
+            layer.mlp.gate_proj, layer.mlp.up_proj, layer.mlp.down_proj)]
+        if any(m.weight.requires_grad or m.bias is not None for m in sharded) or self.lm_head.weight.requires_grad:
+            return None
+        if not hooks_compatible(sharded + [self.lm_head]):
+            return None
+        return sp
+
+    def forward(self, input_ids: Tensor, labels: Tensor | None = None, **kwargs):
+        sp = self._seq_parallel_for(input_ids)
+        if sp is None:
+            return super().forward(input_ids, labels=labels, **kwargs)
+        from ..parallel.sequence_parallel import Published, gather_linear
+        from .common import CausalLMOutput
+
+        m = self.model
+        B, S = input_ids.shape
+        lead = (B, S)
+        rows = B * S // sp.world
+        sp.ensure(B * S, self.config.hidden_size, m.embed_tokens.weight.dtype)
+        # This rank's tokens only: the residual stream stays sharded over tokens between blocks.
+        x = m.embed_tokens(input_ids.reshape(-1)[sp.rank * rows : (sp.rank + 1) * rows])
+        cos, sin = ops.rotary_tables(S, self.config.head_dim, self.config.rope_theta, x.device)
+        for layer in m.layers:
+            x = layer.forward_seq_parallel(x, cos, sin, sp, lead)
+        h = m.norm(x)
+        # The head is replicated: every rank gathers all tokens (inside the GEMM) and computes the
+        # same logits and loss.
+        logits = gather_linear(Published(sp, h), self.lm_head, lead, replicated=True).view(B, S, -1)
+        loss = None
+        if labels is not None:
+            loss = self.loss_function(logits, labels, vocab_size=self.config.vocab_size, **kwargs)
+        return CausalLMOutput(logits=logits, loss=loss)

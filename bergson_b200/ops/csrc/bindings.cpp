@@ -69,6 +69,7 @@ at::Tensor contract_counters(int device, int64_t n) {
 }
 
 int* status_ptr(const at::Tensor& like) { return status_tensor(like.get_device()).data_ptr<int>(); }
+int* status_ptr_current() { return status_tensor(at::cuda::current_device()).data_ptr<int>(); }
 
 }  // namespace
 
@@ -327,6 +328,85 @@ void adamw_multi(std::vector<at::Tensor> ps, std::vector<at::Tensor> ms, std::ve
                         (float)wd, bc1, bc2, (float)grad_scale, cf, type_code(ps[0]), stream()), "adamw_multi");
 }
 
+static at::Tensor upload_table12(const std::vector<std::array<int64_t, 12>>& rows, const at::Device& device) {
+  auto host = at::empty({(int64_t)rows.size(), 12}, at::TensorOptions().dtype(at::kLong).pinned_memory(true));
+  std::memcpy(host.data_ptr<int64_t>(), rows.data(), rows.size() * sizeof(rows[0]));
+  return host.to(device, /*non_blocking=*/true);
+}
+
+static void check_moments(const at::Tensor& p, const at::Tensor& t) {
+  CHECK_CUDA_CONTIG(t);
+  TORCH_CHECK(t.scalar_type() == at::kFloat && t.numel() == p.numel() && t.device() == p.device(),
+              "adamw_traced: moments are fp32 tensors of the parameter's size");
+}
+
+// Out-of-place AdamW step for graphs: returns (new params, new mu, new nu), one launch.
+std::vector<std::vector<at::Tensor>> adamw_traced_fwd(std::vector<at::Tensor> ps, std::vector<at::Tensor> gs,
+                                                      std::vector<at::Tensor> ms, std::vector<at::Tensor> vs, double lr,
+                                                      double b1, double b2, double eps, double eps_root, double wd,
+                                                      int64_t step) {
+  const size_t n = ps.size();
+  TORCH_CHECK(n > 0 && gs.size() == n && ms.size() == n && vs.size() == n, "adamw_traced: list lengths differ");
+  c10::cuda::CUDAGuard guard(ps[0].device());
+  std::vector<at::Tensor> po(n), mo(n), vo(n);
+  std::vector<std::array<int64_t, 12>> rows(n);
+  int64_t max_n = 0;
+  for (size_t i = 0; i < n; ++i) {
+    CHECK_CUDA_CONTIG(ps[i]); CHECK_CUDA_CONTIG(gs[i]);
+    TORCH_CHECK(ps[i].scalar_type() == ps[0].scalar_type() && gs[i].scalar_type() == ps[0].scalar_type() &&
+                gs[i].numel() == ps[i].numel() && ps[i].device() == ps[0].device());
+    check_moments(ps[i], ms[i]); check_moments(ps[i], vs[i]);
+    po[i] = at::empty_like(ps[i]); mo[i] = at::empty_like(ms[i]); vo[i] = at::empty_like(vs[i]);
+    rows[i] = {(int64_t)ps[i].data_ptr(), (int64_t)gs[i].data_ptr(), (int64_t)ms[i].data_ptr(), (int64_t)vs[i].data_ptr(),
+               (int64_t)po[i].data_ptr(), (int64_t)mo[i].data_ptr(), (int64_t)vo[i].data_ptr(), 0, 0, 0, ps[i].numel(), 0};
+    max_n = std::max<int64_t>(max_n, ps[i].numel());
+  }
+  auto table = upload_table12(rows, ps[0].device());
+  const float bc1 = 1.f - (float)std::pow(b1, (double)step), bc2 = 1.f - (float)std::pow(b2, (double)step);
+  check(bgn_adamw_traced(table.data_ptr(), (int)n, max_n, 0, (float)lr, (float)b1, (float)b2, (float)eps, (float)eps_root,
+                         (float)wd, bc1, bc2, type_code(ps[0]), stream()), "adamw_traced_fwd");
+  return {po, mo, vo};
+}
+
+// Vector-Jacobian product of that step: cotangents (cp, cm, cv; undefined tensors count as zero)
+// of the outputs -> cotangents (dp, dg, dm, dv) of the inputs.
+std::vector<std::vector<at::Tensor>> adamw_traced_bwd(std::vector<at::Tensor> gs, std::vector<at::Tensor> ms,
+                                                      std::vector<at::Tensor> vs,
+                                                      std::vector<c10::optional<at::Tensor>> cps,
+                                                      std::vector<c10::optional<at::Tensor>> cms,
+                                                      std::vector<c10::optional<at::Tensor>> cvs, double lr, double b1,
+                                                      double b2, double eps, double eps_root, double wd, int64_t step) {
+  const size_t n = gs.size();
+  TORCH_CHECK(n > 0 && ms.size() == n && vs.size() == n && cps.size() == n && cms.size() == n && cvs.size() == n);
+  c10::cuda::CUDAGuard guard(gs[0].device());
+  std::vector<at::Tensor> dp(n), dg(n), dm(n), dv(n), keep;
+  std::vector<std::array<int64_t, 12>> rows(n);
+  int64_t max_n = 0;
+  auto ptr_of = [&](const c10::optional<at::Tensor>& t, const at::Tensor& like, at::ScalarType st) -> int64_t {
+    if (!t.has_value() || !t->defined()) return 0;
+    at::Tensor c = t->contiguous();
+    TORCH_CHECK(c.is_cuda() && c.scalar_type() == st && c.numel() == like.numel(), "adamw_traced: bad cotangent");
+    keep.push_back(c);
+    return (int64_t)c.data_ptr();
+  };
+  for (size_t i = 0; i < n; ++i) {
+    CHECK_CUDA_CONTIG(gs[i]);
+    TORCH_CHECK(gs[i].scalar_type() == gs[0].scalar_type() && gs[i].device() == gs[0].device());
+    check_moments(gs[i], ms[i]); check_moments(gs[i], vs[i]);
+    dp[i] = at::empty_like(gs[i]); dg[i] = at::empty_like(gs[i]); dm[i] = at::empty_like(ms[i]); dv[i] = at::empty_like(vs[i]);
+    rows[i] = {(int64_t)gs[i].data_ptr(), (int64_t)ms[i].data_ptr(), (int64_t)vs[i].data_ptr(),
+               ptr_of(cps[i], gs[i], gs[0].scalar_type()), ptr_of(cms[i], gs[i], at::kFloat), ptr_of(cvs[i], gs[i], at::kFloat),
+               (int64_t)dp[i].data_ptr(), (int64_t)dg[i].data_ptr(), (int64_t)dm[i].data_ptr(), (int64_t)dv[i].data_ptr(),
+               gs[i].numel(), 0};
+    max_n = std::max<int64_t>(max_n, gs[i].numel());
+  }
+  auto table = upload_table12(rows, gs[0].device());
+  const float bc1 = 1.f - (float)std::pow(b1, (double)step), bc2 = 1.f - (float)std::pow(b2, (double)step);
+  check(bgn_adamw_traced(table.data_ptr(), (int)n, max_n, 1, (float)lr, (float)b1, (float)b2, (float)eps, (float)eps_root,
+                         (float)wd, bc1, bc2, type_code(gs[0]), stream()), "adamw_traced_bwd");
+  return {dp, dg, dm, dv};
+}
+
 // out[0] (+)= sum of squares of every tensor in `xs`; with max_norm > 0 also
 // out[1] = min(1, max_norm / (sqrt(out[0]) + 1e-6)).  `out` is fp32 with at least two elements.
 void multi_sumsq(std::vector<at::Tensor> xs, at::Tensor out, bool accumulate, double max_norm) {
@@ -576,6 +656,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("adamw_multi", &adamw_multi, py::arg("params"), py::arg("mu"), py::arg("nu"), py::arg("grads"), py::arg("lr"),
         py::arg("b1"), py::arg("b2"), py::arg("eps"), py::arg("eps_root"), py::arg("weight_decay"), py::arg("step"),
         py::arg("grad_scale") = 1.0, py::arg("coef") = py::none());
+  m.def("adamw_traced_fwd", &adamw_traced_fwd);
+  m.def("adamw_traced_bwd", &adamw_traced_bwd);
   m.def("multi_sumsq", &multi_sumsq, py::arg("tensors"), py::arg("out"), py::arg("accumulate") = false,
         py::arg("max_norm") = 0.0);
   m.def("row_sumsq", &row_sumsq);

@@ -545,6 +545,75 @@ __global__ void adamw_multi_kernel(const AdamEntry* __restrict__ table, float lr
   }
 }
 
+// Out-of-place AdamW over a list of tensors for steps that stay in an autograd graph, and the
+// vector-Jacobian product of that step.  Entries are 12 eight-byte words.
+//   forward : {p, g, m, v, p_out, m_out, v_out, -, -, -, n, -}
+//   backward: {g, m, v, cp, cm, cv, dp, dg, dm, dv, n, -}  (cp/cm/cv: cotangents of the outputs,
+//             null = zero; m and v are the moments *before* the step)
+// p, g, p_out, cp, dp, dg have element type T; moments and their cotangents are fp32.
+struct AdamTraceEntry {
+  void* w[10];
+  long n;
+  long reserved;
+};
+
+template <typename T>
+__global__ void adamw_traced_fwd_kernel(const AdamTraceEntry* __restrict__ table, float lr, float b1, float b2,
+                                        float eps, float eps_root, float wd, float bc1, float bc2) {
+  const AdamTraceEntry e = table[blockIdx.y];
+  const T* p = static_cast<const T*>(e.w[0]);
+  const T* g = static_cast<const T*>(e.w[1]);
+  const float* m = static_cast<const float*>(e.w[2]);
+  const float* v = static_cast<const float*>(e.w[3]);
+  T* po = static_cast<T*>(e.w[4]);
+  float* mo = static_cast<float*>(e.w[5]);
+  float* vo = static_cast<float*>(e.w[6]);
+  for (long i = blockIdx.x * long(blockDim.x) + threadIdx.x; i < e.n; i += long(gridDim.x) * blockDim.x) {
+    const float gi = to_float<T>(g[i]);
+    const float mi = b1 * m[i] + (1.f - b1) * gi;
+    const float vi = b2 * v[i] + (1.f - b2) * gi * gi;
+    const float pf = to_float<T>(p[i]);
+    const float upd = (mi / bc1) / (sqrtf(vi / bc2 + eps_root) + eps) + wd * pf;
+    mo[i] = mi;
+    vo[i] = vi;
+    po[i] = from_float<T>(pf - lr * upd);
+  }
+}
+
+template <typename T>
+__global__ void adamw_vjp_kernel(const AdamTraceEntry* __restrict__ table, float lr, float b1, float b2, float eps,
+                                 float eps_root, float wd, float bc1, float bc2) {
+  const AdamTraceEntry e = table[blockIdx.y];
+  const T* g = static_cast<const T*>(e.w[0]);
+  const float* m = static_cast<const float*>(e.w[1]);
+  const float* v = static_cast<const float*>(e.w[2]);
+  const T* cp = static_cast<const T*>(e.w[3]);
+  const float* cm = static_cast<const float*>(e.w[4]);
+  const float* cv = static_cast<const float*>(e.w[5]);
+  T* dp = static_cast<T*>(e.w[6]);
+  T* dg = static_cast<T*>(e.w[7]);
+  float* dm = static_cast<float*>(e.w[8]);
+  float* dv = static_cast<float*>(e.w[9]);
+  for (long i = blockIdx.x * long(blockDim.x) + threadIdx.x; i < e.n; i += long(gridDim.x) * blockDim.x) {
+    const float gi = to_float<T>(g[i]);
+    const float mi = b1 * m[i] + (1.f - b1) * gi;  // the step's new moments, recomputed
+    const float vi = b2 * v[i] + (1.f - b2) * gi * gi;
+    const float c_p = cp ? to_float<T>(cp[i]) : 0.f;
+    const float s = sqrtf(vi / bc2 + eps_root);
+    const float den = s + eps;
+    const float du = -lr * c_p;                      // cotangent of the update direction
+    const float d_mhat = du / den;
+    const float d_s = -du * (mi / bc1) / (den * den);
+    const float d_vhat = s > 0.f ? d_s / (2.f * s) : 0.f;
+    const float d_m = (cm ? cm[i] : 0.f) + d_mhat / bc1;
+    const float d_v = (cv ? cv[i] : 0.f) + d_vhat / bc2;
+    dp[i] = from_float<T>(c_p * (1.f - lr * wd));
+    dg[i] = from_float<T>((1.f - b1) * d_m + 2.f * (1.f - b2) * gi * d_v);
+    dm[i] = b1 * d_m;
+    dv[i] = b2 * d_v;
+  }
+}
+
 // Sum of squares over a list of tensors (entries reuse AdamEntry: g = data, n = elements).
 // Every block writes one partial; `multi_sumsq_finish` adds them in a fixed order, so the
 // result does not depend on scheduling.
@@ -753,6 +822,28 @@ extern "C" int bgn_adamw_multi(const void* table, int n_tensors, long max_n, flo
   BGN_DISPATCH(type, {
     adamw_multi_kernel<T><<<grid, 256, 0, st>>>((const AdamEntry*)table, lr, b1, b2, eps, eps_root, wd, bc1, bc2,
                                                 gscale, coef);
+  });
+  return int(cudaGetLastError());
+}
+
+static inline dim3 multi_grid(int n_tensors, long max_n) {
+  long per_row = (max_n + 256 * 8 - 1) / (256 * 8);
+  per_row = per_row < 1 ? 1 : (per_row > 128 ? 128 : per_row);
+  return dim3((unsigned)per_row, (unsigned)n_tensors);
+}
+
+extern "C" int bgn_adamw_traced(const void* table, int n_tensors, long max_n, int backward, float lr, float b1,
+                                float b2, float eps, float eps_root, float wd, float bc1, float bc2, int type,
+                                cudaStream_t st) {
+  if (n_tensors <= 0) return 0;
+  if (n_tensors > 65535) return int(cudaErrorInvalidValue);
+  const dim3 grid = multi_grid(n_tensors, max_n);
+  BGN_DISPATCH(type, {
+    if (backward)
+      adamw_vjp_kernel<T><<<grid, 256, 0, st>>>((const AdamTraceEntry*)table, lr, b1, b2, eps, eps_root, wd, bc1, bc2);
+    else
+      adamw_traced_fwd_kernel<T><<<grid, 256, 0, st>>>((const AdamTraceEntry*)table, lr, b1, b2, eps, eps_root, wd,
+                                                       bc1, bc2);
   });
   return int(cudaGetLastError());
 }

@@ -88,6 +88,15 @@ int bgn_adamw_step(float* p, float* m, float* v, const void* g, void* p_model, l
 int bgn_adamw_multi(const void* table, int n_tensors, long max_n, float lr, float b1, float b2, float eps,
                     float eps_root, float wd, float bc1, float bc2, float gscale, const float* coef,
                     int type, cudaStream_t stream);
+// Out-of-place AdamW over a list of tensors (backward == 0) and the vector-Jacobian product of
+// that step (backward == 1).  `table`: n_tensors entries of twelve 8-byte words,
+//   forward : {p, g, m, v, p_out, m_out, v_out, 0, 0, 0, n, 0}
+//   backward: {g, m, v, cp, cm, cv, dp, dg, dm, dv, n, 0}
+// with m, v the moments before the step, cp/cm/cv the cotangents of the step's outputs (null =
+// zero) and dp/dg/dm/dv the cotangents of its inputs.  p, g and their cotangents have element
+// type `type`; moments are fp32.
+int bgn_adamw_traced(const void* table, int n_tensors, long max_n, int backward, float lr, float b1, float b2,
+                     float eps, float eps_root, float wd, float bc1, float bc2, int type, cudaStream_t stream);
 // Sum of squares over a list of tensors (table entries as above, only g and n are read) into
 // out[0] (added to it when `accumulate`); with max_norm > 0, out[1] = min(1, max_norm /
 // (sqrt(out[0]) + 1e-6)).  `partials` holds bgn_multi_sumsq_blocks() * n_tensors floats; the

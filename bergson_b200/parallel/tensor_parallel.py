@@ -6,6 +6,11 @@ is copied into the group (backward: all-reduce of the input gradient) and the bl
 is all-reduced (backward: identity).  Module names are unchanged, so stores and normaliser
 keys do not depend on the parallel layout.
 
+On GPUs with peer memory the same sharding runs *sequence-parallel*: the residual stream is
+split over tokens between blocks and both collectives move into the GEMM kernels
+(all-gather -> GEMM for the column-parallel projections, GEMM -> reduce-scatter for the
+row-parallel ones; see ``sequence_parallel``).
+
 Per-example projected gradients need no gathering: ``P_out (G^T A) P_in^T`` is a sum over
 the shards of the split dimension, so each rank projects with its *slice* of the projection
 matrix and the ``[N, p, p]`` blocks are summed over the group (one all-reduce of the row
@@ -96,4 +101,14 @@ def apply_tensor_parallel(model, group=None):
             setattr(mlp, name, _shard_linear(getattr(mlp, name), "out", rank, size))
         mlp.down_proj = _shard_linear(mlp.down_proj, "in", rank, size)
         mlp.tp_group = group
+    # With peer memory the blocks run sequence-parallel with the collectives inside the GEMMs
+    # (``sequence_parallel``); the all-reduce path above remains for everything else (CPU / gloo,
+    # odd token counts, trainable sharded weights, hook-based collectors).
+    import os
+
+    from .sequence_parallel import SeqParallel
+
+    sp = SeqParallel(group)
+    if os.environ.get("BERGSON_B200_DISABLE_PEER", "0") != "1" and sp.available():
+        model._seq_parallel = sp
     return model

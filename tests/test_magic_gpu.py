@@ -1,5 +1,5 @@
 """MAGIC's in-place training step on the GPU: the multi-tensor AdamW kernel and the fused
-global-norm clipping coefficient against fp32 PyTorch, and the trainer taking that path."""
+global-norm clipping coefficient against fp32 PyTorch, and the trainer taking that path; the traced step and its VJP kernel."""
 
 import pytest
 import torch
@@ -107,3 +107,53 @@ def test_trainer_inplace_step_uses_the_fused_kernel_and_matches_functional(monke
         torch.testing.assert_close(state.params[k], want.params[k], atol=2e-6, rtol=1e-4)
         torch.testing.assert_close(state.opt_state["nu"][k], want.opt_state["nu"][k], atol=1e-10, rtol=1e-4)
     assert optim.global_norm_coef([torch.ones(3)], 1.0) is None  # CPU tensors: not eligible
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_traced_adamw_step_and_its_vjp_match_autograd(native, dtype):
+    """The one-launch traced step and its hand-written VJP against the same update written
+    with differentiable torch operations (fp64 autograd)."""
+    from bergson_b200.magic import optim
+
+    torch.manual_seed(0)
+    shapes = {"a": (33, 17), "b": (129,), "c": (4, 4, 8)}
+    params = {k: torch.randn(s, device="cuda").to(dtype) for k, s in shapes.items()}
+    grads = {k: (torch.randn(s, device="cuda") * 0.1).to(dtype) for k, s in shapes.items()}
+    opt = optim.adamw(lambda i: 1e-2, betas=(0.9, 0.95), eps=1e-8, eps_root=1e-8, weight_decay=0.1)
+    state = opt.init(params)
+    for k in shapes:  # non-trivial moments, third step
+        state["mu"][k] = torch.randn(shapes[k], device="cuda") * 0.05
+        state["nu"][k] = torch.rand(shapes[k], device="cuda") * 0.01
+    state["count"] = torch.tensor(2)
+
+    def run(ps, gs, mus, nus, fused):
+        st = {"mu": mus, "nu": nus, "count": state["count"]}
+        if fused:
+            new_p, new_s = opt.step_traced(gs, st, ps)
+        else:
+            upd, new_s = opt.update(gs, st, params=ps, inplace=False)
+            new_p = optim.apply_updates(ps, upd)
+        return new_p, new_s
+
+    leaves = [{k: v.clone().requires_grad_(True) for k, v in d.items()} for d in (params, grads, state["mu"], state["nu"])]
+    new_p, new_s = run(*leaves, fused=True)
+    assert new_p["a"].grad_fn is not None and type(new_p["a"].grad_fn).__name__.startswith("_AdamWStepFn")
+    ref_leaves = [{k: v.double().requires_grad_(True) for k, v in d.items()} for d in (params, grads, state["mu"], state["nu"])]
+    ref_p, ref_s = run(*ref_leaves, fused=False)
+    tol = 1e-5 if dtype == torch.float32 else 1e-2
+    for k in shapes:
+        torch.testing.assert_close(new_p[k].double(), ref_p[k], atol=tol, rtol=tol)
+        torch.testing.assert_close(new_s["nu"][k].double(), ref_s["nu"][k], atol=1e-6, rtol=1e-5)
+
+    def vjp(new_p, new_s, leaves, cast):
+        outs = [new_p[k] for k in shapes] + [new_s["mu"][k] for k in shapes] + [new_s["nu"][k] for k in shapes]
+        gen = torch.Generator(device="cuda").manual_seed(1)
+        cots = [torch.randn(o.shape, device="cuda", generator=gen).to(cast(o)) for o in outs]
+        ins = [d[k] for d in leaves for k in shapes]
+        return torch.autograd.grad(outs, ins, grad_outputs=cots)
+
+    got = vjp(new_p, new_s, leaves, lambda o: o.dtype)
+    want = vjp(ref_p, ref_s, ref_leaves, lambda o: torch.float64)
+    for g, w in zip(got, want):
+        scale = w.abs().max().item() + 1e-12
+        assert (g.double() - w).abs().max().item() <= (1e-4 if dtype == torch.float32 else 3e-2) * scale
