@@ -132,6 +132,9 @@ class LlamaForCausalLM(NativeCausalLM):
 
     def hidden(self, input_ids: Tensor) -> Tensor:
         m = self.model
+        sp = self._seq_parallel_for(input_ids)
+        if sp is not None:
+            return self._hidden_seq_parallel(input_ids, sp)
         x = m.embed_tokens(input_ids)
         cos, sin = ops.rotary_tables(
             input_ids.shape[1], self.config.head_dim, self.config.rope_theta, x.device
@@ -143,48 +146,62 @@ class LlamaForCausalLM(NativeCausalLM):
     def _seq_parallel_for(self, input_ids: Tensor):
         """The sequence-parallel context when this call can take the fused tensor-parallel path:
         16-bit CUDA weights, a token count that splits into 128-row blocks per rank, frozen
-        sharded weights, and no hook-based collector on the sharded projections."""
+        sharded weights, and no hook-based collector on the sharded projections.  The reason for
+        staying on the all-reduce path is printed once."""
         sp = getattr(self, "_seq_parallel", None)
-        from ..ops.functional import _composable
+        if sp is None:
+            return None
+        reason = self._seq_parallel_obstacle(sp, input_ids)
+        if reason is None:
+            return sp
+        seen = self.__dict__.setdefault("_sp_reasons", set())
+        if reason not in seen:
+            seen.add(reason)
+            if sp.rank == 0:
+                print(f"tensor parallel: all-reduce path for this call ({reason})", flush=True)
+        return None
 
-        if sp is None or self.gradient_checkpointing or _composable():
-            return None
-        w = self.model.layers[0].self_attn.q_proj.weight
-        if not (w.is_cuda and sp.fits(input_ids.numel(), self.config.hidden_size, w.dtype)):
-            return None
+    def _seq_parallel_obstacle(self, sp, input_ids: Tensor) -> str | None:
+        from ..ops.functional import _composable
         from ..parallel.sequence_parallel import hooks_compatible
 
+        if self.gradient_checkpointing:
+            return "gradient checkpointing"
+        if _composable():
+            return "graph will be differentiated again"
+        w = self.model.layers[0].self_attn.q_proj.weight
+        if not w.is_cuda:
+            return "weights are not on a GPU"
+        if not sp.fits(input_ids.numel(), self.config.hidden_size, w.dtype):
+            return (f"{input_ids.numel()} tokens of {w.dtype} do not split into 128-row blocks over "
+                    f"{sp.world} ranks")
         sharded = [m for layer in self.model.layers for m in (
             layer.self_attn.q_proj, layer.self_attn.k_proj, layer.self_attn.v_proj, layer.self_attn.o_proj,
             layer.mlp.gate_proj, layer.mlp.up_proj, layer.mlp.down_proj)]
-        if any(m.weight.requires_grad or m.bias is not None for m in sharded) or self.lm_head.weight.requires_grad:
-            return None
-        if not hooks_compatible(sharded + [self.lm_head]):
-            return None
-        return sp
+        if any(m.weight.requires_grad or m.bias is not None for m in sharded):
+            return "trainable or biased projections"
+        if not hooks_compatible(sharded):
+            return "a hook-based collector is attached"
+        return None
 
-    def forward(self, input_ids: Tensor, labels: Tensor | None = None, **kwargs):
-        sp = self._seq_parallel_for(input_ids)
-        if sp is None:
-            return super().forward(input_ids, labels=labels, **kwargs)
-        from ..parallel.sequence_parallel import Published, gather_linear
-        from .common import CausalLMOutput
+    def _hidden_seq_parallel(self, input_ids: Tensor, sp) -> Tensor:
+        """Final-norm hidden states with the blocks run on token shards (collectives inside the
+        GEMM kernels); the shards are gathered once at the end because the head is replicated."""
+        from ..parallel.sequence_parallel import gather_tokens
 
         m = self.model
         B, S = input_ids.shape
         lead = (B, S)
         rows = B * S // sp.world
         sp.ensure(B * S, self.config.hidden_size, m.embed_tokens.weight.dtype)
+        if not getattr(sp, "_announced", False):
+            sp._announced = True
+            if sp.rank == 0:
+                print(f"tensor parallel: sequence-parallel blocks over {sp.world} ranks, all-gather and "
+                      "reduce-scatter inside the GEMM kernels (peer memory)", flush=True)
         # This rank's tokens only: the residual stream stays sharded over tokens between blocks.
         x = m.embed_tokens(input_ids.reshape(-1)[sp.rank * rows : (sp.rank + 1) * rows])
         cos, sin = ops.rotary_tables(S, self.config.head_dim, self.config.rope_theta, x.device)
         for layer in m.layers:
             x = layer.forward_seq_parallel(x, cos, sin, sp, lead)
-        h = m.norm(x)
-        # The head is replicated: every rank gathers all tokens (inside the GEMM) and computes the
-        # same logits and loss.
-        logits = gather_linear(Published(sp, h), self.lm_head, lead, replicated=True).view(B, S, -1)
-        loss = None
-        if labels is not None:
-            loss = self.loss_function(logits, labels, vocab_size=self.config.vocab_size, **kwargs)
-        return CausalLMOutput(logits=logits, loss=loss)
+        return gather_tokens(m.norm(x), sp).view(B, S, -1)

@@ -258,3 +258,24 @@ def scatter_linear(x: Tensor, module, sp: SeqParallel, lead: tuple[int, int], re
     if tap is None:
         _check_hooks(module, None)
     return _ScatterLinearFn.apply(x, module.weight, residual, sp, module, tap, lead)
+
+
+class _GatherTokensFn(torch.autograd.Function):
+    """Token shards -> all tokens on every rank, for a consumer that every rank evaluates
+    identically (the replicated head and loss): the backward is this rank's slice."""
+
+    @staticmethod
+    def forward(ctx, shard: Tensor, sp: SeqParallel):
+        shard = shard.contiguous()
+        out = torch.empty((sp.world * shard.shape[0], shard.shape[1]), dtype=shard.dtype, device=shard.device)
+        dist.all_gather_into_tensor(out, shard, group=sp.group)
+        ctx.rows, ctx.rank = shard.shape[0], sp.rank
+        return out
+
+    @staticmethod
+    def backward(ctx, g: Tensor):
+        return g[ctx.rank * ctx.rows : (ctx.rank + 1) * ctx.rows].contiguous(), None
+
+
+def gather_tokens(shard: Tensor, sp: SeqParallel) -> Tensor:
+    return _GatherTokensFn.apply(shard, sp)

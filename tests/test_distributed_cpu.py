@@ -75,3 +75,47 @@ def test_failed_rank_raises_in_parent():
 
     with pytest.raises(RuntimeError, match="child exited"):
         launch_distributed_run("boom", _boom, [], DistributedConfig(nproc_per_node=2))
+
+
+def _exchange(rank, local_rank, world, out_dir):
+    """Each rank holds a batch of its own size; module Grams end up on their owners only."""
+    import torch.distributed as dist
+
+    from bergson_b200.collector.dist_autocorrelation_gradient_collector import (
+        assign_modules, exchange_hessian_gradients)
+    from bergson_b200.distributed import init_dist
+
+    init_dist(rank, local_rank, world)
+    names = ["a", "b", "c"]
+    widths = {"a": 3, "b": 5, "c": 2}
+    owner = assign_modules(names, world)
+    hessians: dict = {}
+    for step in range(2):
+        g = torch.Generator().manual_seed(10 * step + rank)
+        rows = 2 + rank + step  # batch sizes differ between ranks and steps
+        grads = {n: torch.randn(rows, widths[n], generator=g) for n in names}
+        exchange_hessian_gradients(grads, hessians, owner, {n for n in names if owner[n] == rank}, rank)
+    torch.save({"owner": owner, "hessians": hessians}, f"{out_dir}/rank{rank}.pt")
+    dist.barrier()
+
+
+def test_distributed_autocorrelation_exchange_two_ranks(tmp_path):
+    from bergson_b200.config import DistributedConfig
+    from bergson_b200.distributed import launch_distributed_run
+
+    launch_distributed_run("exchange", _exchange, [str(tmp_path)], DistributedConfig(nproc_per_node=2))
+    widths = {"a": 3, "b": 5, "c": 2}
+    want = {n: torch.zeros(w, w) for n, w in widths.items()}
+    for step in range(2):
+        for rank in range(2):
+            g = torch.Generator().manual_seed(10 * step + rank)
+            rows = 2 + rank + step
+            for n in ("a", "b", "c"):
+                p = torch.randn(rows, widths[n], generator=g)
+                want[n] += p.T @ p
+    got = [torch.load(tmp_path / f"rank{r}.pt") for r in range(2)]
+    owner = got[0]["owner"]
+    assert owner == {"a": 0, "b": 0, "c": 1}  # contiguous blocks, the first rank takes the extra module
+    for n, r in owner.items():
+        torch.testing.assert_close(got[r]["hessians"][n], want[n], rtol=1e-5, atol=1e-5)
+        assert n not in got[1 - r]["hessians"]

@@ -84,8 +84,14 @@ def test_fused_collectives_two_gpus():
         assert err_ag < 2e-2, (rank, err_ag)
 
 
-def test_tensor_parallel_fused_build_matches_single_gpu(tmp_path):
-    """CLI build on 1 GPU vs tensor-parallel over 2 GPUs (fused projection kernels, bf16)."""
+@pytest.mark.parametrize("data, token_batch, fused", [
+    ("synthetic:zipf?n=16&len=160&vocab=1024&min_len=90", "640", False),   # ragged: all-reduce path
+    ("synthetic:zipf?n=32&len=128&vocab=1024&min_len=128", "1024", True),  # 8 x 128 tokens: sequence-parallel
+])
+def test_tensor_parallel_fused_build_matches_single_gpu(tmp_path, data, token_batch, fused):
+    """CLI build on 1 GPU vs tensor-parallel over 2 GPUs (fused projection kernels, bf16).  With
+    token counts that split into 128-row blocks per rank the blocks run sequence-parallel with
+    the all-gather and the reduce-scatter inside the GEMM kernels."""
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     import subprocess
@@ -99,13 +105,15 @@ def test_tensor_parallel_fused_build_matches_single_gpu(tmp_path):
     root = Path(__file__).resolve().parents[1]
     common = [sys.executable, "-m", "bergson_b200", "build"]
     opts = ["--model", "native:llama-tiny?hidden_size=128&intermediate_size=256&vocab_size=1024&max_position_embeddings=1024", "--precision", "bf16",
-            "--data.dataset", "synthetic:zipf?n=16&len=160&vocab=1024&min_len=90", "--projection_dim", "16",
-            "--token_batch_size", "640", "--store_dtype", "fp32"]
+            "--data.dataset", data, "--projection_dim", "16",
+            "--token_batch_size", token_batch, "--store_dtype", "fp32"]
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     for name, extra in (("one", ["--nproc_per_node", "1"]), ("tp2", ["--nproc_per_node", "2", "--tensor_parallel", "2"])):
         out = subprocess.run(common + [str(tmp_path / name)] + opts + extra, cwd=root, env=env, capture_output=True,
                              text=True, timeout=600)
         assert out.returncode == 0, out.stderr[-2000:]
+        if name == "tp2":
+            assert ("sequence-parallel blocks over 2 ranks" in out.stdout + out.stderr) == fused
     a, b = np.asarray(load_gradients(tmp_path / "one")), np.asarray(load_gradients(tmp_path / "tp2"))
     assert np.abs(b).max() > 0
     assert np.abs(a - b).max() / np.abs(a).max() < 3e-2
@@ -241,3 +249,74 @@ def test_kfac_factors_two_gpus_match_one(tmp_path):
             assert one[k].shape == two[k].shape
             assert float((one[k] - two[k]).norm() / one[k].norm()) < 2e-3, (sub, k)
             assert float((two[k] - two[k].T).abs().max() / two[k].abs().max()) < 1e-5, (sub, k, "not symmetric")
+
+
+def _seq_parallel_worker(rank, world, port, out):
+    import torch.distributed as dist
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        from bergson_b200.ops import Linear, native
+        from bergson_b200.parallel.sequence_parallel import Published, SeqParallel, gather_linear, scatter_linear
+
+        sp = SeqParallel(dist.group.WORLD)
+        assert sp.available()
+        T, D, N_local, lead = 1024, 256, 192, (4, 256)
+        rows = T // world
+        sp.ensure(T, D, torch.bfloat16)
+        torch.manual_seed(7 + rank)
+        col = Linear(D, N_local, bias=False, device="cuda", dtype=torch.bfloat16).requires_grad_(False)
+        row = Linear(N_local, D, bias=False, device="cuda", dtype=torch.bfloat16).requires_grad_(False)
+        errs = []
+        for step in range(3):  # several rounds: the double-buffered regions get reused
+            shard = torch.randn(rows, D, device="cuda").to(torch.bfloat16).requires_grad_(True)
+            y = gather_linear(Published(sp, shard), col, lead)           # [T, N_local]
+            z = scatter_linear(torch.tanh(y), row, sp, lead, residual=shard)  # [rows, D]
+            cot = torch.randn(rows, D, device="cuda").to(torch.bfloat16)
+            (dx,) = torch.autograd.grad(z, shard, cot)
+            # Reference with NCCL collectives and fp32 math.
+            shards = [torch.empty_like(shard) for _ in range(world)]
+            dist.all_gather(shards, shard.detach())
+            x_full = torch.cat(shards).float().requires_grad_(True)
+            y_ref = x_full @ col.weight.float().T
+            part = torch.tanh(y_ref.to(torch.bfloat16).float()) @ row.weight.float().T
+            cots = [torch.empty_like(cot) for _ in range(world)]
+            dist.all_gather(cots, cot)
+            (dx_part,) = torch.autograd.grad(part, x_full, torch.cat(cots).float())
+            summed = part.detach().clone()
+            dist.all_reduce(summed)
+            dist.all_reduce(dx_part)
+            z_ref = summed[rank * rows : (rank + 1) * rows] + shard.detach().float()
+            dx_ref = dx_part[rank * rows : (rank + 1) * rows] + cot.float()
+            errs.append(float((y.float() - y_ref.detach()).abs().max() / y_ref.abs().max()))
+            errs.append(float((z.float() - z_ref).abs().max() / z_ref.abs().max()))
+            errs.append(float((dx.float() - dx_ref).abs().max() / dx_ref.abs().max()))
+        torch.cuda.synchronize()
+        out.put((rank, max(errs), int(native.kernel_status(rank).item()), sp.barriers, sp.fused_gemms))
+    finally:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def test_sequence_parallel_projections_two_gpus():
+    """All-gather -> GEMM and GEMM -> reduce-scatter (forward and backward) against NCCL
+    collectives around fp32 products."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    import torch.multiprocessing as mp
+
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_seq_parallel_worker, args=(r, 2, port, out)) for r in range(2)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=300)
+        assert p.exitcode == 0, f"rank exited with {p.exitcode}"
+    for rank, err, status, barriers, gemms in sorted(out.get(timeout=10) for _ in range(2)):
+        assert status == 0
+        assert err < 3e-2, (rank, err)
+        assert barriers == 3 * 4 and gemms == 3 * 4  # publish, reduce, publish (bwd), reduce (bwd) per round
