@@ -466,7 +466,7 @@ std::vector<at::Tensor> gemm(at::Tensor a, at::Tensor b, bool a_mn, bool b_mn, c
                              c10::optional<at::Tensor> aux_p, int64_t cta_group, bool sq_accumulate,
                              int64_t wait_cycles, c10::optional<at::Tensor> status, int64_t panel, c10::optional<at::Tensor> trace, bool no_tma_store, bool wide,
                              std::vector<int64_t> a_peer_ptrs, std::vector<int64_t> d_peer_ptrs, int64_t d_rows_per_rank,
-                             int64_t d_slot) {
+                             int64_t d_slot, c10::optional<at::Tensor> gather_done, int64_t gather_rank) {
   TORCH_CHECK(a.is_cuda() && b.is_cuda() && a.scalar_type() == b.scalar_type(), "gemm: CUDA operands of one dtype");
   TORCH_CHECK((a.dim() == 2 || a.dim() == 3) && a.dim() == b.dim() && a.stride(-1) == 1 && b.stride(-1) == 1,
               "gemm: 2-D or 3-D operands with contiguous last dimension");
@@ -482,7 +482,11 @@ std::vector<at::Tensor> gemm(at::Tensor a, at::Tensor b, bool a_mn, bool b_mn, c
   if (gather_world || scatter_world) {
     TORCH_CHECK(!batched && !a_mn && !out_f32 && !accumulate && !sq_accumulate, "gemm: peer forms take a K-major 2-D A and write 16-bit outputs");
   }
-  const int64_t M = (a_mn ? a.size(-1) : a.size(-2)) * (gather_world ? gather_world : 1), K = a_mn ? a.size(-2) : a.size(-1);
+  // With gather_done, `a` is the local [M, K] buffer that the kernel completes from the peers'
+  // blocks while it computes (gather-with-copy); otherwise `a` is this rank's block.
+  const bool gather_copy = gather_world > 0 && gather_done.has_value();
+  const int64_t M = (a_mn ? a.size(-1) : a.size(-2)) * (gather_world && !gather_copy ? gather_world : 1),
+                K = a_mn ? a.size(-2) : a.size(-1);
   const int64_t N = b_mn ? b.size(-1) : b.size(-2), Kb = b_mn ? b.size(-2) : b.size(-1);
   TORCH_CHECK(K == Kb, "gemm: reduction lengths differ (", K, " vs ", Kb, ")");
   const auto out_type = out_f32 ? at::kFloat : a.scalar_type();
@@ -507,7 +511,13 @@ std::vector<at::Tensor> gemm(at::Tensor a, at::Tensor b, bool a_mn, bool b_mn, c
   g.M = (int)M; g.N = (int)N; g.K = (int)K;
   g.lda = a.stride(-2); g.ldb = b.stride(-2); g.ldd = scatter_world ? N : d.stride(-2);
   if (gather_world) {
-    g.gather_world = (int)gather_world; g.gather_rows = (int)a.size(0);
+    g.gather_world = (int)gather_world; g.gather_rows = (int)(gather_copy ? a.size(0) / gather_world : a.size(0));
+    if (gather_copy) {
+      TORCH_CHECK(gather_done->is_cuda() && gather_done->scalar_type() == at::kInt && gather_done->numel() >= gather_world &&
+                  a.is_contiguous() && a.size(0) % gather_world == 0, "gemm: gather_done is an int32 tensor of >= world entries; A contiguous");
+      gather_done->zero_();
+      g.gather_copy = 1; g.gather_rank = (int)gather_rank; g.gather_done = gather_done->data_ptr<int>();
+    }
     for (int64_t r = 0; r < gather_world; ++r) g.a_peers[r] = reinterpret_cast<const void*>(a_peer_ptrs[r]);
   }
   if (scatter_world) {
@@ -671,7 +681,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("out") = py::none(), py::arg("out_f32") = false, py::arg("bias") = py::none(),
         py::arg("accumulate") = false, py::arg("aux_p") = py::none(), py::arg("cta_group") = 2,
         py::arg("sq_accumulate") = false, py::arg("wait_cycles") = 0, py::arg("status") = py::none(), py::arg("panel") = 0, py::arg("trace") = py::none(), py::arg("no_tma_store") = false, py::arg("wide") = false, py::arg("a_peer_ptrs") = std::vector<int64_t>{}, py::arg("d_peer_ptrs") = std::vector<int64_t>{},
-        py::arg("d_rows_per_rank") = 0, py::arg("d_slot") = 0);
+        py::arg("d_rows_per_rank") = 0, py::arg("d_slot") = 0, py::arg("gather_done") = py::none(), py::arg("gather_rank") = 0);
   m.def("proj_contract", &proj_contract);
   m.def("proj_token_rows", &proj_token_rows);
   m.def("wait_probe", &wait_probe);

@@ -131,6 +131,10 @@ extern "C" int bgn_gemm(const BgnGemmArgs* a, int* status, cudaStream_t stream) 
     if (gather && (a->gather_world > kGemmMaxPeers || a->gather_rows % 128 ||
                    long(a->gather_world) * a->gather_rows != a->M))
       return int(cudaErrorInvalidValue);
+    if (gather && a->gather_copy &&
+        (a->gather_rows % kWideTileM || a->lda != a->K || !a->gather_done || a->gather_rank < 0 ||
+         a->gather_rank >= a->gather_world || cg != 2 || !a->wide || !a->a))
+      return int(cudaErrorInvalidValue);
     if (scatter && (a->scatter_world > kGemmMaxPeers || a->scatter_rows <= 0 || a->scatter_slot < 0 ||
                     a->scatter_slot >= a->scatter_world || long(a->scatter_world) * a->scatter_rows < a->M))
       return int(cudaErrorInvalidValue);
@@ -140,13 +144,14 @@ extern "C" int bgn_gemm(const BgnGemmArgs* a, int* status, cudaStream_t stream) 
   // load when M is a multiple of 64, else one load per slab).
   const bool a_blocked = a->a_mn && a->M % 64 == 0;
   const bool b_blocked = a->b_mn && a->N % 64 == 0;
-  if (gather) {
+  const bool gather_copy = gather && a->gather_copy;
+  if (gather && !gather_copy) {
     for (int r = 0; r < a->gather_world; ++r)
       if (!gemm_tmap(&gathered.a[r], a->a_peers[r], a->fmt, a->K, a->gather_rows, 1, a->lda, 0, 128))
         return int(cudaErrorInvalidPitchValue);
   }
-  const void* a_base = gather ? a->a_peers[0] : a->a;
-  const uint64_t a_rows = gather ? uint64_t(a->gather_rows) : uint64_t(a->M);
+  const void* a_base = gather && !gather_copy ? a->a_peers[0] : a->a;
+  const uint64_t a_rows = gather && !gather_copy ? uint64_t(a->gather_rows) : uint64_t(a->M);
   const bool ok_a = !a->a_mn ? gemm_tmap(&ta, a_base, a->fmt, a->K, a_rows, B, a->lda, a->a_batch_stride, 128)
                     : a_blocked ? gemm_tmap_blocked(&ta, a->a, a->fmt, a->M, a->K, B, a->lda, a->a_batch_stride, 2)
                                 : gemm_tmap(&ta, a->a, a->fmt, a->M, a->K, B, a->lda, a->a_batch_stride, 64);
@@ -178,6 +183,13 @@ extern "C" int bgn_gemm(const BgnGemmArgs* a, int* status, cudaStream_t stream) 
   CUtensorMap td = ta;
   p.tma_store = 0;
   p.a_gather_rows = gather ? a->gather_rows : 0;
+  p.gather_copy = gather_copy ? 1 : 0;
+  p.gather_rank = gather_copy ? a->gather_rank : 0;
+  p.gather_world = gather_copy ? a->gather_world : 0;
+  p.tm_shift = gather_copy ? a->gather_rank * (a->gather_rows / kWideTileM) : 0;
+  p.gather_done = gather_copy ? a->gather_done : nullptr;
+  p.d_gather_dst = gather_copy ? const_cast<void*>(a->a) : nullptr;
+  for (int r = 0; r < kGemmMaxPeers; ++r) p.gather_src[r] = gather_copy && r < a->gather_world ? a->a_peers[r] : nullptr;
   p.d_scatter_rows = scatter ? a->scatter_rows : 0;
   p.d_slot = scatter ? a->scatter_slot : 0;
   for (int r = 0; r < kGemmMaxPeers; ++r) p.d_peers[r] = scatter && r < a->scatter_world ? a->d_peers[r] : nullptr;
@@ -197,7 +209,9 @@ extern "C" int bgn_gemm(const BgnGemmArgs* a, int* status, cudaStream_t stream) 
   p.a_blocked = a_blocked ? 1 : 0;
   p.b_blocked = b_blocked ? 1 : 0;
 
-  const bool wide = cg == 2 && a->wide && !gather && !scatter;
+  // The pair kernel reads gathered rows straight from the peers; the wide kernel has the
+  // gather-with-copy form and the scatter epilogue.
+  const bool wide = cg == 2 && a->wide && (!gather || gather_copy);
   const int tile_m = wide ? kWideTileM : 128 * cg;
   const long tiles_m = (a->M + tile_m - 1) / tile_m;
   const long tiles_n = (a->N + kGemmTileN - 1) / kGemmTileN + (a->aux_n > 0 ? 1 : 0);
@@ -218,7 +232,7 @@ extern "C" int bgn_gemm(const BgnGemmArgs* a, int* status, cudaStream_t stream) 
   const int grid = int(groups) * cg;
   cudaError_t e;
   const bool bf = a->fmt == 1;
-  const GemmPeerMaps& pm = gather ? gathered : no_peers;
+  const GemmPeerMaps& pm = gather && !gather_copy ? gathered : no_peers;
   if (wide) {
     e = a->out_f32 ? (bf ? launch_gemm_wide<1, true>(ta, tb, tp, td, p, grid, status, stream)
                          : launch_gemm_wide<0, true>(ta, tb, tp, td, p, grid, status, stream))

@@ -66,6 +66,17 @@ struct GemmParams {
                        // half of a reduce-scatter; the owner adds the slots afterwards)
   int d_slot;
   void* d_peers[kGemmMaxPeers];
+  // Gather-with-copy form (wide kernel only): A is the local [M, K] buffer; the row blocks of
+  // the other ranks are pulled into it by one copier warp per CTA while the tiles of this
+  // rank's own rows are computed, so every remote byte crosses NVLink once.  Tiles are visited
+  // starting at this rank's rows (tm_shift); a producer waits (bounded) for gather_done[src] to
+  // reach the number of CTAs before it loads rows that came from rank src.
+  int gather_copy;
+  int gather_rank, gather_world;
+  int tm_shift;
+  const void* gather_src[kGemmMaxPeers];
+  void* d_gather_dst;  // the local [M, K] buffer that tmap_a describes
+  int* gather_done;
 };
 
 // One tensor map per rank for a row-gathered A operand.

@@ -13,7 +13,9 @@
 // the next tile's MMAs already run.  Other outputs (fp32, accumulate, batched) are stored from
 // registers with 32-byte stores.  The two row blocks are released separately.
 //
-// Warp roles: 0 = A producer, 1 = MMA issuer (leader CTA), 2..9 = epilogue, 10 = B producer.
+// Warp roles: 0 = A producer, 1 = MMA issuer (leader CTA), 2..9 = epilogue, 10 = B producer,
+// 11 = copier (gather-with-copy form only: pulls the other ranks' row blocks of A into local
+// memory over NVLink while the tiles of the local rows run; see GemmParams::gather_copy).
 // Operand layouts, the aux (projection) tile column, bias, accumulation, the batched
 // sum-of-squares form and the bounded waits are those of gemm.cuh.
 #pragma once
@@ -22,7 +24,7 @@
 
 namespace bgn {
 
-constexpr int kWideThreads = 352;
+constexpr int kWideThreads = 384;
 constexpr int kWideTileM = 512;     // rows per CTA pair
 constexpr int kWideABytes = 2 * 128 * kGemmBlockK * 2;   // two row blocks
 constexpr int kWideBBytes = 128 * kGemmBlockK * 2;
@@ -37,6 +39,26 @@ __device__ __forceinline__ void st_global_v8(void* ptr, const uint32_t (&r)[8]) 
   asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(ptr), "r"(r[0]), "r"(r[1]), "r"(r[2]),
                "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
                : "memory");
+}
+
+__device__ __forceinline__ uint4 ld_volatile_v4(const uint4* ptr) {
+  uint4 v;
+  asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(ptr));
+  return v;
+}
+
+__device__ __forceinline__ int ld_acquire_gpu(const int* ptr) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(ptr) : "memory");
+  return v;
+}
+
+// Visit order of the row tiles: rotated so that a rank starts with its own rows.
+__device__ __forceinline__ void rotate_tile(GemmTile& tile, const GemmParams& p, int tiles_m) {
+  if (p.tm_shift > 0) {
+    tile.tm += p.tm_shift;
+    if (tile.tm >= tiles_m) tile.tm -= tiles_m;
+  }
 }
 
 template <int FMT, bool OUT32>
@@ -96,9 +118,31 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       const bool is_a = warp == 0;
       uint32_t stage = 0, phase = 0;
       bool ok = true;
+      uint32_t ready_mask = 0;
       for (long t = group; t < num_tiles && ok; t += num_groups) {
-        const GemmTile tile = gemm_tile(t, tiles_m, tiles_n, tiles_nt, p.panel);
+        GemmTile tile = gemm_tile(t, tiles_m, tiles_n, tiles_nt, p.panel);
+        rotate_tile(tile, p, tiles_m);
         const int m0 = tile.tm * kWideTileM + int(cta_rank) * 128;  // row block 1 starts 256 rows further
+        if (is_a && p.gather_copy) {
+          // Rows that belong to another rank are read from the local copy once every CTA's
+          // copier has delivered its slice of that rank's block.
+          const int src = m0 / p.a_gather_rows;
+          if (src != p.gather_rank && !((ready_mask >> src) & 1u)) {
+            const long long start = clock64();
+            bool arrived = false;
+            while (!(arrived = ld_acquire_gpu(p.gather_done + src) >= int(gridDim.x))) {
+              if (clock64() - start > p.wait_cycles) break;
+              __nanosleep(128);
+            }
+            if (!arrived) {
+              atomicCAS(status, kStatusOk, kStatusTimeoutFlag);
+              ok = false;
+              break;
+            }
+            fence_proxy_async();  // generic-proxy stores of the copiers before this thread's TMA loads
+            ready_mask |= 1u << src;
+          }
+        }
         const int b_rows = tile.aux ? p.aux_n / CG : 128;
         const int n0 = tile.aux ? int(cta_rank) * b_rows : tile.tn * kGemmTileN + int(cta_rank) * b_rows;
         const CUtensorMap* mb = tile.aux ? &tmap_p : &tmap_b;
@@ -226,7 +270,8 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 #pragma unroll
     for (int a = 0; a < 2; ++a) empty_addr[a] = map_to_cta(smem_u32(&tmem_empty_bar[a]), 0);
     for (long t = group; t < num_tiles && ok; t += num_groups, ++local_tile) {
-      const GemmTile tile = gemm_tile(t, tiles_m, tiles_n, tiles_nt, p.panel);
+      GemmTile tile = gemm_tile(t, tiles_m, tiles_n, tiles_nt, p.panel);
+      rotate_tile(tile, p, tiles_m);
       const bool tracing = p.trace != nullptr && group == 0 && leader && warp == 2 && lane == 0;
       const long long e0 = tracing ? clock64() : 0;
       ok = mbar_wait_budget(tmem_full_bar, uint32_t(local_tile) & 1u, p.wait_cycles);
@@ -320,7 +365,13 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           if (tracing) p.trace[local_tile * 8 + 5 + rb] = clock64();
           continue;  // this row block is done (barrier arrival included)
         } else {
-          const long d_row_off = long(tile.batch) * p.d_batch_stride + row * p.ldd + col0;
+          long d_row_off = long(tile.batch) * p.d_batch_stride + row * p.ldd + col0;
+          void* d_base = p.d;
+          if (p.d_scatter_rows > 0 && row_ok) {  // the row's owner receives it in this rank's slot
+            const int owner = int(row / p.d_scatter_rows);
+            d_base = p.d_peers[owner];
+            d_row_off = (long(p.d_slot) * p.d_scatter_rows + (row - long(owner) * p.d_scatter_rows)) * p.ldd + col0;
+          }
 #pragma unroll 1
           for (int cc = 0; cc < 128; cc += 32) {
             const int c = half * 128 + cc;
@@ -343,7 +394,7 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
               }
             }
             if constexpr (OUT32) {
-              float* dst = reinterpret_cast<float*>(p.d) + d_row_off + c;
+              float* dst = reinterpret_cast<float*>(d_base) + d_row_off + c;
               if (p.sq_accumulate) {
                 if (nv == 32 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
 #pragma unroll
@@ -374,7 +425,7 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                   if (i < nv) dst[i] = p.accumulate ? dst[i] + v[i] : v[i];
               }
             } else {
-              InT* dst = reinterpret_cast<InT*>(p.d) + d_row_off + c;
+              InT* dst = reinterpret_cast<InT*>(d_base) + d_row_off + c;
               if (nv == 32 && (reinterpret_cast<uintptr_t>(dst) & 31) == 0) {
 #pragma unroll
                 for (int i = 0; i < 32; i += 16) {
@@ -422,6 +473,33 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       }
       if (tracing) p.trace[local_tile * 8 + 4] = e1;
       (void)e0;
+    }
+  }
+
+  else if (warp == 11 && p.gather_copy) {
+    // ---------------- copier: this CTA's slice of every other rank's row block ----------------
+    const long n_vec = long(p.a_gather_rows) * p.K / 8;  // 16-byte packets per rank block
+    const long per = (n_vec + gridDim.x - 1) / gridDim.x;
+    const long lo = long(blockIdx.x) * per;
+    const long hi = lo + per < n_vec ? lo + per : n_vec;
+    for (int s = 1; s < p.gather_world; ++s) {
+      int r = p.gather_rank + s;
+      if (r >= p.gather_world) r -= p.gather_world;
+      const uint4* src = reinterpret_cast<const uint4*>(p.gather_src[r]);
+      uint4* dst = reinterpret_cast<uint4*>(p.d_gather_dst) + long(r) * n_vec;
+      constexpr int kInFlight = 8;
+      for (long i = lo + lane; i < hi; i += 32 * kInFlight) {
+        uint4 v[kInFlight];
+#pragma unroll
+        for (int j = 0; j < kInFlight; ++j)
+          if (i + 32 * j < hi) v[j] = ld_volatile_v4(src + i + 32 * j);
+#pragma unroll
+        for (int j = 0; j < kInFlight; ++j)
+          if (i + 32 * j < hi) dst[i + 32 * j] = v[j];
+      }
+      __syncwarp();
+      __threadfence();
+      if (lane == 0) atomicAdd(p.gather_done + r, 1);
     }
   }
 

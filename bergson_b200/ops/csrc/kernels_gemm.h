@@ -47,7 +47,14 @@ struct BgnGemmArgs {
   // scatter_world > 0: output rows [o * scatter_rows, (o + 1) * scatter_rows) are stored into
   //   d_peers[o] at row scatter_slot * scatter_rows + local row (row stride ldd); `d` is unused.
   //   The stores are complete on the peers only after a cross-rank barrier that follows the kernel.
+  // gather_copy (with gather_world > 0; wide kernel): `a` is a local [M, K] buffer (lda == K)
+  //   whose rows of rank gather_rank are already in place; one copier warp per CTA pulls the other
+  //   ranks' blocks from a_peers[r] into it while the local rows' tiles run, and tiles of remote
+  //   rows start once gather_done[r] (device ints, zero before the launch) shows that every CTA
+  //   delivered its slice.  gather_rows must be a multiple of 512.
   int gather_world, gather_rows;
+  int gather_copy, gather_rank;
+  int* gather_done;
   const void* a_peers[8];
   int scatter_world, scatter_rows, scatter_slot;
   void* d_peers[8];

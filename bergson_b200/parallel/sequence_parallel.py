@@ -5,9 +5,13 @@ tokens* (rank r holds rows ``[r T/W, (r + 1) T/W)``).  The two kinds of projecti
 onto two fused kernels over NVLink peer memory:
 
 * column-parallel (q/k/v, gate/up; weights split by output features): **all-gather -> GEMM**.
-  Every rank publishes its token shard once in a symmetric buffer; the GEMM's A-operand loads
-  fetch each 128-row block straight from the owning rank's buffer with plain (non-multicast)
-  TMA loads, so the gathered activation never exists in local memory.
+  Every rank publishes its token shard once in a symmetric buffer.  The first projection that
+  consumes it runs the gather inside its GEMM kernel: one copier warp per CTA pulls the other
+  ranks' row blocks over NVLink into a local buffer while the tensor cores work on the tiles of
+  the rank's own rows; tiles of remote rows start when the copiers' counters say their rows
+  have landed (bounded wait).  Every remote byte crosses NVLink once (peer reads are not cached
+  in the local L2, so reading A tiles straight from the peers would fetch them once per output
+  tile column); the other projections of the same input then read the local copy.
 * row-parallel (o_proj, down_proj; weights split by input features): **GEMM -> reduce-scatter**.
   The epilogue stores each output row block into the slot ``[source rank]`` of the row
   owner's buffer (peer stores); after a flag barrier the owner adds the W slots in rank order
@@ -90,6 +94,12 @@ class SeqParallel:
         self.barriers += 1
         native.peer_barrier(self._flags.ptrs, self.rank, self._epoch)
 
+    def gather_counters(self) -> Tensor:
+        """Arrival counters of the copier warps (zeroed by every launch that uses them)."""
+        if getattr(self, "_counters", None) is None:
+            self._counters = torch.zeros(8, dtype=torch.int32, device=self._heap.local.device)
+        return self._counters
+
     def _gather_offset(self, use: int) -> int:
         return (use & 1) * self._per
 
@@ -122,12 +132,34 @@ class SeqParallel:
 
 
 class Published:
-    """A token shard that sits in the peers' gather buffers (valid until two publishes later)."""
+    """A token shard that sits in the peers' gather buffers (valid until two publishes later),
+    and the local ``[T, width]`` buffer that the first consuming GEMM completes."""
 
     def __init__(self, sp: SeqParallel, shard: Tensor):
         self.sp = sp
         self.shard = shard
+        rows, width = shard.shape
+        self.full = torch.empty(sp.world * rows, width, dtype=shard.dtype, device=shard.device)
+        self.full[sp.rank * rows : (sp.rank + 1) * rows].copy_(shard.detach())
         self.ptrs = sp.publish(shard.detach())
+        self.gathered = False
+
+    def gemm(self, weight: Tensor, b_mn: bool, aux_p: Tensor | None):
+        """``gather(shards) @ op(weight)`` (+ the projection side output): the first call pulls
+        the remote rows inside its kernel, later calls find them in ``full``."""
+        from ..ops import native
+
+        sp = self.sp
+        if self.gathered or self.full.shape[0] // sp.world % 512:
+            if not self.gathered:  # blocks too small for the fused form: gather with a copy
+                dist.all_gather_into_tensor(self.full, self.shard.detach().contiguous(), group=sp.group)
+                self.gathered = True
+            return native.gemm(self.full, weight, False, b_mn, None, False, None, False, aux_p, cta_group=2, wide=True)
+        out = native.gemm(self.full, weight, False, b_mn, None, False, None, False, aux_p, cta_group=2, wide=True,
+                          a_peer_ptrs=self.ptrs, gather_done=sp.gather_counters(), gather_rank=sp.rank)
+        sp.fused_gemms += 1
+        self.gathered = True
+        return out
 
 
 def _tap_operands(module, tap, lead: tuple[int, int], like: Tensor):
@@ -165,10 +197,7 @@ class _GatherLinearFn(torch.autograd.Function):
 
         sp = pub.sp
         taps = _tap_operands(module, tap, lead, shard) if tap is not None else None
-        local = shard.detach().contiguous()  # shape, dtype and row stride of every rank's block
-        y, a_proj = native.gemm(local, weight, False, False, None, False, None, False,
-                                taps[0] if taps is not None else None, cta_group=2, a_peer_ptrs=pub.ptrs)
-        sp.fused_gemms += 1
+        y, a_proj = pub.gemm(weight, False, taps[0] if taps is not None else None)
         ctx.save_for_backward(weight, taps[1] if taps is not None else None, a_proj if taps is not None else None)
         ctx.sp, ctx.module, ctx.tap, ctx.lead, ctx.replicated = sp, module, tap if taps is not None else None, lead, replicated
         ctx.rows = shard.shape[0]
@@ -191,7 +220,7 @@ class _GatherLinearFn(torch.autograd.Function):
             dx, _ = native.gemm(mine, weight, False, True, None, False, None, False, None, cta_group=2, wide=True)
             return dx, None, None, None, None, None, None
         ptrs, local = sp.slot_targets()
-        _, g_proj = native.gemm(g, weight, False, True, None, False, None, False, p_out, cta_group=2,
+        _, g_proj = native.gemm(g, weight, False, True, None, False, None, False, p_out, cta_group=2, wide=True,
                                 d_peer_ptrs=ptrs, d_rows_per_rank=rows, d_slot=sp.rank)
         sp.fused_gemms += 1
         if ctx.tap is not None:
@@ -213,7 +242,7 @@ class _ScatterLinearFn(torch.autograd.Function):
         rows = x.shape[0] // sp.world
         ptrs, local = sp.slot_targets()
         _, a_proj = native.gemm(x, weight, False, False, None, False, None, False,
-                                taps[0] if taps is not None else None, cta_group=2,
+                                taps[0] if taps is not None else None, cta_group=2, wide=True,
                                 d_peer_ptrs=ptrs, d_rows_per_rank=rows, d_slot=sp.rank)
         sp.fused_gemms += 1
         y = sp.reduce_slots(local, rows, weight.shape[0], residual)
@@ -230,11 +259,7 @@ class _ScatterLinearFn(torch.autograd.Function):
         sp = ctx.sp
         if weight.requires_grad:
             raise NotImplementedError("sequence-parallel projections do not produce weight gradients")
-        g = g.contiguous()
-        ptrs = sp.publish(g)
-        dx, g_proj = native.gemm(g, weight, False, True, None, False, None, False, p_out, cta_group=2,
-                                 a_peer_ptrs=ptrs)
-        sp.fused_gemms += 1
+        dx, g_proj = Published(sp, g.contiguous()).gemm(weight, True, p_out)
         if ctx.tap is not None:
             ctx.tap.collect(ctx.module, a_proj, g_proj, torch.Size(ctx.lead))
         return dx, None, (g if ctx.has_residual else None), None, None, None, None
