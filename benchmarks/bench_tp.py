@@ -33,6 +33,8 @@ def main():
     ap.add_argument("--seq-len", type=int, default=2048)
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--kernel-table", default="", help="write rank 0's per-kernel device times of one step of each "
+                    "arm (torch profiler, taken after the timed region) to this file")
     args = ap.parse_args()
 
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
@@ -86,7 +88,21 @@ def main():
         clocks = sampler.stop()
         ms = torch.tensor([t0.elapsed_time(t1) / args.steps], device=dev, dtype=torch.float64)
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-        return {"arm": label, "ms_per_step": float(ms), "loss": float(loss), "clocks": clocks}
+        out = {"arm": label, "ms_per_step": float(ms), "loss": float(loss.detach()), "clocks": clocks}
+        if args.kernel_table:
+            from torch.profiler import ProfilerActivity, profile
+
+            with profile(activities=[ProfilerActivity.CUDA]) as prof:
+                step()
+                torch.cuda.synchronize()
+            if rank == 0:
+                with open(args.kernel_table, "a") as f:
+                    f.write(f"== {label} ==\n")
+                    f.write(prof.key_averages().table(sort_by="cuda_time_total", row_limit=25,
+                                                      max_name_column_width=90))
+                    f.write("\n")
+            dist.barrier()
+        return out
 
     results = []
     if sp is not None:

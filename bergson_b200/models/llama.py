@@ -56,6 +56,7 @@ class LlamaAttention(nn.Module):
         q = gather_linear(pub, self.q_proj, lead).view(B, S, self.num_heads, self.head_dim)
         k = gather_linear(pub, self.k_proj, lead).view(B, S, self.kv_heads, self.head_dim)
         v = gather_linear(pub, self.v_proj, lead).view(B, S, self.kv_heads, self.head_dim)
+        pub.release()
         q = ops.rotary(q, cos, sin, self.head_dim)
         k = ops.rotary(k, cos, sin, self.head_dim)
         o = ops.causal_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2))
@@ -84,6 +85,7 @@ class LlamaMLP(nn.Module):
 
         pub = Published(sp, h)
         a = ops.swiglu(gather_linear(pub, self.gate_proj, lead), gather_linear(pub, self.up_proj, lead))
+        pub.release()
         return scatter_linear(a, self.down_proj, sp, lead, residual)
 
 

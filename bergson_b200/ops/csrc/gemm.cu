@@ -89,8 +89,8 @@ static cudaError_t launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, con
 
 template <int FMT, bool OUT32>
 static cudaError_t launch_gemm_wide(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tp,
-                                    const CUtensorMap& td, const GemmParams& p, int grid, int* status,
-                                    cudaStream_t stream) {
+                                    const CUtensorMap& td, const GemmPeerMaps& peers, const GemmParams& p, int grid,
+                                    int* status, cudaStream_t stream) {
   auto kern = gemm_wide_kernel<FMT, OUT32>;
   static bool attr_set = false;  // one flag per instantiation
   if (!attr_set) {
@@ -110,7 +110,7 @@ static cudaError_t launch_gemm_wide(const CUtensorMap& ta, const CUtensorMap& tb
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, kern, ta, tb, tp, td, p, status);
+  return cudaLaunchKernelEx(&cfg, kern, ta, tb, tp, td, peers, p, status);
 }
 
 }  // namespace bgn
@@ -208,6 +208,27 @@ extern "C" int bgn_gemm(const BgnGemmArgs* a, int* status, cudaStream_t stream) 
   }
   p.a_blocked = a_blocked ? 1 : 0;
   p.b_blocked = b_blocked ? 1 : 0;
+  // Reduce-scatter through the wide kernel's staged epilogue: one output map per owner, each
+  // over that rank's [world slots x rows, N] slot region; TMA stores may target peer memory.
+  GemmPeerMaps scatter_maps;
+  bool scatter_tma = false;
+  if (scatter && cg == 2 && a->wide && !a->no_tma_store && a->scatter_rows % 32 == 0 &&
+      long(a->scatter_world) * a->scatter_rows == a->M && a->ldd % 8 == 0) {
+    EncodeTiledFn enc = gemm_encode_fn();
+    scatter_tma = enc != nullptr;
+    for (int o = 0; o < a->scatter_world && scatter_tma; ++o) {
+      cuuint64_t dims[2] = {cuuint64_t(a->N), cuuint64_t(a->scatter_world) * cuuint64_t(a->scatter_rows)};
+      cuuint64_t strides[1] = {cuuint64_t(a->ldd) * 2};
+      cuuint32_t box[2] = {64, 32};
+      cuuint32_t estr[2] = {1, 1};
+      const CUtensorMapDataType dt = a->fmt == 1 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+      scatter_tma = (reinterpret_cast<uintptr_t>(a->d_peers[o]) & 15) == 0 &&
+                    enc(&scatter_maps.a[o], dt, 2, a->d_peers[o], dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    }
+    if (scatter_tma) p.tma_store = 1;
+  }
 
   // The pair kernel reads gathered rows straight from the peers; the wide kernel has the
   // gather-with-copy form and the scatter epilogue.
@@ -233,11 +254,12 @@ extern "C" int bgn_gemm(const BgnGemmArgs* a, int* status, cudaStream_t stream) 
   cudaError_t e;
   const bool bf = a->fmt == 1;
   const GemmPeerMaps& pm = gather && !gather_copy ? gathered : no_peers;
+  const GemmPeerMaps& wide_pm = scatter_tma ? scatter_maps : no_peers;
   if (wide) {
-    e = a->out_f32 ? (bf ? launch_gemm_wide<1, true>(ta, tb, tp, td, p, grid, status, stream)
-                         : launch_gemm_wide<0, true>(ta, tb, tp, td, p, grid, status, stream))
-                   : (bf ? launch_gemm_wide<1, false>(ta, tb, tp, td, p, grid, status, stream)
-                         : launch_gemm_wide<0, false>(ta, tb, tp, td, p, grid, status, stream));
+    e = a->out_f32 ? (bf ? launch_gemm_wide<1, true>(ta, tb, tp, td, wide_pm, p, grid, status, stream)
+                         : launch_gemm_wide<0, true>(ta, tb, tp, td, wide_pm, p, grid, status, stream))
+                   : (bf ? launch_gemm_wide<1, false>(ta, tb, tp, td, wide_pm, p, grid, status, stream)
+                         : launch_gemm_wide<0, false>(ta, tb, tp, td, wide_pm, p, grid, status, stream));
   } else if (cg == 2) {
     e = a->out_f32 ? (bf ? launch_gemm<2, 1, true>(ta, tb, tp, td, pm, p, grid, status, stream)
                          : launch_gemm<2, 0, true>(ta, tb, tp, td, pm, p, grid, status, stream))

@@ -64,8 +64,8 @@ __device__ __forceinline__ void rotate_tile(GemmTile& tile, const GemmParams& p,
 template <int FMT, bool OUT32>
 __global__ void __launch_bounds__(kWideThreads, 1)
 gemm_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                 const __grid_constant__ CUtensorMap tmap_p, const __grid_constant__ CUtensorMap tmap_d, GemmParams p,
-                 int* status) {
+                 const __grid_constant__ CUtensorMap tmap_p, const __grid_constant__ CUtensorMap tmap_d,
+                 const __grid_constant__ GemmPeerMaps peers, GemmParams p, int* status) {
   constexpr int CG = 2;
   using InT = typename std::conditional<FMT == 1, __nv_bfloat16, __half>::type;
   constexpr int kStages = kWideStages;
@@ -351,12 +351,21 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           if (lane == 0) {
             mbar_arrive_cluster(empty_addr[rb]);
             if (row0 < p.M) {
+              // Reduce-scatter form: these 32 rows go to their owner's buffer (a peer mapping),
+              // into this rank's slot, through that rank's tensor map.
+              const CUtensorMap* md = &tmap_d;
+              int row_dst = row0;
+              if (p.d_scatter_rows > 0) {
+                const int owner = row0 / p.d_scatter_rows;
+                md = &peers.a[owner];
+                row_dst = p.d_slot * p.d_scatter_rows + (row0 - owner * p.d_scatter_rows);
+              }
               for (int b = 0; b < 2; ++b) {
                 const int c = half * 128 + b * 64;
                 if (c >= n_valid) break;
                 asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
-                                 reinterpret_cast<uint64_t>(&tmap_d)),
-                             "r"(smem_u32(stg) + uint32_t(b) * 4096u), "r"(col0 + c), "r"(row0)
+                                 reinterpret_cast<uint64_t>(md)),
+                             "r"(smem_u32(stg) + uint32_t(b) * 4096u), "r"(col0 + c), "r"(row_dst)
                              : "memory");
               }
             }

@@ -41,6 +41,7 @@ from torch import Tensor
 from .peer import PeerHeap, symmetric_memory_available
 
 ROW_BLOCK = 128  # rows that one CTA loads; a block must not straddle two ranks' shards
+MAX_CONSUMERS = 3  # projections sharing one published input (q/k/v): their input gradients share a reduce-scatter
 
 
 class SeqParallel:
@@ -80,7 +81,7 @@ class SeqParallel:
             self._flags = PeerHeap(8, torch.int32, self.group)
             self._flags.local.zero_()
         per = rows * width
-        self._heap = PeerHeap((2 + 2 * self.world) * per, dtype, self.group)
+        self._heap = PeerHeap((2 + 2 * MAX_CONSUMERS * self.world) * per, dtype, self.group)
         self._shape = (rows, width, dtype)
         self._per = per
         self._heap.barrier()  # zeroed flags and the new mappings are in place everywhere
@@ -104,7 +105,7 @@ class SeqParallel:
         return (use & 1) * self._per
 
     def _slot_offset(self, use: int) -> int:
-        return (2 + (use & 1) * self.world) * self._per
+        return (2 + (use & 1) * MAX_CONSUMERS * self.world) * self._per
 
     def publish(self, shard: Tensor) -> list[int]:
         """Copy this rank's ``[rows, width]`` shard into the current gather buffer and pass the
@@ -120,14 +121,16 @@ class SeqParallel:
         """Addresses of the current slot region on every rank, and this rank's own region."""
         off = self._slot_offset(self._slot_use)
         self._slot_use += 1
-        local = self._heap.local[off : off + self.world * self._per]
+        local = self._heap.local[off : off + MAX_CONSUMERS * self.world * self._per]
         return [self._heap.ptr(r, off) for r in range(self.world)], local
 
-    def reduce_slots(self, local: Tensor, rows: int, width: int, residual: Tensor | None) -> Tensor:
+    def reduce_slots(self, local: Tensor, rows: int, width: int, residual: Tensor | None, groups: int = 1) -> Tensor:
+        """Barrier, then the sum of ``groups * world`` slots (+ residual) in a fixed order."""
         from ..ops import native
 
         self.barrier()
-        slots = local[: self.world * rows * width].view(self.world, rows, width)
+        n = groups * self.world
+        slots = local[: n * rows * width].view(n, rows, width)
         return native.slot_reduce(slots, residual.contiguous() if residual is not None else None)
 
 
@@ -143,6 +146,30 @@ class Published:
         self.full[sp.rank * rows : (sp.rank + 1) * rows].copy_(shard.detach())
         self.ptrs = sp.publish(shard.detach())
         self.gathered = False
+        self.consumers = 0        # projections whose input gradient will come back
+        self._pushed = 0          # of those, how many have pushed their partial gradient so far
+        self._slots = None
+
+    def release(self) -> None:
+        """Drop the gathered copy once every forward consumer has run."""
+        self.full = None
+
+    def push_target(self, rows: int, width: int) -> tuple[list[int], int]:
+        """Slot addresses for the next consumer's partial input gradient, and its group index."""
+        sp = self.sp
+        if self._slots is None:
+            self._slots = sp.slot_targets()
+        idx = self._pushed
+        self._pushed += 1
+        skip = idx * sp.world * rows * width * sp._heap.itemsize
+        return [p + skip for p in self._slots[0]], idx
+
+    def finish_if_last(self, rows: int, width: int):
+        """The reduce-scattered sum of all consumers' input gradients once the last one has
+        pushed (one barrier and one reduction for the whole group), else None."""
+        if self._pushed < self.consumers:
+            return None
+        return self.sp.reduce_slots(self._slots[1], rows, width, None, groups=self._pushed)
 
     def gemm(self, weight: Tensor, b_mn: bool, aux_p: Tensor | None):
         """``gather(shards) @ op(weight)`` (+ the projection side output): the first call pulls
@@ -198,6 +225,7 @@ class _GatherLinearFn(torch.autograd.Function):
         sp = pub.sp
         taps = _tap_operands(module, tap, lead, shard) if tap is not None else None
         y, a_proj = pub.gemm(weight, False, taps[0] if taps is not None else None)
+        ctx.pub = pub
         ctx.save_for_backward(weight, taps[1] if taps is not None else None, a_proj if taps is not None else None)
         ctx.sp, ctx.module, ctx.tap, ctx.lead, ctx.replicated = sp, module, tap if taps is not None else None, lead, replicated
         ctx.rows = shard.shape[0]
@@ -219,14 +247,15 @@ class _GatherLinearFn(torch.autograd.Function):
             mine = g[sp.rank * rows : (sp.rank + 1) * rows]
             dx, _ = native.gemm(mine, weight, False, True, None, False, None, False, None, cta_group=2, wide=True)
             return dx, None, None, None, None, None, None
-        ptrs, local = sp.slot_targets()
+        ptrs, _ = ctx.pub.push_target(rows, width)
         _, g_proj = native.gemm(g, weight, False, True, None, False, None, False, p_out, cta_group=2, wide=True,
                                 d_peer_ptrs=ptrs, d_rows_per_rank=rows, d_slot=sp.rank)
         sp.fused_gemms += 1
         if ctx.tap is not None:
             ctx.tap.collect(ctx.module, a_proj, g_proj, torch.Size(ctx.lead))
-        dx = sp.reduce_slots(local, rows, width, None)
-        return dx, None, None, None, None, None, None
+        # The projections that share this input share one reduce-scatter: the last one to push
+        # returns the summed gradient, the others contribute nothing of their own.
+        return ctx.pub.finish_if_last(rows, width), None, None, None, None, None, None
 
 
 class _ScatterLinearFn(torch.autograd.Function):
@@ -272,6 +301,10 @@ def gather_linear(pub: Published, module, lead: tuple[int, int], replicated: boo
         tap = None
     if tap is None:
         _check_hooks(module, None)
+    if torch.is_grad_enabled() and pub.shard.requires_grad and not replicated:
+        if pub.consumers >= MAX_CONSUMERS:
+            raise RuntimeError(f"at most {MAX_CONSUMERS} projections may share one published input")
+        pub.consumers += 1
     return _GatherLinearFn.apply(pub.shard, module.weight, pub, module, tap, lead, replicated)
 
 
