@@ -1,75 +1,69 @@
-"""MAGIC step times on one GPU: an ordinary (untraced, in-place) training step and a
-meta-step (the step replayed with a graph plus the vector-Jacobian product that carries the
-parameter / optimizer-state cotangents to the previous state and to the data weights).
+"""MAGIC step times on one GPU for either build, with an optional per-operator table.
 
-    python benchmarks/bench_magic.py [--seqs 8] [--seq-len 512] [--layers 12]
+    python benchmarks/bench_magic.py [--impl ours|reference] [--kernel-table FILE]
 
-Model: random-init GPT-2 (d 768, 12 heads, vocab 50257), bf16 parameters, fp32 AdamW state.
-Prints one JSON line.  The reference's trainer needs the `torchopt` package, which is not
-available offline, so there is no reference arm.
+Runs the ``magic`` metric of ``benchmarks/extra_metrics.py`` (GPT-2 12L d768, 64 x 512 tokens,
+bf16, AdamW: the plain in-place training step and the meta-step = traced step + VJP) and prints
+its JSON.  ``--kernel-table`` additionally profiles one meta-step with the torch profiler
+(after the timed runs) and writes the per-operator device times to FILE.  The reference arm
+needs the package under ``baseline/_ref`` and the stand-ins under ``baseline/shims``.
 """
 
 from __future__ import annotations
 
 import argparse
 import json
+import sys
+from pathlib import Path
 
-from common import cuda_timed
-
-import torch
+ROOT = Path(__file__).resolve().parents[1]
+sys.path.insert(0, str(ROOT))
 
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--seqs", type=int, default=8)
-    ap.add_argument("--seq-len", type=int, default=512)
-    ap.add_argument("--layers", type=int, default=12)
-    ap.add_argument("--dtype", choices=["bf16", "fp32"], default="bf16")
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--kernel-table", default="")
     args = ap.parse_args()
+    if args.impl == "reference":
+        sys.path[:0] = [str(ROOT / "baseline" / "shims"), str(ROOT / "baseline" / "_ref")]
 
-    from bergson_b200.data import zipf_token_ids
-    from bergson_b200.magic import optim
-    from bergson_b200.magic.data_stream import DataStream
-    from bergson_b200.magic.trainer import BackwardState, Trainer
-    from bergson_b200.models import build_model
-    from bergson_b200.models.registry import PRESETS, args_from_dict
-    from datasets import Dataset
+    import torch
 
-    dev = torch.device("cuda:0")
-    dtype = torch.bfloat16 if args.dtype == "bf16" else torch.float32
-    model = build_model(args_from_dict(dict(PRESETS["gpt2"], num_hidden_layers=args.layers)), dtype=dtype, device=dev,
-                        init_on_device=True)
-    model.requires_grad_(True)
-    model.eval()
-    n = args.seqs * 4
-    ids = zipf_token_ids(n, args.seq_len, 50257, seed=0)
-    data = DataStream(Dataset.from_dict({"input_ids": ids, "length": [args.seq_len] * n}), args.seqs, device=dev)
-    trainer, state = Trainer.initialize(model, optim.adamw(lambda s: 3e-4, betas=(0.95, 0.975), eps_root=1e-8,
-                                                           weight_decay=0.01))
-    holder = {"s": state}
+    from benchmarks import extra_metrics as em
 
-    def plain():
-        holder["s"] = trainer.step(holder["s"], data[0], inplace=True)
+    timed = em._magic_run
 
-    t_plain = cuda_timed(plain, warmup=2, iters=5)
+    def run_and_profile(trainer, state, data, dev, world):
+        out = timed(trainer, state, data, dev, world)
+        if args.kernel_table:
+            from torch.profiler import ProfilerActivity, profile
 
-    def meta():
-        st = holder["s"]
-        st.detach_()
-        st.requires_grad = True
-        data.requires_grad = True
-        flat_i = st.differentiable_tensors()
-        nxt = trainer.step(st, data[1], trace=True)
-        flat_f = nxt.differentiable_tensors()
-        cot = [torch.ones_like(t) * 1e-3 for t in flat_f]
-        torch.autograd.grad(flat_f, flat_i + [data.weights], grad_outputs=cot, allow_unused=True)
+            st = trainer.step(state, data[0], inplace=True)
 
-    t_meta = cuda_timed(meta, warmup=1, iters=3)
-    tokens = args.seqs * args.seq_len
-    print(json.dumps({"model": f"gpt2-{args.layers}L-d768", "dtype": args.dtype, "tokens_per_step": tokens,
-                      "train_step_s": t_plain, "meta_step_s": t_meta, "meta_over_train": t_meta / t_plain,
-                      "train_tokens_per_s": tokens / t_plain, "meta_tokens_per_s": tokens / t_meta,
-                      "peak_mem_gb": torch.cuda.max_memory_allocated() / 1e9}))
+            def meta():
+                st.detach_()
+                st.requires_grad = True
+                data.requires_grad = True
+                before = st.differentiable_tensors()
+                after = trainer.step(st, data[1], trace=True).differentiable_tensors()
+                cot = [torch.full_like(t, 1e-3) for t in after]
+                torch.autograd.grad(after, before + [data.weights], grad_outputs=cot, allow_unused=True)
+                st.requires_grad = False
+                data.requires_grad = False
+
+            meta()
+            torch.cuda.synchronize()
+            with profile(activities=[ProfilerActivity.CPU, ProfilerActivity.CUDA]) as prof:
+                meta()
+                torch.cuda.synchronize()
+            with open(args.kernel_table, "w") as f:
+                f.write(prof.key_averages().table(sort_by="cuda_time_total", row_limit=45, max_name_column_width=80))
+        return out
+
+    em._magic_run = run_and_profile
+    fn = em.magic_ours if args.impl == "ours" else em.magic_reference
+    print(json.dumps(dict(fn(0, 0, 1), impl=args.impl)))
 
 
 if __name__ == "__main__":
