@@ -157,3 +157,24 @@ def test_traced_adamw_step_and_its_vjp_match_autograd(native, dtype):
     for g, w in zip(got, want):
         scale = w.abs().max().item() + 1e-12
         assert (g.double() - w).abs().max().item() <= (1e-4 if dtype == torch.float32 else 3e-2) * scale
+
+
+@pytest.mark.parametrize("shape", [(256, 96), (64, 320)])
+def test_newton_schulz_on_the_gemm_kernel_matches_torch(native, shape):
+    from bergson_b200.magic import optim
+
+    torch.manual_seed(0)
+    g = torch.randn(shape, device="cuda").to(torch.bfloat16).requires_grad_(True)
+    out = optim.zeropower_via_newtonschulz(g)
+    assert out.shape == g.shape and type(out.grad_fn).__name__ != "AddmmBackward0"
+    g64 = g.detach().double().requires_grad_(True)
+    ref = optim.zeropower_via_newtonschulz(g64)  # CPU-style path in fp64 (dtype not 16-bit)
+    assert (out.double() - ref).abs().max() <= 6e-2 * ref.abs().max()
+    # Singular values are pushed towards 1 (the iteration's purpose).
+    sv = torch.linalg.svdvals(out.float())
+    assert sv.min() > 0.3 and sv.max() < 1.6
+    # First derivative through the kernel path.
+    probe = torch.randn(shape, device="cuda")
+    (gg,) = torch.autograd.grad((out.float() * probe).sum(), g)
+    (gr,) = torch.autograd.grad((ref * probe.double()).sum(), g64)
+    assert torch.nn.functional.cosine_similarity(gg.double().flatten(), gr.flatten(), dim=0) > 0.98
