@@ -69,3 +69,47 @@ def test_ekfac_pipeline_on_gpu_tracks_the_cpu_run(tmp_path):
             assert rel < (0.08 if sub == "eigenvalue_correction_sharded" else 0.04), (sub, k, rel)
     s_gpu, s_cpu = load_scores(tmp_path / "gpu" / "scores")[:], load_scores(tmp_path / "cpu" / "scores")[:]
     assert np.corrcoef(s_gpu.ravel().astype(np.float64), s_cpu.ravel().astype(np.float64))[0, 1] > 0.98
+
+
+@pytest.mark.parametrize("drop_scale", [1.0, 30.0])
+def test_gram_with_dropped_rows_at_the_fused_path_boundary(drop_scale):
+    """The fused covariance path runs the SYRK over all rows and subtracts the Gram of the
+    skipped ones; it is taken while at most 1/8 of the rows are skipped.  Exactly at that
+    boundary, and with skipped rows far larger than the kept ones (the case where the
+    subtraction cancels most of the sum), the result must still match the masked oracle."""
+    from types import SimpleNamespace
+
+    from bergson_b200.hessians.kfac import _FactorCollector
+
+    torch.manual_seed(0)
+    n, s, d = 8, 64, 256
+    x = torch.randn(n, s, d, device="cuda")
+    mask = torch.ones(n, s, dtype=torch.bool, device="cuda")
+    mask[:, -8:] = False  # 8 of 64 positions per sequence: exactly one eighth
+    x[~mask] *= drop_scale
+    x = x.to(torch.bfloat16)
+    flat = mask.reshape(-1)
+    stub = SimpleNamespace(_keep_idx=flat.nonzero(as_tuple=True)[0], _drop_idx=(~flat).nonzero(as_tuple=True)[0],
+                           _peer=None, _final_batch=False, _flushed=set(), _flushed_in_gemm=set(),
+                           _current_collection_mask=mask, dtype=torch.bfloat16)
+    stub._masked = lambda t: _FactorCollector._masked(stub, t)
+    acc = torch.zeros(d, d, device="cuda")
+    _FactorCollector._gram_into(stub, acc, x)
+    assert stub._drop_idx.numel() * 8 == n * s  # the boundary case of the fused path
+    kept = x.reshape(-1, d)[flat].double()
+    want = kept.T @ kept
+    err = (acc.double() - want).abs().max() / want.abs().max()
+    # fp32 accumulation of sums that are drop_scale^2 / 7 times larger than the result
+    assert err < 1e-5 * max(1.0, drop_scale**2), float(err)
+    # One more skipped row takes the compaction path (no subtraction): same oracle.
+    mask2 = mask.clone()
+    mask2[0, 0] = False
+    flat2 = mask2.reshape(-1)
+    stub2 = SimpleNamespace(**{**stub.__dict__, "_keep_idx": flat2.nonzero(as_tuple=True)[0],
+                               "_drop_idx": (~flat2).nonzero(as_tuple=True)[0], "_current_collection_mask": mask2})
+    stub2._masked = lambda t: _FactorCollector._masked(stub2, t)
+    acc2 = torch.zeros(d, d, device="cuda")
+    _FactorCollector._gram_into(stub2, acc2, x)
+    kept2 = x.reshape(-1, d)[flat2].double()
+    want2 = kept2.T @ kept2
+    assert (acc2.double() - want2).abs().max() / want2.abs().max() < 1e-5 * max(1.0, drop_scale**2)
