@@ -226,6 +226,60 @@ def bench_adamw(small: bool, iters: int):
     return dict(kernel="adamw_step", shape=[n], ms=ms, torch_ms=_time(opt.step, iters), bytes=n * (6 * 4 + 2 + 2), flops=0)
 
 
+def _param_list(small: bool, dtype):
+    """A parameter list shaped like a transformer's: a few large matrices, many small vectors."""
+    big = 8 if small else 24
+    shapes = [(4096, 4096)] * big + [(4096,)] * (4 * big) + [(32768, 1024)]
+    return [torch.randn(s, device="cuda").to(dtype) for s in shapes]
+
+
+def bench_adamw_multi(small: bool, iters: int):
+    """Multi-tensor AdamW (in-place step) and the traced step + VJP pair of MAGIC, one launch each,
+    against torch's fused multi-tensor AdamW on the same list."""
+    from bergson_b200.ops import native
+
+    ps = _param_list(small, torch.bfloat16)
+    gs = [torch.randn_like(p) for p in ps]
+    ms, vs = [torch.zeros(p.shape, device="cuda") for p in ps], [torch.zeros(p.shape, device="cuda") for p in ps]
+    n = sum(p.numel() for p in ps)
+    hp = (3e-4, 0.9, 0.999, 1e-8, 1e-8, 0.01)
+    coef = torch.ones(1, device="cuda")
+    t_step = _time(lambda: native.adamw_multi(ps, ms, vs, gs, *hp, 1, 1.0, coef), iters)
+    ref_p = [torch.nn.Parameter(p.float()) for p in ps]
+    opt = torch.optim.AdamW(ref_p, lr=3e-4, fused=True)
+    for p, g in zip(ref_p, gs):
+        p.grad = g.float()
+    t_torch = _time(opt.step, iters)
+    out = [dict(kernel="adamw_multi (bf16 params, fp32 moments, in place)", shape=[len(ps), n], ms=t_step, torch_ms=t_torch,
+                bytes=n * (2 + 2 + 2 + 4 * 4), flops=0)]
+    t_fwd = _time(lambda: native.adamw_traced_fwd(ps, gs, ms, vs, *hp, 1), iters)
+    cps, cms, cvs = [torch.randn_like(p) for p in ps], [torch.randn_like(m) for m in ms], [None] * len(ps)
+    t_bwd = _time(lambda: native.adamw_traced_bwd(gs, ms, vs, cps, cms, cvs, *hp, 1), iters)
+    out.append(dict(kernel="adamw_traced_fwd (out of place)", shape=[len(ps), n], ms=t_fwd, torch_ms=t_torch,
+                    bytes=n * (2 + 2 + 4 + 4 + 2 + 4 + 4), flops=0))
+    out.append(dict(kernel="adamw_traced_bwd (VJP)", shape=[len(ps), n], ms=t_bwd, torch_ms=t_torch,
+                    bytes=n * (2 + 4 + 4 + 2 + 4 + 2 + 2 + 4 + 4), flops=0))
+    acc = torch.zeros(2, device="cuda")
+    t_norm = _time(lambda: native.multi_sumsq(gs, acc, False, 1.0), iters)
+    t_norm_torch = _time(lambda: torch.nn.utils.get_total_norm(gs), iters)
+    out.append(dict(kernel="multi_sumsq (clipping coefficient)", shape=[len(ps), n], ms=t_norm, torch_ms=t_norm_torch,
+                    bytes=n * 2, flops=0))
+    return out
+
+
+def bench_slot_reduce(small: bool, iters: int):
+    """Owner-side sum of reduce-scatter slots (+ residual), 8 slots of [2048, 8192] bf16."""
+    from bergson_b200.ops import native
+
+    w, rows, d = (2, 8192, 4096) if small else (8, 2048, 8192)
+    slots = torch.randn(w, rows, d, device="cuda").to(torch.bfloat16)
+    res = torch.randn(rows, d, device="cuda").to(torch.bfloat16)
+    out = torch.empty_like(res)
+    ms = _time(lambda: native.slot_reduce(slots, res, out), iters)
+    ref = _time(lambda: torch.add(res.float(), slots.float().sum(0)).to(torch.bfloat16), iters)
+    return dict(kernel="slot_reduce", shape=[w, rows, d], ms=ms, torch_ms=ref, bytes=(w + 2) * rows * d * 2, flops=0)
+
+
 def bench_contract(small: bool, iters: int):
     """Per-example 16 x S x 16 contraction of the projected operands (deterministic order)."""
     from bergson_b200.ops import native
@@ -283,7 +337,8 @@ def bench_gemm_case(small: bool, iters: int):
 BENCHES = {"proj_right": bench_proj_right, "proj_left_outer": bench_proj_left_outer, "cov_syrk": bench_cov_syrk,
            "tn_gemm": bench_tn_gemm, "ce_fwd": bench_ce, "rmsnorm_fwd": bench_rmsnorm, "linear_gemm": bench_linear_gemm, "ce_bwd": bench_ce_bwd,
            "rmsnorm_bwd": bench_rmsnorm_bwd, "adamw": bench_adamw, "proj_contract": bench_contract, "rotary": bench_rotary,
-           "swiglu_bwd": bench_swiglu, "gemm_case": bench_gemm_case}
+           "swiglu_bwd": bench_swiglu, "gemm_case": bench_gemm_case, "adamw_multi": bench_adamw_multi,
+           "slot_reduce": bench_slot_reduce}
 
 
 def main():

@@ -59,3 +59,95 @@ def simple_fsdp(params: dict[str, Tensor]) -> tuple[dict[str, Tensor], dict[str,
 
 def gather_params(shards: dict[str, Tensor], shapes: dict[str, torch.Size]) -> dict[str, Tensor]:
     return {k: gather_param(s, shapes[k]) for k, s in shards.items()}
+
+
+# --------------------------------------------------------------------------- #
+# Per-module gathering
+# --------------------------------------------------------------------------- #
+
+
+class _Regather:
+    """What autograd keeps instead of a gathered parameter: enough to gather it again."""
+
+    __slots__ = ("key",)
+
+    def __init__(self, key: str):
+        self.key = key
+
+
+class LazyGather:
+    """Run a module whose trainable parameters live as row shards, gathering each
+    parameter only around the forward of the module that owns it.
+
+    * A forward pre-hook on every parameter-owning module gathers that module's parameters
+      (differentiable all-gather), the forward hook drops them again: at any moment only the
+      running module's full parameters exist, instead of the whole model's.
+    * Operations save their weight for the backward pass; ``saved_tensors_hooks`` replaces
+      each saved gathered parameter by a marker, and unpacking gathers it again from the
+      shard, *with* autograd history, so the backward of the backward still reaches the
+      shard (what a metagradient needs).  Peak memory is shards + one module's parameters +
+      activations, at the price of a second all-gather per parameter in the backward pass.
+
+    The reference gets the same effect from DTensor parametrisations
+    (``bergson/magic/fsdp.py``); its full parameters are likewise gathered per module call.
+    """
+
+    def __init__(self, model: torch.nn.Module, shards: dict[str, Tensor], shapes: dict[str, torch.Size]):
+        self.model, self.shards, self.shapes = model, shards, shapes
+        self.gathers = 0  # forward gathers + re-gathers (read by the tests)
+        self.packed = 0   # saved gathered parameters that were replaced by a marker
+        key_of = {}
+        for name, p in model.named_parameters(remove_duplicate=False):
+            key_of.setdefault(id(p), name)
+        # (module, attribute, state key) for every trainable parameter slot, tied slots included
+        self.slots: dict[torch.nn.Module, list[tuple[str, str]]] = {}
+        for mod in model.modules():
+            for leaf, p in mod._parameters.items():
+                if p is not None and key_of.get(id(p)) in shards:
+                    self.slots.setdefault(mod, []).append((leaf, key_of[id(p)]))
+        self._live: dict[int, str] = {}
+        self._handles: list = []
+        self._originals: dict[tuple[int, str], torch.nn.Parameter] = {}
+
+    def _gather(self, key: str) -> Tensor:
+        self.gathers += 1
+        return gather_param(self.shards[key], self.shapes[key])
+
+    def _pre(self, mod, args):
+        for leaf, key in self.slots[mod]:
+            full = self._gather(key)
+            self._live[id(full)] = key
+            self._originals[(id(mod), leaf)] = mod._parameters.pop(leaf)
+            setattr(mod, leaf, full)  # plain attribute: keeps the autograd history of the gather
+
+    def _post(self, mod, args, output):
+        for leaf, _ in self.slots[mod]:
+            full = mod.__dict__.pop(leaf, None)
+            if full is not None:
+                self._live.pop(id(full), None)
+            mod._parameters[leaf] = self._originals.pop((id(mod), leaf))
+
+    def _pack(self, t: Tensor):
+        key = self._live.get(id(t))
+        if key is None:
+            return t
+        self.packed += 1
+        return _Regather(key)
+
+    def _unpack(self, obj):
+        return self._gather(obj.key) if isinstance(obj, _Regather) else obj
+
+    def __enter__(self):
+        for mod in self.slots:
+            self._handles.append(mod.register_forward_pre_hook(self._pre))
+            self._handles.append(mod.register_forward_hook(self._post, always_call=True))
+        self._saved = torch.autograd.graph.saved_tensors_hooks(self._pack, self._unpack)
+        self._saved.__enter__()
+        return self
+
+    def __exit__(self, *exc):
+        self._saved.__exit__(*exc)
+        for h in self._handles:
+            h.remove()
+        self._handles.clear()
+        return False

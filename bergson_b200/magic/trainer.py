@@ -42,7 +42,7 @@ from ..utils.worker_utils import setup_model_and_peft
 from . import optim
 from .collectives import all_reduce_sum
 from .data_stream import DataStream
-from .fsdp import gather_params, simple_fsdp
+from .fsdp import LazyGather, gather_params, simple_fsdp
 from .grad_accum import (
     accumulate_grads,
     maybe_get_cuda_rng_state,
@@ -250,11 +250,20 @@ class Trainer:
         self.model = model
         self.optimizer = optimizer
         self.param_shapes = param_shapes  # full shapes when parameters are sharded
+        self.lazy_gather = os.environ.get("BERGSON_B200_FSDP_GATHER", "module") != "all"
+        self.gather_count = 0
         self._last_loss = 0.0
 
     # -- forward --------------------------------------------------------------------------
 
     def call_model(self, params: dict, inputs: dict, buffers: dict | None = None):
+        if self.param_shapes is not None and self.lazy_gather:
+            # Sharded parameters are gathered around each owning module's forward (and again when
+            # the backward pass needs them), never all at once.
+            with LazyGather(self.model, params, self.param_shapes) as lazy:
+                out = functional_call(self.model, dict(buffers or {}), args=(), kwargs=inputs)
+            self.gather_count += lazy.gathers
+            return out
         full = gather_params(params, self.param_shapes) if self.param_shapes is not None else params
         return functional_call(self.model, {**full, **(buffers or {})}, args=(), kwargs=inputs)
 

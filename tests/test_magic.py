@@ -168,3 +168,42 @@ def test_pad_dataset_to_batch_size():
     ds = tiny_dataset(n=5, length=6, ragged=False)
     out, num_docs, pad, wpad = pad_dataset_to_batch_size(ds, 4, 5, "train", 1)
     assert len(out) == 8 and pad == 3 and wpad == 3 and num_docs == 8
+
+
+def test_lazy_gather_matches_functional_call_to_second_order():
+    """Per-module gathering with re-gathering in the backward pass gives the same loss, the
+    same gradients and the same gradient-of-gradient as handing the model all parameters."""
+    from torch.func import functional_call
+
+    from bergson_b200.magic.fsdp import LazyGather
+
+    torch.manual_seed(0)
+    model = tiny_model("gpt2", dtype=torch.float64, num_hidden_layers=2)
+    model.eval()
+    params = {k: v.detach().clone().requires_grad_(True) for k, v in model.named_parameters()}
+    shapes = {k: v.shape for k, v in params.items()}
+    x = torch.randint(0, 128, (3, 9))
+
+    def second_order(loss, ps):
+        grads = torch.autograd.grad(loss, ps, create_graph=True)
+        inner = sum((g * g).sum() for g in grads)
+        return grads, torch.autograd.grad(inner, ps, allow_unused=True)
+
+    plist = list(params.values())
+    want_loss = functional_call(model, params, args=(), kwargs={"input_ids": x, "labels": x}).loss
+    want_g, want_gg = second_order(want_loss, plist)
+    with LazyGather(model, params, shapes) as lazy:
+        got_loss = model(input_ids=x, labels=x).loss
+    assert lazy.packed > 0 and lazy.gathers >= len(shapes)  # tied embeddings are gathered per use
+    got_g, got_gg = second_order(got_loss, plist)
+    assert lazy.gathers > len(shapes) + 1  # the backward pass gathered again
+    torch.testing.assert_close(got_loss, want_loss)
+    for a, b in zip(got_g, want_g):
+        torch.testing.assert_close(a, b)
+    for a, b in zip(got_gg, want_gg):
+        if b is None:
+            assert a is None
+        else:
+            torch.testing.assert_close(a, b, rtol=1e-6, atol=1e-9)
+    # The module's own parameters are back in place.
+    assert all(isinstance(p, torch.nn.Parameter) for p in model.parameters())

@@ -320,3 +320,31 @@ def test_sequence_parallel_projections_two_gpus():
         assert status == 0
         assert err < 3e-2, (rank, err)
         assert barriers == 3 * 4 and gemms == 3 * 4  # publish, reduce, publish (bwd), reduce (bwd) per round
+
+
+def test_magic_fsdp_matches_ddp_two_gpus(tmp_path):
+    """`magic` on 2 GPUs with sharded parameters (gathered per module over NCCL, gathered again
+    in the backward and the double-backward pass) against plain data parallelism."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    import numpy as np
+
+    from bergson_b200.data import load_scores
+
+    root = Path(__file__).resolve().parents[1]
+    opts = ["--model", "native:gpt2-tiny?vocab_size=256", "--precision", "fp32",
+            "--data.dataset", "synthetic:zipf?n=16&len=16&vocab=256&min_len=16",
+            "--query.dataset", "synthetic:zipf?n=4&len=16&vocab=256&seed=1&min_len=16", "--batch_size", "4",
+            "--query_method", "mean", "--lr", "1e-3", "--max_grad_norm", "1.0", "--nproc_per_node", "2"]
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    for name, fsdp in (("ddp", "false"), ("fsdp", "true")):
+        out = subprocess.run([sys.executable, "-m", "bergson_b200", "magic", str(tmp_path / name), "--fsdp", fsdp] + opts,
+                             cwd=root, env=env, capture_output=True, text=True, timeout=900)
+        assert out.returncode == 0, out.stderr[-2000:]
+    a, b = load_scores(tmp_path / "ddp" / "scores")[:], load_scores(tmp_path / "fsdp" / "scores")[:]
+    assert np.abs(a).max() > 0
+    np.testing.assert_allclose(a, b, rtol=2e-3, atol=2e-4 * np.abs(a).max())
