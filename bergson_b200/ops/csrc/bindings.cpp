@@ -413,15 +413,17 @@ void multi_sumsq(std::vector<at::Tensor> xs, at::Tensor out, bool accumulate, do
   const size_t n = xs.size();
   TORCH_CHECK(n > 0 && out.is_cuda() && out.scalar_type() == at::kFloat && out.numel() >= 2 && out.is_contiguous());
   std::vector<std::array<int64_t, 6>> rows(n);
+  int64_t max_n = 0;
   for (size_t i = 0; i < n; ++i) {
     CHECK_CUDA_CONTIG(xs[i]);
     TORCH_CHECK(xs[i].scalar_type() == xs[0].scalar_type() && xs[i].device() == out.device());
     rows[i] = {0, 0, 0, (int64_t)xs[i].data_ptr(), xs[i].numel(), 0};
+    max_n = std::max<int64_t>(max_n, xs[i].numel());
   }
   c10::cuda::CUDAGuard guard(out.device());
   auto table = upload_table(rows, out.device());
   auto partials = at::empty({(int64_t)n * bgn_multi_sumsq_blocks()}, out.options());
-  check(bgn_multi_sumsq(table.data_ptr(), (int)n, partials.data_ptr<float>(), out.data_ptr<float>(), accumulate,
+  check(bgn_multi_sumsq(table.data_ptr(), (int)n, max_n, partials.data_ptr<float>(), out.data_ptr<float>(), accumulate,
                         (float)max_norm, type_code(xs[0]), stream()), "multi_sumsq");
 }
 

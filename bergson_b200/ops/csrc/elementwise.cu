@@ -558,6 +558,33 @@ struct AdamTraceEntry {
 };
 
 template <typename T>
+struct alignas(4 * sizeof(T)) Pack4 {
+  T v[4];
+};
+
+// True when the element count and every non-null pointer allow 4-element packets.
+__device__ __forceinline__ bool packs_ok(const AdamTraceEntry& e, int n_ptr, size_t t_bytes, unsigned t_mask) {
+  if (e.n & 3) return false;
+  for (int i = 0; i < n_ptr; ++i) {
+    const uintptr_t a = reinterpret_cast<uintptr_t>(e.w[i]);
+    const size_t need = ((t_mask >> i) & 1u) ? 4 * t_bytes : 16;  // T-typed or fp32 slot
+    if (a & (need - 1)) return false;
+  }
+  return true;
+}
+
+template <typename T>
+__device__ __forceinline__ void adamw_fwd_one(T p, T g, float m, float v, T& po, float& mo, float& vo, float lr, float b1,
+                                              float b2, float eps, float eps_root, float wd, float bc1, float bc2) {
+  const float gi = to_float<T>(g);
+  mo = b1 * m + (1.f - b1) * gi;
+  vo = b2 * v + (1.f - b2) * gi * gi;
+  const float pf = to_float<T>(p);
+  const float upd = (mo / bc1) / (sqrtf(vo / bc2 + eps_root) + eps) + wd * pf;
+  po = from_float<T>(pf - lr * upd);
+}
+
+template <typename T>
 __global__ void adamw_traced_fwd_kernel(const AdamTraceEntry* __restrict__ table, float lr, float b1, float b2,
                                         float eps, float eps_root, float wd, float bc1, float bc2) {
   const AdamTraceEntry e = table[blockIdx.y];
@@ -568,16 +595,46 @@ __global__ void adamw_traced_fwd_kernel(const AdamTraceEntry* __restrict__ table
   T* po = static_cast<T*>(e.w[4]);
   float* mo = static_cast<float*>(e.w[5]);
   float* vo = static_cast<float*>(e.w[6]);
-  for (long i = blockIdx.x * long(blockDim.x) + threadIdx.x; i < e.n; i += long(gridDim.x) * blockDim.x) {
-    const float gi = to_float<T>(g[i]);
-    const float mi = b1 * m[i] + (1.f - b1) * gi;
-    const float vi = b2 * v[i] + (1.f - b2) * gi * gi;
-    const float pf = to_float<T>(p[i]);
-    const float upd = (mi / bc1) / (sqrtf(vi / bc2 + eps_root) + eps) + wd * pf;
-    mo[i] = mi;
-    vo[i] = vi;
-    po[i] = from_float<T>(pf - lr * upd);
+  const long tid = blockIdx.x * long(blockDim.x) + threadIdx.x, stride = long(gridDim.x) * blockDim.x;
+  if (packs_ok(e, 7, sizeof(T), 0b0010011u)) {
+    for (long i = tid; i < (e.n >> 2); i += stride) {
+      const Pack4<T> pp = reinterpret_cast<const Pack4<T>*>(p)[i], gp = reinterpret_cast<const Pack4<T>*>(g)[i];
+      const float4 m4 = reinterpret_cast<const float4*>(m)[i], v4 = reinterpret_cast<const float4*>(v)[i];
+      Pack4<T> o;
+      float4 mo4, vo4;
+      adamw_fwd_one<T>(pp.v[0], gp.v[0], m4.x, v4.x, o.v[0], mo4.x, vo4.x, lr, b1, b2, eps, eps_root, wd, bc1, bc2);
+      adamw_fwd_one<T>(pp.v[1], gp.v[1], m4.y, v4.y, o.v[1], mo4.y, vo4.y, lr, b1, b2, eps, eps_root, wd, bc1, bc2);
+      adamw_fwd_one<T>(pp.v[2], gp.v[2], m4.z, v4.z, o.v[2], mo4.z, vo4.z, lr, b1, b2, eps, eps_root, wd, bc1, bc2);
+      adamw_fwd_one<T>(pp.v[3], gp.v[3], m4.w, v4.w, o.v[3], mo4.w, vo4.w, lr, b1, b2, eps, eps_root, wd, bc1, bc2);
+      reinterpret_cast<Pack4<T>*>(po)[i] = o;
+      reinterpret_cast<float4*>(mo)[i] = mo4;
+      reinterpret_cast<float4*>(vo)[i] = vo4;
+    }
+    return;
   }
+  for (long i = tid; i < e.n; i += stride)
+    adamw_fwd_one<T>(p[i], g[i], m[i], v[i], po[i], mo[i], vo[i], lr, b1, b2, eps, eps_root, wd, bc1, bc2);
+}
+
+template <typename T>
+__device__ __forceinline__ void adamw_vjp_one(T g, float m, float v, float c_p, float c_m, float c_v, T& dp, T& dg,
+                                              float& dm, float& dv, float lr, float b1, float b2, float eps,
+                                              float eps_root, float wd, float bc1, float bc2) {
+  const float gi = to_float<T>(g);
+  const float mi = b1 * m + (1.f - b1) * gi;  // the step's new moments, recomputed
+  const float vi = b2 * v + (1.f - b2) * gi * gi;
+  const float s = sqrtf(vi / bc2 + eps_root);
+  const float den = s + eps;
+  const float du = -lr * c_p;  // cotangent of the update direction
+  const float d_mhat = du / den;
+  const float d_s = -du * (mi / bc1) / (den * den);
+  const float d_vhat = s > 0.f ? d_s / (2.f * s) : 0.f;
+  const float d_m = c_m + d_mhat / bc1;
+  const float d_v = c_v + d_vhat / bc2;
+  dp = from_float<T>(c_p * (1.f - lr * wd));
+  dg = from_float<T>((1.f - b1) * d_m + 2.f * (1.f - b2) * gi * d_v);
+  dm = b1 * d_m;
+  dv = b2 * d_v;
 }
 
 template <typename T>
@@ -594,24 +651,37 @@ __global__ void adamw_vjp_kernel(const AdamTraceEntry* __restrict__ table, float
   T* dg = static_cast<T*>(e.w[7]);
   float* dm = static_cast<float*>(e.w[8]);
   float* dv = static_cast<float*>(e.w[9]);
-  for (long i = blockIdx.x * long(blockDim.x) + threadIdx.x; i < e.n; i += long(gridDim.x) * blockDim.x) {
-    const float gi = to_float<T>(g[i]);
-    const float mi = b1 * m[i] + (1.f - b1) * gi;  // the step's new moments, recomputed
-    const float vi = b2 * v[i] + (1.f - b2) * gi * gi;
-    const float c_p = cp ? to_float<T>(cp[i]) : 0.f;
-    const float s = sqrtf(vi / bc2 + eps_root);
-    const float den = s + eps;
-    const float du = -lr * c_p;                      // cotangent of the update direction
-    const float d_mhat = du / den;
-    const float d_s = -du * (mi / bc1) / (den * den);
-    const float d_vhat = s > 0.f ? d_s / (2.f * s) : 0.f;
-    const float d_m = (cm ? cm[i] : 0.f) + d_mhat / bc1;
-    const float d_v = (cv ? cv[i] : 0.f) + d_vhat / bc2;
-    dp[i] = from_float<T>(c_p * (1.f - lr * wd));
-    dg[i] = from_float<T>((1.f - b1) * d_m + 2.f * (1.f - b2) * gi * d_v);
-    dm[i] = b1 * d_m;
-    dv[i] = b2 * d_v;
+  const long tid = blockIdx.x * long(blockDim.x) + threadIdx.x, stride = long(gridDim.x) * blockDim.x;
+  if (packs_ok(e, 10, sizeof(T), 0b0011001001u)) {  // null cotangent pointers are aligned by definition
+    for (long i = tid; i < (e.n >> 2); i += stride) {
+      const Pack4<T> gp = reinterpret_cast<const Pack4<T>*>(g)[i];
+      const float4 m4 = reinterpret_cast<const float4*>(m)[i], v4 = reinterpret_cast<const float4*>(v)[i];
+      Pack4<T> cpp;
+      float c_p[4] = {0.f, 0.f, 0.f, 0.f};
+      if (cp) {
+        cpp = reinterpret_cast<const Pack4<T>*>(cp)[i];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) c_p[k] = to_float<T>(cpp.v[k]);
+      }
+      const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+      const float4 cm4 = cm ? reinterpret_cast<const float4*>(cm)[i] : zero;
+      const float4 cv4 = cv ? reinterpret_cast<const float4*>(cv)[i] : zero;
+      Pack4<T> dpp, dgp;
+      float4 dm4, dv4;
+      adamw_vjp_one<T>(gp.v[0], m4.x, v4.x, c_p[0], cm4.x, cv4.x, dpp.v[0], dgp.v[0], dm4.x, dv4.x, lr, b1, b2, eps, eps_root, wd, bc1, bc2);
+      adamw_vjp_one<T>(gp.v[1], m4.y, v4.y, c_p[1], cm4.y, cv4.y, dpp.v[1], dgp.v[1], dm4.y, dv4.y, lr, b1, b2, eps, eps_root, wd, bc1, bc2);
+      adamw_vjp_one<T>(gp.v[2], m4.z, v4.z, c_p[2], cm4.z, cv4.z, dpp.v[2], dgp.v[2], dm4.z, dv4.z, lr, b1, b2, eps, eps_root, wd, bc1, bc2);
+      adamw_vjp_one<T>(gp.v[3], m4.w, v4.w, c_p[3], cm4.w, cv4.w, dpp.v[3], dgp.v[3], dm4.w, dv4.w, lr, b1, b2, eps, eps_root, wd, bc1, bc2);
+      reinterpret_cast<Pack4<T>*>(dp)[i] = dpp;
+      reinterpret_cast<Pack4<T>*>(dg)[i] = dgp;
+      reinterpret_cast<float4*>(dm)[i] = dm4;
+      reinterpret_cast<float4*>(dv)[i] = dv4;
+    }
+    return;
   }
+  for (long i = tid; i < e.n; i += stride)
+    adamw_vjp_one<T>(g[i], m[i], v[i], cp ? to_float<T>(cp[i]) : 0.f, cm ? cm[i] : 0.f, cv ? cv[i] : 0.f, dp[i], dg[i],
+                     dm[i], dv[i], lr, b1, b2, eps, eps_root, wd, bc1, bc2);
 }
 
 // Sum of squares over a list of tensors (entries reuse AdamEntry: g = data, n = elements).
@@ -622,10 +692,28 @@ __global__ void multi_sumsq_kernel(const AdamEntry* __restrict__ table, float* _
   __shared__ float red[32];
   const AdamEntry e = table[blockIdx.y];
   const T* g = static_cast<const T*>(e.g);
+  constexpr int V = 16 / sizeof(T);
   float ss = 0.f;
-  for (long i = blockIdx.x * long(blockDim.x) + threadIdx.x; i < e.n; i += long(gridDim.x) * blockDim.x) {
-    const float f = to_float<T>(g[i]);
-    ss = fmaf(f, f, ss);
+  const long tid = blockIdx.x * long(blockDim.x) + threadIdx.x, stride = long(gridDim.x) * blockDim.x;
+  if ((reinterpret_cast<uintptr_t>(g) & 15) == 0) {
+    const long n_vec = e.n / V;
+    for (long i = tid; i < n_vec; i += stride) {
+      const Vec<T> v = load_vec(g + i * V);
+#pragma unroll
+      for (int k = 0; k < V; ++k) {
+        const float f = to_float<T>(v.v[k]);
+        ss = fmaf(f, f, ss);
+      }
+    }
+    for (long i = n_vec * V + tid; i < e.n; i += stride) {
+      const float f = to_float<T>(g[i]);
+      ss = fmaf(f, f, ss);
+    }
+  } else {
+    for (long i = tid; i < e.n; i += stride) {
+      const float f = to_float<T>(g[i]);
+      ss = fmaf(f, f, ss);
+    }
   }
   ss = block_sum(ss, red);
   if (threadIdx.x == 0) partials[blockIdx.y * long(gridDim.x) + blockIdx.x] = ss;
@@ -827,7 +915,7 @@ extern "C" int bgn_adamw_multi(const void* table, int n_tensors, long max_n, flo
 }
 
 static inline dim3 multi_grid(int n_tensors, long max_n) {
-  long per_row = (max_n + 256 * 8 - 1) / (256 * 8);
+  long per_row = (max_n / 4 + 256 * 8 - 1) / (256 * 8);
   per_row = per_row < 1 ? 1 : (per_row > 128 ? 128 : per_row);
   return dim3((unsigned)per_row, (unsigned)n_tensors);
 }
@@ -848,14 +936,18 @@ extern "C" int bgn_adamw_traced(const void* table, int n_tensors, long max_n, in
   return int(cudaGetLastError());
 }
 
-extern "C" int bgn_multi_sumsq_blocks(void) { return 16; }
+extern "C" int bgn_multi_sumsq_blocks(void) { return 128; }
 
-extern "C" int bgn_multi_sumsq(const void* table, int n_tensors, float* partials, float* out, int accumulate,
-                               float max_norm, int type, cudaStream_t st) {
+extern "C" int bgn_multi_sumsq(const void* table, int n_tensors, long max_n, float* partials, float* out,
+                               int accumulate, float max_norm, int type, cudaStream_t st) {
   if (n_tensors <= 0 || n_tensors > 65535) return int(cudaErrorInvalidValue);
-  const dim3 grid(16, (unsigned)n_tensors);
+  // Blocks per tensor follow the largest one (about eight 16-byte packets per thread, at most
+  // 128); blocks of shorter tensors write a zero partial and retire.
+  int blocks = int((max_n / 8 + 256 * 8 - 1) / (256 * 8));
+  blocks = blocks < 1 ? 1 : (blocks > 128 ? 128 : blocks);
+  const dim3 grid((unsigned)blocks, (unsigned)n_tensors);
   BGN_DISPATCH(type, { multi_sumsq_kernel<T><<<grid, 256, 0, st>>>((const AdamEntry*)table, partials); });
-  multi_sumsq_finish_kernel<<<1, 1024, 0, st>>>(partials, 16L * n_tensors, out, accumulate, max_norm);
+  multi_sumsq_finish_kernel<<<1, 1024, 0, st>>>(partials, long(blocks) * n_tensors, out, accumulate, max_norm);
   return int(cudaGetLastError());
 }
 

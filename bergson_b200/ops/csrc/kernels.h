@@ -99,10 +99,10 @@ int bgn_adamw_traced(const void* table, int n_tensors, long max_n, int backward,
                      float eps, float eps_root, float wd, float bc1, float bc2, int type, cudaStream_t stream);
 // Sum of squares over a list of tensors (table entries as above, only g and n are read) into
 // out[0] (added to it when `accumulate`); with max_norm > 0, out[1] = min(1, max_norm /
-// (sqrt(out[0]) + 1e-6)).  `partials` holds bgn_multi_sumsq_blocks() * n_tensors floats; the
-// partials are added in a fixed order.
+// (sqrt(out[0]) + 1e-6)).  `partials` holds bgn_multi_sumsq_blocks() * n_tensors floats (an upper
+// bound); max_n is the largest tensor's element count; the partials are added in a fixed order.
 int bgn_multi_sumsq_blocks(void);
-int bgn_multi_sumsq(const void* table, int n_tensors, float* partials, float* out, int accumulate,
+int bgn_multi_sumsq(const void* table, int n_tensors, long max_n, float* partials, float* out, int accumulate,
                     float max_norm, int type, cudaStream_t stream);
 // out[r] += sum_k x[r, k]^2  (x 16-bit or fp32).
 int bgn_row_sumsq(const void* x, float* out, long rows, long d, long ldx, int type,
