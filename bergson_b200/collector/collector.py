@@ -10,12 +10,15 @@ computed as ``(g P_out^T)^T (a P_in^T)`` (reference
 Two execution paths produce the same numbers:
 
 * the **torch path** (any device, every option), and
-* the **fused path** (CUDA, 16-bit activations, ``projection_dim == 16``, no Adam
-  normaliser, no bias column): ``a P_in^T`` runs in a TMA-fed tcgen05 kernel in the
-  forward hook, and in the backward hook one kernel projects ``g``, contracts over the
-  example's tokens against the cached ``a P_in^T`` and adds the 16x16 block into the
-  fp32 row accumulator of the batch at the module's column offset.  Adafactor row and
-  column scales are folded into the projection matrices once.
+* the **fused path** (CUDA, 16-bit activations, ``projection_dim`` 8..64, no Adam
+  normaliser): in-tree layers emit ``a P_in^T`` and ``g P_out^T`` as side outputs of their
+  own forward and input-gradient GEMMs (``ops.linear`` taps); a contraction kernel turns both
+  into the example's ``p x p`` block (or per-token rows) in the fp32 row accumulator of the
+  batch at the module's column offset.  Adafactor row and column scales are folded into the
+  projection matrices once; a bias column is the constant vector ``P_in[:, I]`` added to the
+  projected activations.  Layers that are not in-tree take the hook form of the same path
+  (``projection_dim == 16``): a skinny projection kernel in the forward hook, and one kernel
+  in the backward hook that projects ``g`` and contracts.
 """
 
 from __future__ import annotations
@@ -106,7 +109,7 @@ class _FusedTap:
         module._tapped = True  # the forward hook that follows skips this call
         i = getattr(module, LayerAdapter.in_attr(module))
         o = getattr(module, LayerAdapter.out_attr(module))
-        return c._tap_matrices(self.name, o, i, x.device, x.dtype)
+        return c._tap_matrices(self.name, o, i, x.device, x.dtype, bool(module._collect_bias))
 
     def collect(self, module: nn.Module, a_proj: Tensor, g_proj: Tensor, lead_shape) -> None:
         from ..ops import native
@@ -115,6 +118,11 @@ class _FusedTap:
         p = c.per_module_projection_dim
         acc = c._row_acc[: c._fused_rows]
         off = c._col_offsets[self.name]
+        bias_col = c._tap_bias.get(self.name)
+        if bias_col is not None:
+            # The bias gradient is the gradient for a constant input of one: its projection adds
+            # the same vector (the bias column of P_in) to every token's projected activation.
+            a_proj = a_proj + bias_col
         if c.attribute_tokens:
             native.proj_token_rows(g_proj, a_proj, c._token_index, acc, p, off)
         else:
@@ -160,6 +168,7 @@ class HookCollectorBase(ContextDecorator, ABC):
         self._row_acc: Tensor | None = None
         self._col_offsets: dict[str, int] = {}
         self._fused_mats: dict = {}
+        self._tap_bias: dict[str, Tensor] = {}  # name -> bias column of the input projection
         self._fused_written: set[str] = set()
 
         self.target_info = self.discover_targets(
@@ -478,15 +487,18 @@ class HookCollectorBase(ContextDecorator, ABC):
             self._fused_mats[key] = (p_in.to(dtype).contiguous(), p_out.to(dtype).contiguous())
         return self._fused_mats[key]
 
-    def _tap_matrices(self, name: str, o: int, i: int, device, dtype) -> tuple[Tensor, Tensor]:
+    def _tap_matrices(self, name: str, o: int, i: int, device, dtype, bias: bool = False) -> tuple[Tensor, Tensor]:
         """(P_in [p16, I], P_out [p16, O]) for the GEMM side outputs: the projection matrices
-        with the Adafactor column / row scales folded in, rows zero-padded to a multiple of 16."""
+        with the Adafactor column / row scales folded in, rows zero-padded to a multiple of 16.
+        With ``bias`` the input projection has one more column (the bias acts as an input that
+        is always one); that column is kept aside in ``_tap_bias`` and added to the projected
+        activations when the tap collects."""
         key = ("tap", name, device, dtype)
         if key not in self._fused_mats:
             p = self.per_module_projection_dim
             assert p is not None
             p16 = (p + 15) // 16 * 16
-            p_in = self.projection(name, p, i, "right", device, dtype).float()
+            p_in = self.projection(name, p, i + 1 if bias else i, "right", device, dtype).float()
             p_out = self.projection(name, p, o, "left", device, dtype).float()
             norm = self.processor.normalizers.get(name)
             if isinstance(norm, AdafactorNormalizer):
@@ -494,11 +506,15 @@ class HookCollectorBase(ContextDecorator, ABC):
                 p_in = p_in * col.to(device).float()[None, :]
                 p_out = p_out * row.to(device).float()[None, :]
             pad = lambda m: torch.cat([m, m.new_zeros(p16 - p, m.shape[1])]) if p16 > p else m  # noqa: E731
-            self._fused_mats[key] = (pad(p_in).to(dtype).contiguous(), pad(p_out).to(dtype).contiguous())
+            p_in = pad(p_in).to(dtype)
+            if bias:
+                self._tap_bias[name] = p_in[:, i].float().contiguous()  # [p16], rounded like the matrix
+                p_in = p_in[:, :i]
+            self._fused_mats[key] = (p_in.contiguous(), pad(p_out).to(dtype).contiguous())
         return self._fused_mats[key]
 
     def _tap_accepts(self, module: nn.Module, x: Tensor) -> bool:
-        if not self._fused_enabled or module._collect_bias:
+        if not self._fused_enabled:
             return False
         if x.dtype not in (torch.bfloat16, torch.float16) or x.ndim != 3 or x.shape[0] != getattr(self, "_fused_n", -1):
             return False

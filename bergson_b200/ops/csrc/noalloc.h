@@ -24,6 +24,8 @@ enum { kBgnNoAllocMaxD = 8192, kBgnNoAllocPartials = 296 };
 // pointer is null; bgn_noalloc_last_error() then names which, or gives the CUDA error's text.
 //
 // * Allocates nothing: no cudaMalloc, cudaFree or allocating library call.
+// * Every pointer and the stream must belong to the device that is current at the call: the
+//   scratch of that device is used, and nothing checks where the buffers live.
 // * The first call on each device resolves the device address of the scratch array
 //   (cudaGetSymbolAddress with that device current); later calls only launch kernels.
 // * All calls on a device share the scratch, which keeps the previous call's contents;
