@@ -59,26 +59,40 @@ def _make_split_hessian(hessians: dict[str, torch.Tensor], modules: list[str], d
     return transform
 
 
-def _gather_queries_ok(score_cfg: ScoreConfig, preprocess_cfg: PreprocessConfig, device, dtype, attribute_tokens) -> bool:
-    """Whether the queries can stay sharded over the ranks and be read through the fused
-    all-gather + score GEMM: CUDA ranks of one NVLink domain, 16-bit scoring, row-wise query
-    preprocessing only (no aggregation over queries, no index-side transform).  Every input is
-    the same on all ranks, so all ranks take the same branch."""
+def _gather_queries_obstacle(score_cfg: ScoreConfig, preprocess_cfg: PreprocessConfig, device, dtype,
+                             attribute_tokens) -> str | None:
+    """None when the queries can stay sharded over the ranks and be read through the fused
+    all-gather + score GEMM, else the reason why not: it takes CUDA ranks of one NVLink domain,
+    16-bit scoring and row-wise query preprocessing only (no aggregation over queries, no
+    index-side transform).  Every input is the same on all ranks, so all ranks take the same
+    branch."""
     import os
 
     import torch.distributed as dist
 
     from ..parallel.peer import symmetric_memory_available
 
-    if not (dist.is_initialized() and dist.get_world_size() > 1) or torch.device(device).type != "cuda":
-        return False
-    if os.environ.get("BERGSON_B200_DISABLE_PEER") == "1" or not symmetric_memory_available():
-        return False
-    if dtype not in (torch.bfloat16, torch.float16) or attribute_tokens:
-        return False
+    if not (dist.is_initialized() and dist.get_world_size() > 1):
+        return "single rank"
+    if torch.device(device).type != "cuda":
+        return "not on GPUs"
+    if os.environ.get("BERGSON_B200_DISABLE_PEER") == "1":
+        return "BERGSON_B200_DISABLE_PEER=1"
+    if not symmetric_memory_available():
+        return "peer memory is not available to these ranks"
+    if dtype not in (torch.bfloat16, torch.float16):
+        return f"scoring in {dtype}"
+    if attribute_tokens:
+        return "per-token rows"
     if preprocess_cfg.aggregation != "none" or preprocess_cfg.normalize_aggregated_grad:
-        return False
-    return not (preprocess_cfg.hessian_path and preprocess_cfg.unit_normalize)
+        return "queries are aggregated"
+    if preprocess_cfg.hessian_path and preprocess_cfg.unit_normalize:
+        return "index-side preconditioning"
+    return None
+
+
+def _gather_queries_ok(score_cfg: ScoreConfig, preprocess_cfg: PreprocessConfig, device, dtype, attribute_tokens) -> bool:
+    return _gather_queries_obstacle(score_cfg, preprocess_cfg, device, dtype, attribute_tokens) is None
 
 
 def create_scorer(path: Path, data: Dataset, score_cfg: ScoreConfig, preprocess_cfg: PreprocessConfig, device,
@@ -169,9 +183,11 @@ def score_worker(rank: int, local_rank: int, world_size: int, index_cfg: IndexCo
     ranges = [None] if qbs is None or qbs >= num_queries else [
         (lo, min(lo + qbs, num_queries)) for lo in range(0, num_queries, qbs)
     ]
-    shard_queries = _gather_queries_ok(score_cfg, preprocess_cfg, device, dtype, index_cfg.attribute_tokens)
-    if shard_queries and rank == 0:
-        print(f"score: query rows sharded over {world_size} ranks in peer memory (all-gather fused into the score GEMM)")
+    obstacle = _gather_queries_obstacle(score_cfg, preprocess_cfg, device, dtype, index_cfg.attribute_tokens)
+    shard_queries = obstacle is None
+    if rank == 0 and world_size > 1:
+        print(f"score: query rows sharded over {world_size} ranks in peer memory (all-gather fused into the score GEMM)"
+              if shard_queries else f"score: query rows replicated on every rank ({obstacle})", flush=True)
     for qr in ranges:
         scorer = create_scorer(index_cfg.partial_run_path, ds, score_cfg, preprocess_cfg, device=device, dtype=dtype,
                                attribute_tokens=index_cfg.attribute_tokens, query_range=qr,

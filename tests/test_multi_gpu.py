@@ -144,6 +144,7 @@ def test_score_with_sharded_queries_matches_single_gpu(tmp_path):
         return out
 
     build_model = [m if m != "--index_cfg.precision" else "--precision" for m in model]
+    model = model + ["--score_cfg.precision", "bf16"]  # the fused gather needs 16-bit scoring (default: fp32)
     cli("build", tmp_path / "query", "--data.dataset", "synthetic:zipf?n=13&len=160&vocab=1024&seed=1&min_len=90",
         *build_model, "--nproc_per_node", "1")
     data = ["--data.dataset", "synthetic:zipf?n=24&len=160&vocab=1024&seed=0&min_len=90"]
