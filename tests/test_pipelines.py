@@ -113,3 +113,20 @@ def test_help_for_every_command():
         out = subprocess.run([sys.executable, "-m", "bergson_b200", name, "--help"], capture_output=True, text=True,
                              cwd=Path(__file__).resolve().parents[1])
         assert out.returncode == 0 and "usage" in out.stdout.lower(), (name, out.stderr[-500:])
+
+
+def test_interrupted_build_is_refused_then_overwritten(tmp_path):
+    """A run that died leaves `<run>.part` behind: the next build refuses to touch it unless
+    asked to overwrite, and the overwritten run equals a fresh one."""
+    run("build", tmp_path / "fresh", *COMMON, "--data.dataset", TRAIN, "--projection_dim", "4")
+    part = tmp_path / "broken.part"
+    part.mkdir()
+    (part / "gradients.bin").write_bytes(b"\x00" * 100)  # truncated store of the dead run
+    (part / "info.json").write_text("{")                 # and a half-written header
+    with pytest.raises(FileExistsError, match="already exists"):
+        run("build", tmp_path / "broken", *COMMON, "--data.dataset", TRAIN, "--projection_dim", "4")
+    assert (part / "gradients.bin").stat().st_size == 100  # nothing was touched
+    run("build", tmp_path / "broken", *COMMON, "--data.dataset", TRAIN, "--projection_dim", "4", "--overwrite", "true")
+    assert not part.exists()
+    a, b = np.asarray(load_gradients(tmp_path / "fresh")), np.asarray(load_gradients(tmp_path / "broken"))
+    np.testing.assert_array_equal(a, b)
