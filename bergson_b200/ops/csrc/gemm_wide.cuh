@@ -496,7 +496,7 @@ gemm_wide_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       if (r >= p.gather_world) r -= p.gather_world;
       const uint4* src = reinterpret_cast<const uint4*>(p.gather_src[r]);
       uint4* dst = reinterpret_cast<uint4*>(p.d_gather_dst) + long(r) * n_vec;
-      constexpr int kInFlight = 8;
+      constexpr int kInFlight = 16;
       for (long i = lo + lane; i < hi; i += 32 * kInFlight) {
         uint4 v[kInFlight];
 #pragma unroll
