@@ -169,3 +169,43 @@ def test_linear_pads_odd_output_sizes_and_stays_twice_differentiable():
     (gw64,) = torch.autograd.grad(gx64.pow(2).sum(), w64)
     assert (gx.double() - gx64).abs().max() <= 3e-2 * gx64.abs().max()
     assert (gw.double() - gw64).abs().max() <= 5e-2 * gw64.abs().max()
+
+
+def test_gather_with_copy_and_scatter_forms_on_one_gpu():
+    """The peer forms of the wide GEMM with both "ranks" on this GPU (every table entry is a
+    local buffer): the copier warps fill the other rank's rows of A while the own rows' tiles
+    run, and the epilogue scatters row blocks into the owners' slots."""
+    from bergson_b200.ops import native
+
+    torch.manual_seed(0)
+    world, rows, K, N = 2, 512, 384, 320
+    shards = [torch.randn(rows, K, device="cuda").to(torch.bfloat16) for _ in range(world)]
+    w = (torch.randn(N, K, device="cuda") * 0.1).to(torch.bfloat16)
+    want = torch.cat(shards).float() @ w.float().T
+    for rank in range(world):
+        full = torch.zeros(world * rows, K, device="cuda", dtype=torch.bfloat16)
+        full[rank * rows : (rank + 1) * rows] = shards[rank]
+        done = torch.zeros(8, dtype=torch.int32, device="cuda")
+        y, _ = native.gemm(full, w, False, False, None, False, None, False, None, cta_group=2, wide=True,
+                           a_peer_ptrs=[s.data_ptr() for s in shards], gather_done=done, gather_rank=rank)
+        torch.cuda.synchronize()
+        assert torch.equal(full, torch.cat(shards))  # the copiers delivered the other rank's rows
+        assert int(done[1 - rank]) > 0 and int(done[rank]) == 0
+        assert (y.float() - want).abs().max() <= 2e-2 * want.abs().max()
+    # Scatter: rank `slot` pushes row block o of its product into owner o's [world, rows, N] region.
+    x = torch.cat(shards)
+    regions = [torch.full((world, rows, N), float("nan"), device="cuda", dtype=torch.bfloat16) for _ in range(world)]
+    for slot in range(world):
+        native.gemm(x, w, False, False, None, False, None, False, None, cta_group=2, wide=True,
+                    d_peer_ptrs=[r.data_ptr() for r in regions], d_rows_per_rank=rows, d_slot=slot)
+    torch.cuda.synchronize()
+    for owner in range(world):
+        block = want[owner * rows : (owner + 1) * rows]
+        for slot in range(world):
+            got = regions[owner][slot].float()
+            assert torch.isfinite(got).all()
+            assert (got - block).abs().max() <= 2e-2 * want.abs().max()
+        summed = native.slot_reduce(regions[owner], shards[owner][:, :N].contiguous())
+        ref = shards[owner][:, :N].float() + 2 * block
+        assert (summed.float() - ref).abs().max() <= 3e-2 * ref.abs().max()
+    assert int(native.kernel_status(0).item()) == 0
