@@ -768,11 +768,24 @@ class CollectorComputer:
         self.logger.info(f"Total processed: {total.item()}")
 
 
+def _direct_hidden_ok(model) -> bool:
+    """In-tree models can skip the last position's logits by calling ``hidden`` and the head
+    themselves, unless the model is wrapped by FSDP2: its parameters are only gathered by the
+    hooks of ``__call__``."""
+    if not isinstance(model, NativeCausalLM):
+        return False
+    try:
+        from torch.distributed.fsdp import FSDPModule
+    except ImportError:  # older torch: no fully_shard, nothing to bypass
+        return True
+    return not isinstance(model, FSDPModule)
+
+
 def _per_token_losses(model, x: Tensor, targets: Tensor, label_smoothing: float = 0.0) -> tuple[Tensor, Tensor]:
     """(per-token CE ``[N, S-1]`` in fp32, logits or None).  In-tree models skip the
     last position's logits and use the fused CE kernel; other models go through
     ``model(x).logits``."""
-    if isinstance(model, NativeCausalLM):
+    if _direct_hidden_ok(model):
         h = model.hidden(x)[:, :-1]
         logits = model.get_output_embeddings()(h)
     else:
@@ -821,7 +834,7 @@ def fwd_bwd_hessian_factory(index_cfg: IndexConfig, hessian_cfg: HessianConfig) 
         targets = y[:, 1:]
         masks = targets != -100
         denoms = masks.sum(dim=1).clamp_min(1).float() if index_cfg.loss_reduction == "mean" else 1.0
-        if isinstance(model, NativeCausalLM):
+        if _direct_hidden_ok(model):
             logits = model.get_output_embeddings()(model.hidden(x)[:, :-1])
         else:
             logits = model(x).logits[:, :-1]

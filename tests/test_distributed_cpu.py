@@ -119,3 +119,12 @@ def test_distributed_autocorrelation_exchange_two_ranks(tmp_path):
     for n, r in owner.items():
         torch.testing.assert_close(got[r]["hessians"][n], want[n], rtol=1e-5, atol=1e-5)
         assert n not in got[1 - r]["hessians"]
+
+
+def test_fsdp2_build_two_ranks_equals_one(tmp_path):
+    """`--fsdp true` wraps the layers with `fully_shard`; the store must not depend on it."""
+    opt = ["--model", MODEL, "--data.dataset", TRAIN, "--projection_dim", "4", "--token_batch_size", "64"]
+    run("build", tmp_path / "plain", *opt, "--nproc_per_node", 1)
+    run("build", tmp_path / "fsdp", *opt, "--nproc_per_node", 2, "--fsdp", "true")
+    a, b = np.asarray(load_gradients(tmp_path / "plain")), np.asarray(load_gradients(tmp_path / "fsdp"))
+    np.testing.assert_allclose(a, b, rtol=1e-4, atol=1e-6)
