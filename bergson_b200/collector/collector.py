@@ -15,8 +15,8 @@ Two execution paths produce the same numbers:
   own forward and input-gradient GEMMs (``ops.linear`` taps); a contraction kernel turns both
   into the example's ``p x p`` block (or per-token rows) in the fp32 row accumulator of the
   batch at the module's column offset.  Adafactor row and column scales are folded into the
-  projection matrices once; a bias column is the constant vector ``P_in[:, I]`` added to the
-  projected activations.  Layers that are not in-tree take the hook form of the same path
+  projection matrices once; without a normaliser a bias column is the constant vector
+  ``P_in[:, I]`` added to the projected activations.  Layers that are not in-tree take the hook form of the same path
   (``projection_dim == 16``): a skinny projection kernel in the forward hook, and one kernel
   in the backward hook that projects ``g`` and contracts.
 """
@@ -521,7 +521,12 @@ class HookCollectorBase(ContextDecorator, ABC):
         name = module._name
         if name not in self._col_offsets or name in self.attention_cfgs:
             return False
-        return not isinstance(self.processor.normalizers.get(name), AdamNormalizer)
+        norm = self.processor.normalizers.get(name)
+        if module._collect_bias and norm is not None:
+            # A normaliser scales the bias gradient by its own second moments, i.e. with another
+            # left projection than the weight block's: that case stays on the hook path.
+            return False
+        return not isinstance(norm, AdamNormalizer)
 
     def begin_fused_batch(self, n: int, device, collection_mask: Tensor | None = None) -> None:
         """Zero the fp32 row accumulator of the coming batch (one row per document, or per
