@@ -141,6 +141,26 @@ std::vector<at::Tensor> layernorm_bwd(at::Tensor dy, at::Tensor x, at::Tensor w,
   return {dx, dw, db};
 }
 
+// Backward of layernorm_bwd: (cotangent of dx, of dw, of db) -> (d_dy, d_x, d_w).
+std::vector<at::Tensor> layernorm_bwd_bwd(at::Tensor cu, at::Tensor cw, at::Tensor cb, at::Tensor dy, at::Tensor x,
+                                          at::Tensor w, at::Tensor mean, at::Tensor rstd) {
+  CHECK_CUDA_CONTIG(cu); CHECK_CUDA_CONTIG(dy); CHECK_CUDA_CONTIG(x);
+  TORCH_CHECK(cu.scalar_type() == x.scalar_type() && dy.scalar_type() == x.scalar_type() && cu.numel() == x.numel() &&
+              dy.numel() == x.numel() && x.dim() == 2);
+  c10::cuda::CUDAGuard guard(x.device());
+  auto wc = w.to(x.scalar_type()).contiguous();
+  auto vw = cw.to(at::kFloat).contiguous(), sb = cb.to(at::kFloat).contiguous();
+  TORCH_CHECK(vw.numel() == x.size(1) && sb.numel() == x.size(1));
+  auto d_dy = at::empty_like(x), d_x = at::empty_like(x);
+  const int n_partial = (int)std::min<int64_t>(x.size(0), 148 * 2);
+  auto pw = at::empty({n_partial, x.size(1)}, x.options().dtype(at::kFloat));
+  check(bgn_layernorm_bwd_bwd(cu.data_ptr(), vw.data_ptr<float>(), sb.data_ptr<float>(), dy.data_ptr(), x.data_ptr(),
+                              wc.data_ptr(), mean.data_ptr<float>(), rstd.data_ptr<float>(), d_dy.data_ptr(),
+                              d_x.data_ptr(), pw.data_ptr<float>(), n_partial, x.size(0), (int)x.size(1), type_code(x),
+                              stream()), "layernorm_bwd_bwd");
+  return {d_dy, d_x, pw.sum(0).to(w.scalar_type())};
+}
+
 at::Tensor rotary(at::Tensor x, at::Tensor cos, at::Tensor sin, int64_t rot, bool inverse) {
   CHECK_CUDA_CONTIG(x);
   TORCH_CHECK(x.dim() == 4, "rotary expects [B, S, H, D]");
@@ -176,6 +196,17 @@ at::Tensor gelu_fwd(at::Tensor x, bool tanh_approx) {
   auto y = at::empty_like(x);
   check(bgn_gelu_fwd(x.data_ptr(), y.data_ptr(), x.numel(), tanh_approx, type_code(x), stream()), "gelu_fwd");
   return y;
+}
+
+std::vector<at::Tensor> gelu_bwd_bwd(at::Tensor c, at::Tensor dy, at::Tensor x, bool tanh_approx) {
+  CHECK_CUDA_CONTIG(c); CHECK_CUDA_CONTIG(dy); CHECK_CUDA_CONTIG(x);
+  TORCH_CHECK(c.scalar_type() == x.scalar_type() && dy.scalar_type() == x.scalar_type() && c.numel() == x.numel() &&
+              dy.numel() == x.numel());
+  c10::cuda::CUDAGuard guard(x.device());
+  auto d_dy = at::empty_like(x), d_x = at::empty_like(x);
+  check(bgn_gelu_bwd_bwd(c.data_ptr(), dy.data_ptr(), x.data_ptr(), d_dy.data_ptr(), d_x.data_ptr(), x.numel(),
+                         tanh_approx, type_code(x), stream()), "gelu_bwd_bwd");
+  return {d_dy, d_x};
 }
 
 at::Tensor gelu_bwd(at::Tensor dy, at::Tensor x, bool tanh_approx) {
@@ -652,11 +683,13 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("rmsnorm_bwd", &rmsnorm_bwd);
   m.def("layernorm_fwd", &layernorm_fwd);
   m.def("layernorm_bwd", &layernorm_bwd);
+  m.def("layernorm_bwd_bwd", &layernorm_bwd_bwd);
   m.def("rotary", &rotary);
   m.def("swiglu_fwd", &swiglu_fwd);
   m.def("swiglu_bwd", &swiglu_bwd);
   m.def("gelu_fwd", &gelu_fwd);
   m.def("gelu_bwd", &gelu_bwd);
+  m.def("gelu_bwd_bwd", &gelu_bwd_bwd);
   m.def("ce_fwd", &ce_fwd);
   m.def("ce_bwd", &ce_bwd);
   m.def("proj_right", &proj_right);

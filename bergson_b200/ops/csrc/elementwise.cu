@@ -238,6 +238,89 @@ __global__ void layernorm_bwd_kernel(const T* __restrict__ dy, const T* __restri
   }
 }
 
+// Backward of layernorm_bwd.  With g = dy * w, xh = (x - mean) * rstd, the first backward is
+//   dx = rstd * (g - mean(g) - xh * mean(g xh)),  dw = sum_rows dy xh,  db = sum_rows dy.
+// Given cotangents U (of dx, [rows, d]), Vw (of dw, [d]) and Sb (of db, [d]) this kernel returns
+//   d_dy = w * rstd * P(U) + Vw * xh + Sb
+//   d_x  = -rstd^2 * (xh * (mean(g U) - mean(g) mean(U) - mean(g xh) mean(U xh)) + mean(U xh) * P'(g) + mean(g xh) * P'(U))
+//          + rstd * P(Vw * dy)
+//   d_w  = sum_rows dy * rstd * P(U)
+// where P(z) = z - mean(z) - xh * mean(z xh) and P'(z) = z - mean(z) - xh * mean(z xh) (the same
+// projection; written twice for readability of the formula).  All means run over the row.
+template <typename T>
+__global__ void layernorm_bwd_bwd_kernel(const T* __restrict__ U, const float* __restrict__ Vw,
+                                         const float* __restrict__ Sb, const T* __restrict__ dy,
+                                         const T* __restrict__ x, const T* __restrict__ w,
+                                         const float* __restrict__ mean, const float* __restrict__ rstd,
+                                         T* __restrict__ d_dy, T* __restrict__ d_x, float* __restrict__ dw_partial,
+                                         long rows, int d) {
+  __shared__ float red[32];
+  constexpr int V = Vec<T>::N;
+  constexpr int kMaxPer = 4;
+  float dw_acc[kMaxPer][V];
+#pragma unroll
+  for (int a = 0; a < kMaxPer; ++a)
+#pragma unroll
+    for (int k = 0; k < V; ++k) dw_acc[a][k] = 0.f;
+
+  for (long r = blockIdx.x; r < rows; r += gridDim.x) {
+    const T* xr = x + r * d;
+    const T* gr = dy + r * d;
+    const T* ur = U + r * d;
+    const float mu = mean[r], rs = rstd[r];
+    float sg = 0.f, sgx = 0.f, su = 0.f, sux = 0.f, sgu = 0.f, sq = 0.f, sqx = 0.f;
+    for (int i = threadIdx.x * V; i < d; i += blockDim.x * V) {
+      Vec<T> xv = load_vec(xr + i), gv = load_vec(gr + i), uv = load_vec(ur + i), wv = load_vec(w + i);
+#pragma unroll
+      for (int k = 0; k < V; ++k) {
+        const float xh = (to_float<T>(xv.v[k]) - mu) * rs;
+        const float gy = to_float<T>(gv.v[k]);
+        const float g = gy * to_float<T>(wv.v[k]);
+        const float u = to_float<T>(uv.v[k]);
+        const float q = Vw[i + k] * gy;
+        sg += g;
+        sgx = fmaf(g, xh, sgx);
+        su += u;
+        sux = fmaf(u, xh, sux);
+        sgu = fmaf(g, u, sgu);
+        sq += q;
+        sqx = fmaf(q, xh, sqx);
+      }
+    }
+    const float inv_d = 1.f / d;
+    const float a = block_sum(sg, red) * inv_d, b = block_sum(sgx, red) * inv_d;
+    const float mU = block_sum(su, red) * inv_d, c = block_sum(sux, red) * inv_d;
+    const float mgu = block_sum(sgu, red) * inv_d;
+    const float mq = block_sum(sq, red) * inv_d, mqx = block_sum(sqx, red) * inv_d;
+    const float e = mgu - a * mU - b * c;
+    int slot = 0;
+    for (int i = threadIdx.x * V; i < d; i += blockDim.x * V, ++slot) {
+      Vec<T> xv = load_vec(xr + i), gv = load_vec(gr + i), uv = load_vec(ur + i), wv = load_vec(w + i), o1, o2;
+#pragma unroll
+      for (int k = 0; k < V; ++k) {
+        const float xh = (to_float<T>(xv.v[k]) - mu) * rs;
+        const float gy = to_float<T>(gv.v[k]);
+        const float wk = to_float<T>(wv.v[k]);
+        const float g = gy * wk;
+        const float u = to_float<T>(uv.v[k]);
+        const float vw = Vw[i + k];
+        const float pu = u - mU - xh * c;
+        const float pg = g - a - xh * b;
+        const float pq = vw * gy - mq - xh * mqx;
+        o1.v[k] = from_float<T>(wk * rs * pu + vw * xh + Sb[i + k]);
+        o2.v[k] = from_float<T>(-rs * rs * (xh * e + c * pg + b * pu) + rs * pq);
+        if (slot < kMaxPer) dw_acc[slot][k] = fmaf(gy, rs * pu, dw_acc[slot][k]);
+      }
+      store_vec(d_dy + r * d + i, o1);
+      store_vec(d_x + r * d + i, o2);
+    }
+  }
+  int slot = 0;
+  for (int i = threadIdx.x * V; i < d && slot < kMaxPer; i += blockDim.x * V, ++slot)
+#pragma unroll
+    for (int k = 0; k < V; ++k) dw_partial[long(blockIdx.x) * d + i + k] = dw_acc[slot][k];
+}
+
 // ---- rotary ---------------------------------------------------------------------------
 
 template <typename T>
@@ -388,6 +471,39 @@ __global__ void gelu_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ 
     for (int k = 0; k < V; ++k)
       o.v[k] = from_float<T>(to_float<T>(gv.v[k]) * gelu_grad_f(to_float<T>(xv.v[k]), tanh_approx));
     store_vec(dx + i, o);
+  }
+}
+
+// Second derivative of GELU (for the backward of the backward).
+__device__ __forceinline__ float gelu_grad2_f(float x, bool tanh_approx) {
+  if (tanh_approx) {
+    const float k = 0.7978845608028654f, c = 0.044715f;
+    const float t = tanhf(k * (x + c * x * x * x));
+    const float s = 1.f - t * t;
+    const float u1 = k * (1.f + 3.f * c * x * x);  // u'
+    const float u2 = k * 6.f * c * x;               // u''
+    return s * (u1 + x * (0.5f * u2 - t * u1 * u1));
+  }
+  return 0.3989422804014327f * __expf(-0.5f * x * x) * (2.f - x * x);
+}
+
+// Backward of gelu_bwd: dx = dy * gelu'(x).  Given the cotangent c of dx:
+//   d_dy = c * gelu'(x),   d_x = c * dy * gelu''(x).
+template <typename T>
+__global__ void gelu_bwd_bwd_kernel(const T* __restrict__ c, const T* __restrict__ dy, const T* __restrict__ x,
+                                    T* __restrict__ d_dy, T* __restrict__ d_x, long n, int tanh_approx) {
+  constexpr int V = Vec<T>::N;
+  for (long i = (blockIdx.x * long(blockDim.x) + threadIdx.x) * V; i < n;
+       i += long(gridDim.x) * blockDim.x * V) {
+    Vec<T> cv = load_vec(c + i), gv = load_vec(dy + i), xv = load_vec(x + i), o1, o2;
+#pragma unroll
+    for (int k = 0; k < V; ++k) {
+      const float xf = to_float<T>(xv.v[k]), cf = to_float<T>(cv.v[k]);
+      o1.v[k] = from_float<T>(cf * gelu_grad_f(xf, tanh_approx));
+      o2.v[k] = from_float<T>(cf * to_float<T>(gv.v[k]) * gelu_grad2_f(xf, tanh_approx));
+    }
+    store_vec(d_dy + i, o1);
+    store_vec(d_x + i, o2);
   }
 }
 
@@ -813,6 +929,19 @@ extern "C" int bgn_layernorm_bwd(const void* dy, const void* x, const void* w, c
   return int(cudaGetLastError());
 }
 
+extern "C" int bgn_layernorm_bwd_bwd(const void* U, const float* Vw, const float* Sb, const void* dy, const void* x,
+                                     const void* w, const float* mean, const float* rstd, void* d_dy, void* d_x,
+                                     float* dw_partial, int n_partial, long rows, int d, int type, cudaStream_t st) {
+  BGN_DISPATCH(type, {
+    const int threads = vec_threads(d, Vec<T>::N);
+    if (d % Vec<T>::N || d > threads * Vec<T>::N * 4 || n_partial < 1) return int(cudaErrorInvalidValue);
+    layernorm_bwd_bwd_kernel<T><<<n_partial, threads, 0, st>>>((const T*)U, Vw, Sb, (const T*)dy, (const T*)x,
+                                                              (const T*)w, mean, rstd, (T*)d_dy, (T*)d_x, dw_partial,
+                                                              rows, d);
+  });
+  return int(cudaGetLastError());
+}
+
 extern "C" int bgn_rotary(const void* x, const float* cosT, const float* sinT, void* y, long B, int S,
                           int H, int D, int rot, int inverse, int type, cudaStream_t st) {
   const long heads = B * S * H;
@@ -852,6 +981,16 @@ extern "C" int bgn_gelu_fwd(const void* x, void* y, long n, int tanh_approx, int
   BGN_DISPATCH(type, {
     if (n % Vec<T>::N) return int(cudaErrorInvalidValue);
     gelu_fwd_kernel<T><<<grid_for(n, 256 * Vec<T>::N), 256, 0, st>>>((const T*)x, (T*)y, n, tanh_approx);
+  });
+  return int(cudaGetLastError());
+}
+
+extern "C" int bgn_gelu_bwd_bwd(const void* c, const void* dy, const void* x, void* d_dy, void* d_x, long n,
+                                int tanh_approx, int type, cudaStream_t st) {
+  BGN_DISPATCH(type, {
+    if (n % Vec<T>::N) return int(cudaErrorInvalidValue);
+    gelu_bwd_bwd_kernel<T><<<grid_for(n, 256 * Vec<T>::N), 256, 0, st>>>((const T*)c, (const T*)dy, (const T*)x,
+                                                                         (T*)d_dy, (T*)d_x, n, tanh_approx);
   });
   return int(cudaGetLastError());
 }

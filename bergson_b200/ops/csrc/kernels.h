@@ -63,6 +63,12 @@ int bgn_layernorm_fwd(const void* x, const void* w, const void* b, void* y, floa
 int bgn_layernorm_bwd(const void* dy, const void* x, const void* w, const float* mean,
                       const float* rstd, void* dx, float* dw_partial, float* db_partial,
                       int n_partial, long rows, int d, int type, cudaStream_t stream);
+// Backward of bgn_layernorm_bwd: cotangents U (of dx, [rows, d], element type), Vw and Sb (of dw and
+// db, [d] fp32) -> d_dy, d_x ([rows, d]) and per-block partial sums of d_w ([n_partial, d] fp32,
+// n_partial = number of blocks launched; d at most 4 packets per thread).
+int bgn_layernorm_bwd_bwd(const void* U, const float* Vw, const float* Sb, const void* dy, const void* x,
+                          const void* w, const float* mean, const float* rstd, void* d_dy, void* d_x,
+                          float* dw_partial, int n_partial, long rows, int d, int type, cudaStream_t stream);
 // x: [B, S, H, D]; cos/sin: [S, rot/2] fp32; rotate-half on the first `rot` features.
 int bgn_rotary(const void* x, const float* cos, const float* sin, void* y, long B, int S, int H,
                int D, int rot, int inverse, int type, cudaStream_t stream);
@@ -72,6 +78,10 @@ int bgn_swiglu_bwd(const void* dy, const void* gate, const void* up, void* dgate
 int bgn_gelu_fwd(const void* x, void* y, long n, int tanh_approx, int type, cudaStream_t stream);
 int bgn_gelu_bwd(const void* dy, const void* x, void* dx, long n, int tanh_approx, int type,
                  cudaStream_t stream);
+// Backward of gelu_bwd (dx = dy * gelu'(x)): given the cotangent c of dx, d_dy = c * gelu'(x) and
+// d_x = c * dy * gelu''(x).  n must be a multiple of the 16-byte packet.
+int bgn_gelu_bwd_bwd(const void* c, const void* dy, const void* x, void* d_dy, void* d_x, long n, int tanh_approx,
+                     int type, cudaStream_t stream);
 // logits [T, V]; loss[T], lse[T] fp32; targets int64 (ignore_index -> loss 0).
 int bgn_ce_fwd(const void* logits, const long* targets, float* loss, float* lse, long T, int V,
                long ignore_index, int type, cudaStream_t stream);

@@ -50,6 +50,16 @@ def use_fused(*tensors: Tensor) -> bool:
     return native.available()
 
 
+def _kernels_ready(*tensors: Tensor) -> bool:
+    """CUDA tensors and a loaded extension, whether or not composable mode is on (for the ops
+    whose kernels cover the backward of the backward as well)."""
+    if not all(t is None or t.is_cuda for t in tensors):
+        return False
+    from . import native
+
+    return native.available()
+
+
 # --------------------------------------------------------------------------- #
 # normalisation
 # --------------------------------------------------------------------------- #
@@ -92,6 +102,34 @@ def layer_norm_ref(x: Tensor, weight: Tensor, bias: Tensor | None, eps: float) -
     return F.layer_norm(x, (x.shape[-1],), weight, bias, eps)
 
 
+class _LayerNormBwdFn(torch.autograd.Function):
+    """``(dy, x, w) -> (dx, dw, db)`` of LayerNorm as a function with its own backward kernel
+    (the backward of the backward), so that a graph built with ``create_graph=True`` can be
+    differentiated once more.  ``mean`` and ``rstd`` are the forward's row statistics of ``x``;
+    their dependence on ``x`` is part of the kernel's formulas."""
+
+    @staticmethod
+    def forward(ctx, dy2, x2, weight, mean, rstd):
+        from . import native
+
+        dy2 = dy2.contiguous()
+        dx, dw, db = native.layernorm_bwd(dy2, x2, weight, mean, rstd, True)
+        ctx.save_for_backward(dy2, x2, weight, mean, rstd)
+        return dx, dw, db
+
+    @staticmethod
+    @torch.autograd.function.once_differentiable
+    def backward(ctx, cu, cw, cb):
+        from . import native
+
+        dy2, x2, weight, mean, rstd = ctx.saved_tensors
+        cu = torch.zeros_like(x2) if cu is None else cu.contiguous()
+        cw = torch.zeros_like(weight) if cw is None else cw
+        cb = torch.zeros_like(weight) if cb is None else cb
+        d_dy, d_x, d_w = native.layernorm_bwd_bwd(cu, cw, cb, dy2, x2, weight, mean, rstd)
+        return d_dy, d_x, d_w, None, None
+
+
 class _LayerNormFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, weight, bias, eps):
@@ -106,17 +144,24 @@ class _LayerNormFn(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dy):
-        from . import native
-
         x2, weight, mean, rstd = ctx.saved_tensors
-        dy2 = dy.reshape(-1, dy.shape[-1]).contiguous()
+        dy2 = dy.reshape(-1, dy.shape[-1])
         need_w = ctx.needs_input_grad[1] or (ctx.has_bias and ctx.needs_input_grad[2])
-        dx, dw, db = native.layernorm_bwd(dy2, x2, weight, mean, rstd, need_w)
+        if not need_w and not torch.is_grad_enabled():
+            # Frozen affine parameters and no graph to build: skip the weight-gradient partials.
+            from . import native
+
+            dx, _, _ = native.layernorm_bwd(dy2.contiguous(), x2, weight, mean, rstd, False)
+            return dx.view(ctx.shape), None, None, None
+        dx, dw, db = _LayerNormBwdFn.apply(dy2, x2, weight, mean, rstd)
         return dx.view(ctx.shape), dw, (db if ctx.has_bias else None), None
 
 
 def layer_norm(x: Tensor, weight: Tensor, bias: Tensor | None, eps: float) -> Tensor:
-    if use_fused(x, weight) and x.dtype in (torch.bfloat16, torch.float16, torch.float32):
+    """LayerNorm on the kernels: forward, backward and the backward of the backward."""
+    d, packet = x.shape[-1], 16 // max(x.element_size(), 1)
+    if (x.is_cuda and x.dtype in (torch.bfloat16, torch.float16, torch.float32) and _kernels_ready(x, weight)
+            and d % packet == 0 and d <= 2048 * packet):
         return _LayerNormFn.apply(x, weight, bias, eps)
     return layer_norm_ref(x, weight, bias, eps)
 
@@ -200,25 +245,50 @@ def gelu_ref(x: Tensor, approximate: str = "none") -> Tensor:
     return F.gelu(x, approximate=approximate)
 
 
+class _GELUBwdFn(torch.autograd.Function):
+    """``dx = dy * gelu'(x)`` as a function of ``(dy, x)`` with its own backward kernel, so that
+    a graph built with ``create_graph=True`` can be differentiated once more."""
+
+    @staticmethod
+    def forward(ctx, dy, x, tanh_approx):
+        from . import native
+
+        dy, x = dy.contiguous(), x.contiguous()
+        ctx.save_for_backward(dy, x)
+        ctx.tanh_approx = tanh_approx
+        return native.gelu_bwd(dy, x, tanh_approx)
+
+    @staticmethod
+    @torch.autograd.function.once_differentiable
+    def backward(ctx, c):
+        from . import native
+
+        dy, x = ctx.saved_tensors
+        d_dy, d_x = native.gelu_bwd_bwd(c.contiguous(), dy, x, ctx.tanh_approx)
+        return d_dy, d_x, None
+
+
 class _GELUFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, tanh_approx):
         from . import native
 
+        x = x.contiguous()
         ctx.save_for_backward(x)
         ctx.tanh_approx = tanh_approx
-        return native.gelu_fwd(x.contiguous(), tanh_approx)
+        return native.gelu_fwd(x, tanh_approx)
 
     @staticmethod
     def backward(ctx, dy):
-        from . import native
-
         (x,) = ctx.saved_tensors
-        return native.gelu_bwd(dy.contiguous(), x.contiguous(), ctx.tanh_approx), None
+        return _GELUBwdFn.apply(dy, x, ctx.tanh_approx), None
 
 
 def gelu(x: Tensor, approximate: str = "none") -> Tensor:
-    if use_fused(x) and x.dtype in (torch.bfloat16, torch.float16, torch.float32):
+    """GELU on the kernels: forward, backward and the backward of the backward (what a traced
+    training step needs); a third derivative is refused by autograd."""
+    if (_kernels_ready(x) and x.dtype in (torch.bfloat16, torch.float16, torch.float32)
+            and x.numel() % (16 // x.element_size()) == 0):
         return _GELUFn.apply(x, approximate == "tanh")
     return gelu_ref(x, approximate)
 

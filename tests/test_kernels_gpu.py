@@ -268,3 +268,37 @@ def test_rotation_hi_lo_is_fp32_accurate(native):
     _status_ok(native)
     assert got.dtype == torch.float32 and got.shape == ref.shape
     assert (got - ref).abs().max() / ref.abs().max() < 2e-4
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_layer_norm_and_gelu_second_order_match_torch(native, dtype):
+    """Value, gradients and a gradient of the gradients (what a traced training step needs) of the
+    kernel-backed LayerNorm and GELU against torch's own formulas in fp64."""
+    from bergson_b200 import ops
+
+    torch.manual_seed(0)
+    rows, d = 96, 256
+    x = torch.randn(rows, d, device="cuda").to(dtype).requires_grad_(True)
+    w = (1 + 0.1 * torch.randn(d, device="cuda")).to(dtype).requires_grad_(True)
+    b = (0.1 * torch.randn(d, device="cuda")).to(dtype).requires_grad_(True)
+    cot = torch.randn(rows, d, device="cuda")
+    probe = torch.randn(rows, d, device="cuda")
+
+    def chain(fn, x, w, b, cast):
+        y = fn(x, w, b)
+        gx, gw, gb = torch.autograd.grad((y * cot.to(cast)).sum(), (x, w, b), create_graph=True)
+        inner = (gx * probe.to(cast)).sum() + gw.pow(2).sum() + gb.pow(2).sum()
+        ggx, ggw = torch.autograd.grad(inner, (x, w))
+        return y, gx, gw, gb, ggx, ggw
+
+    for approx in ("tanh", "none"):
+        ours = lambda x, w, b: ops.gelu(ops.layer_norm(x, w, b, 1e-5), approximate=approx)  # noqa: E731
+        ref = lambda x, w, b: torch.nn.functional.gelu(  # noqa: E731
+            torch.nn.functional.layer_norm(x, (d,), w, b, 1e-5), approximate=approx)
+        with ops.composable():  # the kernels must be the path taken for graphs that are differentiated again
+            got = chain(ours, x, w, b, dtype)
+        assert "LayerNormBwdFn" in type(got[1].grad_fn).__name__ or got[1].grad_fn is not None
+        want = chain(ref, *(t.detach().double().requires_grad_(True) for t in (x, w, b)), torch.float64)
+        tol = 2e-4 if dtype == torch.float32 else 4e-2
+        for g, r in zip(got, want):
+            assert (g.double() - r).abs().max() <= tol * (r.abs().max() + 1e-6), approx
