@@ -198,6 +198,18 @@ at::Tensor gelu_fwd(at::Tensor x, bool tanh_approx) {
   return y;
 }
 
+std::vector<at::Tensor> softmax_bwd_bwd(at::Tensor c, at::Tensor dy, at::Tensor y) {
+  CHECK_CUDA_CONTIG(c); CHECK_CUDA_CONTIG(dy); CHECK_CUDA_CONTIG(y);
+  TORCH_CHECK(c.scalar_type() == y.scalar_type() && dy.scalar_type() == y.scalar_type() && c.numel() == y.numel() &&
+              dy.numel() == y.numel() && y.dim() >= 1);
+  c10::cuda::CUDAGuard guard(y.device());
+  auto d_dy = at::empty_like(y), d_y = at::empty_like(y);
+  const int64_t n = y.size(-1);
+  check(bgn_softmax_bwd_bwd(c.data_ptr(), dy.data_ptr(), y.data_ptr(), d_dy.data_ptr(), d_y.data_ptr(), y.numel() / n,
+                            (int)n, type_code(y), stream()), "softmax_bwd_bwd");
+  return {d_dy, d_y};
+}
+
 std::vector<at::Tensor> gelu_bwd_bwd(at::Tensor c, at::Tensor dy, at::Tensor x, bool tanh_approx) {
   CHECK_CUDA_CONTIG(c); CHECK_CUDA_CONTIG(dy); CHECK_CUDA_CONTIG(x);
   TORCH_CHECK(c.scalar_type() == x.scalar_type() && dy.scalar_type() == x.scalar_type() && c.numel() == x.numel() &&
@@ -690,6 +702,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gelu_fwd", &gelu_fwd);
   m.def("gelu_bwd", &gelu_bwd);
   m.def("gelu_bwd_bwd", &gelu_bwd_bwd);
+  m.def("softmax_bwd_bwd", &softmax_bwd_bwd);
   m.def("ce_fwd", &ce_fwd);
   m.def("ce_bwd", &ce_bwd);
   m.def("proj_right", &proj_right);

@@ -507,6 +507,48 @@ __global__ void gelu_bwd_bwd_kernel(const T* __restrict__ c, const T* __restrict
   }
 }
 
+// ---- softmax: backward of the backward ---------------------------------------------------
+// The softmax backward is dx = y * (dy - sum(dy y)) per row.  Given the cotangent c of dx:
+//   d_dy = y * (c - sum(c y)),   d_y = c * (dy - sum(dy y)) - dy * sum(c y).
+// One warp per row (rows are attention rows: a few hundred to a few thousand elements).
+template <typename T>
+__global__ void softmax_bwd_bwd_kernel(const T* __restrict__ c, const T* __restrict__ dy, const T* __restrict__ y,
+                                       T* __restrict__ d_dy, T* __restrict__ d_y, long rows, int n) {
+  constexpr int V = Vec<T>::N;
+  const int lane = threadIdx.x & 31;
+  const long warp = (blockIdx.x * long(blockDim.x) + threadIdx.x) >> 5;
+  const long n_warps = (long(gridDim.x) * blockDim.x) >> 5;
+  for (long r = warp; r < rows; r += n_warps) {
+    const T* cr = c + r * n;
+    const T* gr = dy + r * n;
+    const T* yr = y + r * n;
+    float s = 0.f, t = 0.f;
+    for (int i = lane * V; i < n; i += 32 * V) {
+      const Vec<T> cv = load_vec(cr + i), gv = load_vec(gr + i), yv = load_vec(yr + i);
+#pragma unroll
+      for (int k = 0; k < V; ++k) {
+        const float yf = to_float<T>(yv.v[k]);
+        s = fmaf(to_float<T>(gv.v[k]), yf, s);
+        t = fmaf(to_float<T>(cv.v[k]), yf, t);
+      }
+    }
+    s = warp_sum(s);
+    t = warp_sum(t);
+    for (int i = lane * V; i < n; i += 32 * V) {
+      const Vec<T> cv = load_vec(cr + i), gv = load_vec(gr + i), yv = load_vec(yr + i);
+      Vec<T> o1, o2;
+#pragma unroll
+      for (int k = 0; k < V; ++k) {
+        const float cf = to_float<T>(cv.v[k]), gf = to_float<T>(gv.v[k]), yf = to_float<T>(yv.v[k]);
+        o1.v[k] = from_float<T>(yf * (cf - t));
+        o2.v[k] = from_float<T>(cf * (gf - s) - gf * t);
+      }
+      store_vec(d_dy + r * n + i, o1);
+      store_vec(d_y + r * n + i, o2);
+    }
+  }
+}
+
 // ---- cross entropy --------------------------------------------------------------------
 
 template <typename T>
@@ -981,6 +1023,18 @@ extern "C" int bgn_gelu_fwd(const void* x, void* y, long n, int tanh_approx, int
   BGN_DISPATCH(type, {
     if (n % Vec<T>::N) return int(cudaErrorInvalidValue);
     gelu_fwd_kernel<T><<<grid_for(n, 256 * Vec<T>::N), 256, 0, st>>>((const T*)x, (T*)y, n, tanh_approx);
+  });
+  return int(cudaGetLastError());
+}
+
+extern "C" int bgn_softmax_bwd_bwd(const void* c, const void* dy, const void* y, void* d_dy, void* d_y, long rows, int n,
+                                   int type, cudaStream_t st) {
+  BGN_DISPATCH(type, {
+    if (n % Vec<T>::N || rows <= 0) return int(cudaErrorInvalidValue);
+    long blocks = (rows + 7) / 8;  // eight warps (rows) per block
+    if (blocks > 148L * 32) blocks = 148L * 32;
+    softmax_bwd_bwd_kernel<T><<<int(blocks), 256, 0, st>>>((const T*)c, (const T*)dy, (const T*)y, (T*)d_dy, (T*)d_y,
+                                                           rows, n);
   });
   return int(cudaGetLastError());
 }

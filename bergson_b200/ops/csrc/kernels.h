@@ -78,6 +78,10 @@ int bgn_swiglu_bwd(const void* dy, const void* gate, const void* up, void* dgate
 int bgn_gelu_fwd(const void* x, void* y, long n, int tanh_approx, int type, cudaStream_t stream);
 int bgn_gelu_bwd(const void* dy, const void* x, void* dx, long n, int tanh_approx, int type,
                  cudaStream_t stream);
+// Backward of the softmax backward (dx = y * (dy - sum(dy y)) per row of length n): given the
+// cotangent c of dx, d_dy = y * (c - sum(c y)) and d_y = c * (dy - sum(dy y)) - dy * sum(c y).
+int bgn_softmax_bwd_bwd(const void* c, const void* dy, const void* y, void* d_dy, void* d_y, long rows, int n,
+                        int type, cudaStream_t stream);
 // Backward of gelu_bwd (dx = dy * gelu'(x)): given the cotangent c of dx, d_dy = c * gelu'(x) and
 // d_x = c * dy * gelu''(x).  n must be a multiple of the 16-byte packet.
 int bgn_gelu_bwd_bwd(const void* c, const void* dy, const void* x, void* d_dy, void* d_x, long n, int tanh_approx,

@@ -298,6 +298,47 @@ def gelu(x: Tensor, approximate: str = "none") -> Tensor:
 # --------------------------------------------------------------------------- #
 
 
+class _SoftmaxBwdFn(torch.autograd.Function):
+    """``dx = y * (dy - sum(dy y))`` as a function of ``(dy, y)`` whose own backward is one kernel."""
+
+    @staticmethod
+    def forward(ctx, dy, y):
+        dy, y = dy.contiguous(), y.contiguous()
+        ctx.save_for_backward(dy, y)
+        return torch._softmax_backward_data(dy, y, -1, y.dtype)
+
+    @staticmethod
+    @torch.autograd.function.once_differentiable
+    def backward(ctx, c):
+        from . import native
+
+        dy, y = ctx.saved_tensors
+        d_dy, d_y = native.softmax_bwd_bwd(c.contiguous(), dy, y)
+        return d_dy, d_y
+
+
+class _SoftmaxFn(torch.autograd.Function):
+    """Row softmax over the last dimension, differentiable twice (the second time on a kernel)."""
+
+    @staticmethod
+    def forward(ctx, x):
+        y = torch.softmax(x, dim=-1)
+        ctx.save_for_backward(y)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        (y,) = ctx.saved_tensors
+        return _SoftmaxBwdFn.apply(dy, y)
+
+
+def _softmax_last(x: Tensor) -> Tensor:
+    if (x.dtype in (torch.bfloat16, torch.float16, torch.float32) and _kernels_ready(x)
+            and x.shape[-1] % (16 // x.element_size()) == 0):
+        return _SoftmaxFn.apply(x)
+    return torch.softmax(x, dim=-1)
+
+
 _CAUSAL_BIAS: dict = {}
 
 
@@ -329,7 +370,7 @@ def causal_attention(q: Tensor, k: Tensor, v: Tensor, scale: float | None = None
             v = v.repeat_interleave(rep, dim=1)
         bias = _causal_bias(S, q.dtype, q.device)
         att = torch.baddbmm(bias, (q * scale).reshape(B * Hq, S, D), k.reshape(B * Hq, S, D).transpose(1, 2))
-        att = torch.softmax(att, dim=-1)
+        att = _softmax_last(att)
         return torch.bmm(att, v.reshape(B * Hq, S, D)).view(B, Hq, S, D)
     return F.scaled_dot_product_attention(
         q, k, v, is_causal=True, scale=scale, enable_gqa=(Hkv != Hq)

@@ -302,3 +302,34 @@ def test_layer_norm_and_gelu_second_order_match_torch(native, dtype):
         tol = 2e-4 if dtype == torch.float32 else 4e-2
         for g, r in zip(got, want):
             assert (g.double() - r).abs().max() <= tol * (r.abs().max() + 1e-6), approx
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_attention_softmax_second_order_matches_torch(native, dtype):
+    """The explicit attention path (scores, softmax, values) differentiated twice: the softmax's
+    backward of the backward runs on the kernel; compared with torch in fp64."""
+    from bergson_b200 import ops
+
+    torch.manual_seed(0)
+    B, H, S, D = 2, 3, 64, 16
+    q, k, v = ((torch.randn(B, H, S, D, device="cuda") * 0.5).to(dtype).requires_grad_(True) for _ in range(3))
+    cot, probe = torch.randn(B, H, S, D, device="cuda"), torch.randn(B, H, S, D, device="cuda")
+
+    def chain(fn, q, k, v, cast):
+        o = fn(q, k, v)
+        gq, gk, gv = torch.autograd.grad((o * cot.to(cast)).sum(), (q, k, v), create_graph=True)
+        inner = (gq * probe.to(cast)).sum() + (gk * gk).sum() + (gv * probe.to(cast)).sum()
+        return (o, gq, gk, gv) + torch.autograd.grad(inner, (q, k, v))
+
+    def ref(q, k, v):
+        att = (q @ k.transpose(-1, -2)) / D**0.5
+        att = att.masked_fill(~torch.ones(S, S, dtype=torch.bool, device="cuda").tril(), float("-inf"))
+        return torch.softmax(att, -1) @ v
+
+    with ops.composable():
+        got = chain(ops.causal_attention, q, k, v, dtype)
+    want = chain(ref, *(t.detach().double().requires_grad_(True) for t in (q, k, v)), torch.float64)
+    tol = 1e-4 if dtype == torch.float32 else 5e-2
+    for g, r in zip(got, want):
+        assert torch.isfinite(g).all()
+        assert (g.double() - r).abs().max() <= tol * (r.abs().max() + 1e-6)
