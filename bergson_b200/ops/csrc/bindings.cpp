@@ -242,6 +242,20 @@ std::vector<at::Tensor> ce_fwd(at::Tensor logits, at::Tensor targets, int64_t ig
   return {loss, lse};
 }
 
+std::vector<at::Tensor> ce_bwd_bwd(at::Tensor c, at::Tensor logits, at::Tensor targets, at::Tensor lse, at::Tensor dloss,
+                                   int64_t ignore_index) {
+  CHECK_CUDA_CONTIG(c); CHECK_CUDA_CONTIG(logits); CHECK_CUDA_CONTIG(targets); CHECK_CUDA_CONTIG(lse); CHECK_CUDA_CONTIG(dloss);
+  TORCH_CHECK(logits.dim() == 2 && c.sizes() == logits.sizes() && c.scalar_type() == logits.scalar_type() &&
+              targets.scalar_type() == at::kLong && lse.scalar_type() == at::kFloat && dloss.scalar_type() == at::kFloat);
+  c10::cuda::CUDAGuard guard(logits.device());
+  auto d_logits = at::empty_like(logits);
+  auto d_dloss = at::empty({logits.size(0)}, logits.options().dtype(at::kFloat));
+  check(bgn_ce_bwd_bwd(c.data_ptr(), logits.data_ptr(), targets.data_ptr<int64_t>(), lse.data_ptr<float>(),
+                       dloss.data_ptr<float>(), d_logits.data_ptr(), d_dloss.data_ptr<float>(), logits.size(0),
+                       (int)logits.size(1), ignore_index, type_code(logits), stream()), "ce_bwd_bwd");
+  return {d_logits, d_dloss};
+}
+
 at::Tensor ce_bwd(at::Tensor logits, at::Tensor targets, at::Tensor lse, at::Tensor dloss, int64_t ignore_index) {
   CHECK_CUDA_CONTIG(logits); CHECK_CUDA_CONTIG(dloss);
   c10::cuda::CUDAGuard guard(logits.device());
@@ -705,6 +719,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("softmax_bwd_bwd", &softmax_bwd_bwd);
   m.def("ce_fwd", &ce_fwd);
   m.def("ce_bwd", &ce_bwd);
+  m.def("ce_bwd_bwd", &ce_bwd_bwd);
   m.def("proj_right", &proj_right);
   m.def("proj_left_outer", &proj_left_outer);
   m.def("tn_gemm", &tn_gemm);

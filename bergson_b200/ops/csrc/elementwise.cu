@@ -1066,6 +1066,66 @@ extern "C" int bgn_ce_fwd(const void* logits, const long* targets, float* loss, 
   return int(cudaGetLastError());
 }
 
+// Backward of ce_bwd (dlogits = (softmax(z) - onehot) * dloss per row).  Given the cotangent C of
+// dlogits:  with p = softmax(z) and s = sum_v C_v p_v,
+//   d_dloss = s - C_target,    d_z_v = dloss * p_v * (C_v - s);   both zero for ignored rows.
+namespace bgn {
+template <typename T>
+__global__ void ce_bwd_bwd_kernel(const T* __restrict__ C, const T* __restrict__ logits,
+                                  const long* __restrict__ targets, const float* __restrict__ lse,
+                                  const float* __restrict__ dloss, T* __restrict__ d_logits,
+                                  float* __restrict__ d_dloss, int V_, long ignore_index) {
+  __shared__ float red[32];
+  const long r = blockIdx.x;
+  const T* z = logits + r * V_;
+  const T* c = C + r * V_;
+  T* dz = d_logits + r * V_;
+  const long t = targets[r];
+  const bool ignored = t == ignore_index;
+  const float l = lse[r];
+  constexpr int V = Vec<T>::N;
+  const bool vec_ok = (V_ % V) == 0;
+  float s = 0.f;
+  if (!ignored) {
+    if (vec_ok) {
+      for (int i = threadIdx.x * V; i < V_; i += blockDim.x * V) {
+        const Vec<T> zv = load_vec(z + i), cv = load_vec(c + i);
+#pragma unroll
+        for (int k = 0; k < V; ++k) s = fmaf(to_float<T>(cv.v[k]), __expf(to_float<T>(zv.v[k]) - l), s);
+      }
+    } else {
+      for (int i = threadIdx.x; i < V_; i += blockDim.x) s = fmaf(to_float<T>(c[i]), __expf(to_float<T>(z[i]) - l), s);
+    }
+  }
+  s = block_sum(s, red);
+  const float g = ignored ? 0.f : dloss[r];
+  if (threadIdx.x == 0) d_dloss[r] = ignored ? 0.f : s - to_float<T>(c[t]);
+  if (vec_ok) {
+    for (int i = threadIdx.x * V; i < V_; i += blockDim.x * V) {
+      const Vec<T> zv = load_vec(z + i), cv = load_vec(c + i);
+      Vec<T> o;
+#pragma unroll
+      for (int k = 0; k < V; ++k)
+        o.v[k] = from_float<T>(g * __expf(to_float<T>(zv.v[k]) - l) * (to_float<T>(cv.v[k]) - s));
+      store_vec(dz + i, o);
+    }
+  } else {
+    for (int i = threadIdx.x; i < V_; i += blockDim.x)
+      dz[i] = from_float<T>(g * __expf(to_float<T>(z[i]) - l) * (to_float<T>(c[i]) - s));
+  }
+}
+}  // namespace bgn
+
+extern "C" int bgn_ce_bwd_bwd(const void* C, const void* logits, const long* targets, const float* lse,
+                              const float* dloss, void* d_logits, float* d_dloss, long T_, int V, long ignore_index,
+                              int type, cudaStream_t st) {
+  BGN_DISPATCH(type, {
+    ce_bwd_bwd_kernel<T><<<T_, 512, 0, st>>>((const T*)C, (const T*)logits, targets, lse, dloss, (T*)d_logits, d_dloss,
+                                             V, ignore_index);
+  });
+  return int(cudaGetLastError());
+}
+
 extern "C" int bgn_ce_bwd(const void* logits, const long* targets, const float* lse, const float* dloss,
                           void* dlogits, long T_, int V, long ignore_index, int type, cudaStream_t st) {
   BGN_DISPATCH(type, {

@@ -91,6 +91,9 @@ int bgn_ce_fwd(const void* logits, const long* targets, float* loss, float* lse,
                long ignore_index, int type, cudaStream_t stream);
 int bgn_ce_bwd(const void* logits, const long* targets, const float* lse, const float* dloss,
                void* dlogits, long T, int V, long ignore_index, int type, cudaStream_t stream);
+// Backward of bgn_ce_bwd: cotangent C [T, V] of dlogits -> d_logits [T, V] and d_dloss [T] (fp32).
+int bgn_ce_bwd_bwd(const void* C, const void* logits, const long* targets, const float* lse, const float* dloss,
+                   void* d_logits, float* d_dloss, long T, int V, long ignore_index, int type, cudaStream_t stream);
 // Fused AdamW on flat fp32 master state; writes the 16-bit/32-bit model copy as well.
 int bgn_adamw_step(float* p, float* m, float* v, const void* g, void* p_model, long n, float lr,
                    float b1, float b2, float eps, float eps_root, float wd, float bc1, float bc2,

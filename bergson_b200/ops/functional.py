@@ -391,10 +391,36 @@ def token_cross_entropy_ref(
     )
 
 
+class _TokenCEBwdFn(torch.autograd.Function):
+    """``dlogits = (softmax(logits) - onehot) * dloss`` as a function of ``(logits, dloss)`` with
+    its own backward kernel, so that a graph built with ``create_graph=True`` can be
+    differentiated once more (``lse`` is the forward's log-sum-exp of ``logits``; its
+    dependence on ``logits`` is part of the kernel's formula)."""
+
+    @staticmethod
+    def forward(ctx, logits, dloss, targets, lse, ignore_index):
+        from . import native
+
+        dloss = dloss.contiguous().float()
+        ctx.save_for_backward(logits, dloss, targets, lse)
+        ctx.ignore_index = ignore_index
+        return native.ce_bwd(logits, targets, lse, dloss, ignore_index)
+
+    @staticmethod
+    @torch.autograd.function.once_differentiable
+    def backward(ctx, c):
+        from . import native
+
+        logits, dloss, targets, lse = ctx.saved_tensors
+        d_logits, d_dloss = native.ce_bwd_bwd(c.contiguous(), logits, targets, lse, dloss, ctx.ignore_index)
+        return d_logits, d_dloss, None, None, None
+
+
 class _TokenCEFn(torch.autograd.Function):
     """Per-row CE over ``[T, V]`` logits: one pass computes loss and log-sum-exp;
     the backward rewrites ``(softmax - onehot) * dloss`` in one pass, in the logits'
-    own dtype, without an fp32 ``[T, V]`` intermediate."""
+    own dtype, without an fp32 ``[T, V]`` intermediate; the backward of that backward is a
+    kernel as well."""
 
     @staticmethod
     def forward(ctx, logits, targets, ignore_index):
@@ -408,11 +434,8 @@ class _TokenCEFn(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dloss):
-        from . import native
-
         logits, targets, lse = ctx.saved_tensors
-        dlogits = native.ce_bwd(logits, targets, lse, dloss.contiguous().float(), ctx.ignore_index)
-        return dlogits, None, None
+        return _TokenCEBwdFn.apply(logits, dloss, targets, lse, ctx.ignore_index), None, None
 
 
 def token_cross_entropy(
@@ -421,8 +444,9 @@ def token_cross_entropy(
     """``[T, V]`` logits, ``[T]`` targets -> ``[T]`` fp32 losses (0 where ignored)."""
     if (
         label_smoothing == 0.0
-        and use_fused(logits)
         and logits.dtype in (torch.bfloat16, torch.float16, torch.float32)
+        and _kernels_ready(logits, targets)
+        and logits.shape[0] > 0
     ):
         return _TokenCEFn.apply(logits, targets, ignore_index)
     return token_cross_entropy_ref(logits, targets, ignore_index, label_smoothing)

@@ -46,14 +46,22 @@ def weighted_causal_lm_ce(
         assert example_weight.shape in ((B,), (B, T))
 
     z = logits[:, :-1]
-    z = (z if z.dtype == torch.float64 else z.float()).reshape(-1, V)
     tgt = labels[:, 1:].reshape(-1)
+    if z.is_cuda and z.dtype in (torch.bfloat16, torch.float16, torch.float32):
+        # Per-token CE on the kernels (fp32 arithmetic on the logits' own dtype, no fp32 copy of
+        # the [tokens, vocabulary] matrix; differentiable twice).
+        from ..ops import token_cross_entropy
 
-    if example_weight is None and reduction == "mean":
-        return F.cross_entropy(z, tgt, ignore_index=ignore_index)
-
-    tok = F.cross_entropy(z, tgt, reduction="none", ignore_index=ignore_index)
-    tok = tok.view(B, T - 1)
+        tok = token_cross_entropy(z.reshape(-1, V), tgt, ignore_index=ignore_index)
+        if example_weight is None and reduction == "mean":
+            return tok.sum() / (tgt != ignore_index).sum().clamp_min(1)
+        tok = tok.view(B, T - 1)
+    else:
+        z = (z if z.dtype == torch.float64 else z.float()).reshape(-1, V)
+        if example_weight is None and reduction == "mean":
+            return F.cross_entropy(z, tgt, ignore_index=ignore_index)
+        tok = F.cross_entropy(z, tgt, reduction="none", ignore_index=ignore_index)
+        tok = tok.view(B, T - 1)
     if example_weight is None:
         w = tok.new_ones(B, 1)
     elif example_weight.ndim == 2:

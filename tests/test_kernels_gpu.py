@@ -333,3 +333,33 @@ def test_attention_softmax_second_order_matches_torch(native, dtype):
     for g, r in zip(got, want):
         assert torch.isfinite(g).all()
         assert (g.double() - r).abs().max() <= tol * (r.abs().max() + 1e-6)
+
+
+@pytest.mark.parametrize("dtype,V", [(torch.float32, 1000), (torch.bfloat16, 1003)])
+def test_token_cross_entropy_second_order_matches_torch(native, dtype, V):
+    """Per-token CE on the kernels, differentiated twice (odd vocabulary sizes take the scalar
+    loops), with ignored rows, against torch in fp64."""
+    from bergson_b200 import ops
+
+    torch.manual_seed(0)
+    T = 37
+    z = (torch.randn(T, V, device="cuda") * 2).to(dtype).requires_grad_(True)
+    w = torch.rand(T, device="cuda").requires_grad_(True)
+    tgt = torch.randint(0, V, (T,), device="cuda")
+    tgt[::5] = -100
+    probe = torch.randn(T, V, device="cuda")
+
+    def chain(ce, z, w, cast):
+        loss = (ce(z) * w.to(cast)).sum()
+        (gz,) = torch.autograd.grad(loss, z, create_graph=True)
+        ggz, ggw = torch.autograd.grad((gz * probe.to(cast)).sum(), (z, w))
+        return loss, gz, ggz, ggw
+
+    with ops.composable():
+        got = chain(lambda z: ops.token_cross_entropy(z, tgt), z, w, torch.float32)
+    z64, w64 = z.detach().double().requires_grad_(True), w.detach().double().requires_grad_(True)
+    want = chain(lambda z: torch.nn.functional.cross_entropy(z, tgt, reduction="none", ignore_index=-100), z64, w64,
+                 torch.float64)
+    tol = 1e-4 if dtype == torch.float32 else 3e-2
+    for g, r in zip(got, want):
+        assert (g.double() - r).abs().max() <= tol * (r.abs().max() + 1e-6)
