@@ -137,14 +137,17 @@ class _LayerNormFn(torch.autograd.Function):
 
         x2 = x.reshape(-1, x.shape[-1]).contiguous()
         y, mean, rstd = native.layernorm_fwd(x2, weight, bias, eps)
-        ctx.save_for_backward(x2, weight, mean, rstd)
+        # The input itself is saved (not the reshaped copy): only a saved *input* keeps its place
+        # in the graph, which the backward of the backward needs to reach x.
+        ctx.save_for_backward(x, weight, mean, rstd)
         ctx.shape = x.shape
         ctx.has_bias = bias is not None
         return y.view(x.shape)
 
     @staticmethod
     def backward(ctx, dy):
-        x2, weight, mean, rstd = ctx.saved_tensors
+        x, weight, mean, rstd = ctx.saved_tensors
+        x2 = x.reshape(-1, x.shape[-1]).contiguous()
         dy2 = dy.reshape(-1, dy.shape[-1])
         need_w = ctx.needs_input_grad[1] or (ctx.has_bias and ctx.needs_input_grad[2])
         if not need_w and not torch.is_grad_enabled():
@@ -273,10 +276,9 @@ class _GELUFn(torch.autograd.Function):
     def forward(ctx, x, tanh_approx):
         from . import native
 
-        x = x.contiguous()
-        ctx.save_for_backward(x)
+        ctx.save_for_backward(x)  # the input itself, so that it keeps its place in the graph
         ctx.tanh_approx = tanh_approx
-        return native.gelu_fwd(x, tanh_approx)
+        return native.gelu_fwd(x.contiguous(), tanh_approx)
 
     @staticmethod
     def backward(ctx, dy):
@@ -426,16 +428,15 @@ class _TokenCEFn(torch.autograd.Function):
     def forward(ctx, logits, targets, ignore_index):
         from . import native
 
-        logits = logits.contiguous()
-        loss, lse = native.ce_fwd(logits, targets, ignore_index)
-        ctx.save_for_backward(logits, targets, lse)
+        loss, lse = native.ce_fwd(logits.contiguous(), targets, ignore_index)
+        ctx.save_for_backward(logits, targets, lse)  # the input itself: it keeps its place in the graph
         ctx.ignore_index = ignore_index
         return loss
 
     @staticmethod
     def backward(ctx, dloss):
         logits, targets, lse = ctx.saved_tensors
-        return _TokenCEBwdFn.apply(logits, dloss, targets, lse, ctx.ignore_index), None, None
+        return _TokenCEBwdFn.apply(logits.contiguous(), dloss, targets, lse, ctx.ignore_index), None, None
 
 
 def token_cross_entropy(

@@ -101,18 +101,18 @@ class _GemmFn(torch.autograd.Function):
     def forward(ctx, a: Tensor, b: Tensor, a_mn: bool, b_mn: bool, bias: Tensor | None):
         from . import native
 
-        a, b = _as_operand(a), _as_operand(b)
+        # The inputs themselves are saved: only a saved input keeps its place in the graph, which
+        # the backward of the backward needs; copies for alignment are made again (tracked) there.
         ctx.save_for_backward(a, b)
         ctx.layout = (a_mn, b_mn)
         ctx.has_bias = bias is not None
-        d, _ = native.gemm(a, b, a_mn, b_mn, None, False, bias, False, None, **_gemm_form())
+        d, _ = native.gemm(_as_operand(a), _as_operand(b), a_mn, b_mn, None, False, bias, False, None, **_gemm_form())
         return d
 
     @staticmethod
     def backward(ctx, g: Tensor):
         a, b = ctx.saved_tensors
         a_mn, b_mn = ctx.layout
-        g = _as_operand(g)
         da = db = dbias = None
         if ctx.needs_input_grad[0]:
             # [M, K] = g B, or in A's transposed storage [K, M] = B^T g^T.

@@ -178,3 +178,45 @@ def test_newton_schulz_on_the_gemm_kernel_matches_torch(native, shape):
     (gg,) = torch.autograd.grad((out.float() * probe).sum(), g)
     (gr,) = torch.autograd.grad((ref * probe.double()).sum(), g64)
     assert torch.nn.functional.cosine_similarity(gg.double().flatten(), gr.flatten(), dim=0) > 0.98
+
+
+@pytest.mark.parametrize("family", ["gpt2", "llama"])
+def test_meta_step_on_kernels_matches_cpu_fp64(native, family):
+    """One traced step plus its VJP (the metagradient building block) on the GPU in fp32, where
+    GEMMs, LayerNorm, GELU, softmax, cross-entropy and AdamW run on kernels to second order,
+    against the same computation on the CPU in fp64."""
+    from bergson_b200.magic import optim
+    from bergson_b200.magic.data_stream import DataStream
+    from bergson_b200.magic.trainer import Trainer
+
+    from .helpers import tiny_dataset, tiny_model
+
+    def run(device, dtype):
+        torch.manual_seed(0)
+        model = tiny_model(family, dtype=dtype, num_hidden_layers=2, hidden_size=64, intermediate_size=128,
+                           num_attention_heads=4, vocab_size=128).to(device)
+        model.requires_grad_(True)
+        model.eval()
+        opt = optim.adamw(lambda i: 1e-2, betas=(0.9, 0.95), eps_root=1e-8, weight_decay=0.01)
+        trainer, state = Trainer.initialize(model, opt)
+        data = DataStream(tiny_dataset(n=8, length=16, ragged=False), 4, device=device)
+        data.weights.data = data.weights.data.to(dtype)
+        state = trainer.step(state, data[0], inplace=False)  # non-trivial moments
+        state.detach_()
+        state.requires_grad = True
+        data.requires_grad = True
+        before = state.differentiable_tensors()
+        after = trainer.step(state, data[1], trace=True).differentiable_tensors()
+        gen = torch.Generator().manual_seed(1)
+        cot = [torch.randn(t.shape, generator=gen).to(device, t.dtype) * 1e-2 for t in after]
+        grads = torch.autograd.grad(after, before + [data.weights], grad_outputs=cot, allow_unused=True)
+        return [None if g is None else g.detach().double().cpu() for g in grads]
+
+    got = run("cuda", torch.float32)
+    want = run("cpu", torch.float64)
+    assert len(got) == len(want)
+    for g, w in zip(got, want):
+        assert (g is None) == (w is None)
+        if w is not None and w.abs().max() > 0:
+            assert (g - w).abs().max() <= 2e-3 * w.abs().max() + 1e-9
+    assert want[-1].abs().max() > 0  # the data-weight gradient is not trivially zero
