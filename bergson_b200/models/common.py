@@ -140,11 +140,25 @@ class NativeCausalLM(nn.Module):
 
     def forward(self, input_ids: Tensor, labels: Tensor | None = None, **kwargs) -> CausalLMOutput:
         h = self.hidden(input_ids)
-        logits = self.get_output_embeddings()(h)
+        head = self.get_output_embeddings()
+        V = self.config.vocab_size
+        ours = getattr(self.loss_function, "func", self.loss_function) is weighted_causal_lm_ce
+        if (labels is not None and V % 8 and ours and getattr(head, "bias", None) is None
+                and not head._forward_hooks):
+            # A vocabulary that is not a multiple of 8 is padded for the head's GEMM; the loss
+            # runs on the padded width (the extra columns cannot win any probability) and the
+            # logits handed back are the view without them.
+            from ..ops.linear import linear_keep_padding
+
+            padded = linear_keep_padding(h, head.weight)
+            if padded is not None:
+                loss = self.loss_function(padded, labels, vocab_size=V, padded_vocab=True, **kwargs)
+                return CausalLMOutput(logits=padded[..., :V], loss=loss)
+        logits = head(h)
         loss = None
         if labels is not None:
             loss = self.loss_function(
-                logits, labels, vocab_size=self.config.vocab_size, **kwargs
+                logits, labels, vocab_size=V, **kwargs
             )
         return CausalLMOutput(logits=logits, loss=loss)
 

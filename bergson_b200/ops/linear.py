@@ -125,8 +125,13 @@ class _GemmFn(torch.autograd.Function):
         return da, db, None, None, dbias
 
 
-def _composable_linear(x: Tensor, weight: Tensor, bias: Tensor | None, layout: str) -> Tensor | None:
-    """The any-order-differentiable product on the kernel, or None when the shapes do not fit."""
+PAD_LOGIT = -30000.0  # what padded output columns hold when the caller keeps them (exp underflows to 0)
+
+
+def _composable_linear(x: Tensor, weight: Tensor, bias: Tensor | None, layout: str, keep_pad: bool = False) -> Tensor | None:
+    """The any-order-differentiable product on the kernel, or None when the shapes do not fit.
+    With ``keep_pad`` the padded columns stay in the result, filled with ``PAD_LOGIT`` through
+    the GEMM's bias epilogue (for a softmax / cross-entropy that runs on the padded width)."""
     oi = layout == "oi"
     in_f = weight.shape[1] if oi else weight.shape[0]
     out_f = weight.shape[0] if oi else weight.shape[1]
@@ -139,9 +144,22 @@ def _composable_linear(x: Tensor, weight: Tensor, bias: Tensor | None, layout: s
         return None
     w = F.pad(weight, (0, 0, 0, pad)) if pad else weight
     bb = F.pad(bias, (0, pad)) if (pad and bias is not None) else bias
+    if pad and keep_pad:
+        fill = x.new_zeros(out_f + pad)
+        fill[out_f:] = PAD_LOGIT
+        bb = fill if bb is None else bb + fill
     y = _GemmFn.apply(x.reshape(-1, in_f), w, False, not oi, bb)
     y = y.view(*x.shape[:-1], out_f + pad)
-    return y[..., :out_f] if pad else y
+    return y[..., :out_f] if (pad and not keep_pad) else y
+
+
+def linear_keep_padding(x: Tensor, weight: Tensor) -> Tensor | None:
+    """``x @ weight^T`` on the kernel with the output width rounded up to a multiple of 8 and the
+    extra columns set to ``PAD_LOGIT`` (contiguous result), or None when the kernel path does
+    not apply.  For heads whose vocabulary size is not a multiple of 8."""
+    if not _kernel_ready(x, weight) or weight.dim() != 2:
+        return None
+    return _composable_linear(x, weight, None, "oi", keep_pad=True)
 
 
 def _aux_fits(rows: int, cols: int, device) -> bool:

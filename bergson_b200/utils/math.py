@@ -26,6 +26,7 @@ def weighted_causal_lm_ce(
     shift_loss_mask: Tensor | None = None,
     vocab_size: int | None = None,
     reduction: str = "mean",
+    padded_vocab: bool = False,
     **_ignored,
 ) -> Tensor:
     """Next-token cross entropy with per-example ``[B]`` or per-token ``[B, T]``
@@ -40,8 +41,11 @@ def weighted_causal_lm_ce(
     assert logits.ndim == 3 and labels.ndim == 2
     B, T, V = logits.shape
     assert labels.shape == (B, T)
-    if vocab_size is not None:
+    if vocab_size is not None and not padded_vocab:
         assert V == vocab_size, f"Expected vocab size {vocab_size}, got {V}"
+    if padded_vocab:
+        # Columns from vocab_size on hold a large negative constant: they vanish from the softmax.
+        assert vocab_size is not None and vocab_size <= V < vocab_size + 8, (vocab_size, V)
     if example_weight is not None:
         assert example_weight.shape in ((B,), (B, T))
 
@@ -52,10 +56,15 @@ def weighted_causal_lm_ce(
         # the [tokens, vocabulary] matrix; differentiable twice).
         from ..ops import token_cross_entropy
 
-        tok = token_cross_entropy(z.reshape(-1, V), tgt, ignore_index=ignore_index)
+        if logits.is_contiguous():
+            # All T positions with the targets shifted and the last one ignored: the [B, T, V]
+            # logits are read in place instead of copying the [:, :-1] slice.
+            shifted = torch.cat([labels[:, 1:], labels.new_full((B, 1), ignore_index)], dim=1).reshape(-1)
+            tok = token_cross_entropy(logits.view(-1, V), shifted, ignore_index=ignore_index).view(B, T)[:, :-1]
+        else:
+            tok = token_cross_entropy(z.reshape(-1, V), tgt, ignore_index=ignore_index).view(B, T - 1)
         if example_weight is None and reduction == "mean":
             return tok.sum() / (tgt != ignore_index).sum().clamp_min(1)
-        tok = tok.view(B, T - 1)
     else:
         z = (z if z.dtype == torch.float64 else z.float()).reshape(-1, V)
         if example_weight is None and reduction == "mean":

@@ -220,3 +220,27 @@ def test_meta_step_on_kernels_matches_cpu_fp64(native, family):
         if w is not None and w.abs().max() > 0:
             assert (g - w).abs().max() <= 2e-3 * w.abs().max() + 1e-9
     assert want[-1].abs().max() > 0  # the data-weight gradient is not trivially zero
+
+
+def test_padded_vocabulary_head_loss_matches_plain_path(native):
+    """A vocabulary that is not a multiple of 8: the head's GEMM and the loss run on the padded
+    width; loss, logits and gradients must equal the unpadded torch computation."""
+    from .helpers import tiny_model
+
+    torch.manual_seed(0)
+    model = tiny_model("gpt2", dtype=torch.bfloat16, num_hidden_layers=1, vocab_size=131).to("cuda")
+    model.eval()
+    x = torch.randint(0, 131, (3, 24), device="cuda")
+    w = torch.rand(3, device="cuda")
+    out = model(input_ids=x, labels=x, example_weight=w)
+    assert out.logits.shape == (3, 24, 131) and out.logits.stride(-2) == 136  # view of the padded rows
+    h = model.hidden(x)
+    logits = (h.float() @ model.get_output_embeddings().weight.float().T)
+    tok = torch.nn.functional.cross_entropy(logits[:, :-1].reshape(-1, 131), x[:, 1:].reshape(-1), reduction="none")
+    want = (tok.view(3, 23) * w[:, None]).sum() / (3 * 23)
+    torch.testing.assert_close(out.loss.float(), want, rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(out.logits.float(), logits, rtol=5e-2, atol=5e-2)
+    (g,) = torch.autograd.grad(out.loss, model.get_output_embeddings().weight)
+    (g_ref,) = torch.autograd.grad(want, model.get_output_embeddings().weight)
+    assert g.shape == g_ref.shape
+    assert torch.nn.functional.cosine_similarity(g.float().flatten(), g_ref.float().flatten(), dim=0) > 0.99
