@@ -47,7 +47,13 @@ def score_rows(rows: Tensor, queries: Tensor, dtype: torch.dtype, need_sq: bool)
     queries = queries.to(dtype)
     if use_fused(rows, queries) and dtype in _TC_DTYPES and rows.shape[1] % 8 == 0:
         rows = rows.contiguous()
-        scores = native.tn_gemm(rows, queries.contiguous())
+        queries = queries.contiguous()
+        if rows.shape[0] >= 512 and queries.shape[0] % 4 == 0:
+            # Many rows on both sides (a query batch against a store chunk): the wide CTA-pair GEMM
+            # with fp32 output; the 128-row kernel below serves the small per-batch products.
+            scores, _ = native.gemm(rows, queries, False, False, None, True, None, False, None, cta_group=2, wide=True)
+        else:
+            scores = native.tn_gemm(rows, queries)
         sq = None
         if need_sq:
             sq = torch.zeros(rows.shape[0], device=rows.device, dtype=torch.float32)
