@@ -141,6 +141,37 @@ std::vector<at::Tensor> layernorm_bwd(at::Tensor dy, at::Tensor x, at::Tensor w,
   return {dx, dw, db};
 }
 
+// Backward of rmsnorm_bwd: (cotangent of dx, of dw) -> (d_dy, d_x, d_w).
+std::vector<at::Tensor> rmsnorm_bwd_bwd(at::Tensor cu, at::Tensor cw, at::Tensor dy, at::Tensor x, at::Tensor w,
+                                        at::Tensor rstd) {
+  CHECK_CUDA_CONTIG(cu); CHECK_CUDA_CONTIG(dy); CHECK_CUDA_CONTIG(x);
+  TORCH_CHECK(cu.scalar_type() == x.scalar_type() && dy.scalar_type() == x.scalar_type() && cu.numel() == x.numel() &&
+              dy.numel() == x.numel() && x.dim() == 2);
+  c10::cuda::CUDAGuard guard(x.device());
+  auto wc = w.to(x.scalar_type()).contiguous();
+  auto vw = cw.to(at::kFloat).contiguous();
+  TORCH_CHECK(vw.numel() == x.size(1));
+  auto d_dy = at::empty_like(x), d_x = at::empty_like(x);
+  const int n_partial = (int)std::min<int64_t>(x.size(0), 148 * 2);
+  auto pw = at::empty({n_partial, x.size(1)}, x.options().dtype(at::kFloat));
+  check(bgn_rmsnorm_bwd_bwd(cu.data_ptr(), vw.data_ptr<float>(), dy.data_ptr(), x.data_ptr(), wc.data_ptr(),
+                            rstd.data_ptr<float>(), d_dy.data_ptr(), d_x.data_ptr(), pw.data_ptr<float>(), n_partial,
+                            x.size(0), (int)x.size(1), type_code(x), stream()), "rmsnorm_bwd_bwd");
+  return {d_dy, d_x, pw.sum(0).to(w.scalar_type())};
+}
+
+std::vector<at::Tensor> swiglu_bwd_bwd(at::Tensor cg, at::Tensor cu, at::Tensor dy, at::Tensor g, at::Tensor u) {
+  CHECK_CUDA_CONTIG(cg); CHECK_CUDA_CONTIG(cu); CHECK_CUDA_CONTIG(dy); CHECK_CUDA_CONTIG(g); CHECK_CUDA_CONTIG(u);
+  TORCH_CHECK(cg.numel() == g.numel() && cu.numel() == g.numel() && dy.numel() == g.numel() && u.numel() == g.numel() &&
+              cg.scalar_type() == g.scalar_type() && cu.scalar_type() == g.scalar_type() &&
+              dy.scalar_type() == g.scalar_type() && u.scalar_type() == g.scalar_type());
+  c10::cuda::CUDAGuard guard(g.device());
+  auto d_dy = at::empty_like(g), d_g = at::empty_like(g), d_u = at::empty_like(g);
+  check(bgn_swiglu_bwd_bwd(cg.data_ptr(), cu.data_ptr(), dy.data_ptr(), g.data_ptr(), u.data_ptr(), d_dy.data_ptr(),
+                           d_g.data_ptr(), d_u.data_ptr(), g.numel(), type_code(g), stream()), "swiglu_bwd_bwd");
+  return {d_dy, d_g, d_u};
+}
+
 // Backward of layernorm_bwd: (cotangent of dx, of dw, of db) -> (d_dy, d_x, d_w).
 std::vector<at::Tensor> layernorm_bwd_bwd(at::Tensor cu, at::Tensor cw, at::Tensor cb, at::Tensor dy, at::Tensor x,
                                           at::Tensor w, at::Tensor mean, at::Tensor rstd) {
@@ -710,6 +741,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("layernorm_fwd", &layernorm_fwd);
   m.def("layernorm_bwd", &layernorm_bwd);
   m.def("layernorm_bwd_bwd", &layernorm_bwd_bwd);
+  m.def("rmsnorm_bwd_bwd", &rmsnorm_bwd_bwd);
+  m.def("swiglu_bwd_bwd", &swiglu_bwd_bwd);
   m.def("rotary", &rotary);
   m.def("swiglu_fwd", &swiglu_fwd);
   m.def("swiglu_bwd", &swiglu_bwd);

@@ -130,6 +130,75 @@ __global__ void rmsnorm_bwd_kernel(const T* __restrict__ dy, const T* __restrict
   }
 }
 
+// Backward of rmsnorm_bwd.  With g = dy * w, xh = x * rstd, the first backward is
+//   dx = rstd * (g - xh * mean(g xh)),   dw = sum_rows dy xh.
+// Given cotangents U (of dx) and Vw (of dw, [d] fp32):
+//   d_dy = w * rstd * P(U) + Vw * xh,   d_w = sum_rows dy * rstd * P(U),
+//   d_x  = -rstd^2 * (xh * (mean(g U) - mean(g xh) mean(U xh)) + mean(U xh) * P(g) + mean(g xh) * P(U))
+//          + rstd * P(Vw * dy),         with P(z) = z - xh * mean(z xh).
+template <typename T>
+__global__ void rmsnorm_bwd_bwd_kernel(const T* __restrict__ U, const float* __restrict__ Vw,
+                                       const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ w,
+                                       const float* __restrict__ rstd, T* __restrict__ d_dy, T* __restrict__ d_x,
+                                       float* __restrict__ dw_partial, long rows, int d) {
+  __shared__ float red[32];
+  constexpr int V = Vec<T>::N;
+  constexpr int kMaxPer = 4;
+  float dw_acc[kMaxPer][V];
+#pragma unroll
+  for (int a = 0; a < kMaxPer; ++a)
+#pragma unroll
+    for (int k = 0; k < V; ++k) dw_acc[a][k] = 0.f;
+  for (long r = blockIdx.x; r < rows; r += gridDim.x) {
+    const T* xr = x + r * d;
+    const T* gr = dy + r * d;
+    const T* ur = U + r * d;
+    const float rs = rstd[r];
+    float sgx = 0.f, sux = 0.f, sgu = 0.f, sqx = 0.f;
+    for (int i = threadIdx.x * V; i < d; i += blockDim.x * V) {
+      Vec<T> xv = load_vec(xr + i), gv = load_vec(gr + i), uv = load_vec(ur + i), wv = load_vec(w + i);
+#pragma unroll
+      for (int k = 0; k < V; ++k) {
+        const float xh = to_float<T>(xv.v[k]) * rs;
+        const float gy = to_float<T>(gv.v[k]);
+        const float g = gy * to_float<T>(wv.v[k]);
+        const float u = to_float<T>(uv.v[k]);
+        sgx = fmaf(g, xh, sgx);
+        sux = fmaf(u, xh, sux);
+        sgu = fmaf(g, u, sgu);
+        sqx = fmaf(Vw[i + k] * gy, xh, sqx);
+      }
+    }
+    const float inv_d = 1.f / d;
+    const float b = block_sum(sgx, red) * inv_d, c = block_sum(sux, red) * inv_d;
+    const float mgu = block_sum(sgu, red) * inv_d, mqx = block_sum(sqx, red) * inv_d;
+    const float e = mgu - b * c;
+    int slot = 0;
+    for (int i = threadIdx.x * V; i < d; i += blockDim.x * V, ++slot) {
+      Vec<T> xv = load_vec(xr + i), gv = load_vec(gr + i), uv = load_vec(ur + i), wv = load_vec(w + i), o1, o2;
+#pragma unroll
+      for (int k = 0; k < V; ++k) {
+        const float xh = to_float<T>(xv.v[k]) * rs;
+        const float gy = to_float<T>(gv.v[k]);
+        const float wk = to_float<T>(wv.v[k]);
+        const float g = gy * wk;
+        const float vw = Vw[i + k];
+        const float pu = to_float<T>(uv.v[k]) - xh * c;
+        const float pg = g - xh * b;
+        o1.v[k] = from_float<T>(wk * rs * pu + vw * xh);
+        o2.v[k] = from_float<T>(-rs * rs * (xh * e + c * pg + b * pu) + rs * (vw * gy - xh * mqx));
+        if (slot < kMaxPer) dw_acc[slot][k] = fmaf(gy, rs * pu, dw_acc[slot][k]);
+      }
+      store_vec(d_dy + r * d + i, o1);
+      store_vec(d_x + r * d + i, o2);
+    }
+  }
+  int slot = 0;
+  for (int i = threadIdx.x * V; i < d && slot < kMaxPer; i += blockDim.x * V, ++slot)
+#pragma unroll
+    for (int k = 0; k < V; ++k) dw_partial[long(blockIdx.x) * d + i + k] = dw_acc[slot][k];
+}
+
 // ---- LayerNorm ------------------------------------------------------------------------
 
 template <typename T>
@@ -427,6 +496,35 @@ __global__ void swiglu_bwd_kernel(const T* __restrict__ dy, const T* __restrict_
     }
     store_vec(dg + i, og);
     store_vec(du + i, ou);
+  }
+}
+
+// Backward of swiglu_bwd (dg = dy * u * silu'(g), du = dy * silu(g)).  Given cotangents cg (of dg)
+// and cu (of du):  d_dy = cg * u * silu'(g) + cu * silu(g),
+//                  d_g  = cg * dy * u * silu''(g) + cu * dy * silu'(g),   d_u = cg * dy * silu'(g).
+template <typename T>
+__global__ void swiglu_bwd_bwd_kernel(const T* __restrict__ cg, const T* __restrict__ cu, const T* __restrict__ dy,
+                                      const T* __restrict__ g, const T* __restrict__ u, T* __restrict__ d_dy,
+                                      T* __restrict__ d_g, T* __restrict__ d_u, long n) {
+  constexpr int V = Vec<T>::N;
+  for (long i = (blockIdx.x * long(blockDim.x) + threadIdx.x) * V; i < n;
+       i += long(gridDim.x) * blockDim.x * V) {
+    Vec<T> av = load_vec(cg + i), bv = load_vec(cu + i), yv = load_vec(dy + i), gv = load_vec(g + i), uv = load_vec(u + i);
+    Vec<T> o1, o2, o3;
+#pragma unroll
+    for (int k = 0; k < V; ++k) {
+      const float a = to_float<T>(gv.v[k]), b = to_float<T>(uv.v[k]), d = to_float<T>(yv.v[k]);
+      const float ca = to_float<T>(av.v[k]), cb = to_float<T>(bv.v[k]);
+      const float sg = sigmoidf_(a);
+      const float s1 = sg * (1.f + a * (1.f - sg));
+      const float s2 = sg * (1.f - sg) * (2.f + a * (1.f - 2.f * sg));
+      o1.v[k] = from_float<T>(ca * b * s1 + cb * a * sg);
+      o2.v[k] = from_float<T>(ca * d * b * s2 + cb * d * s1);
+      o3.v[k] = from_float<T>(ca * d * s1);
+    }
+    store_vec(d_dy + i, o1);
+    store_vec(d_g + i, o2);
+    store_vec(d_u + i, o3);
   }
 }
 
@@ -946,6 +1044,29 @@ extern "C" int bgn_rmsnorm_bwd(const void* dy, const void* x, const void* w, con
     if (d % Vec<T>::N || (dw_partial && d > threads * Vec<T>::N * 4)) return int(cudaErrorInvalidValue);
     const int grid = dw_partial ? n_partial : int(rows < 148L * 8 ? rows : 148L * 8);
     rmsnorm_bwd_kernel<T><<<grid, threads, 0, st>>>((const T*)dy, (const T*)x, (const T*)w, rstd, (T*)dx, dw_partial, rows, d);
+  });
+  return int(cudaGetLastError());
+}
+
+extern "C" int bgn_rmsnorm_bwd_bwd(const void* U, const float* Vw, const void* dy, const void* x, const void* w,
+                                   const float* rstd, void* d_dy, void* d_x, float* dw_partial, int n_partial,
+                                   long rows, int d, int type, cudaStream_t st) {
+  BGN_DISPATCH(type, {
+    const int threads = vec_threads(d, Vec<T>::N);
+    if (d % Vec<T>::N || d > threads * Vec<T>::N * 4 || n_partial < 1) return int(cudaErrorInvalidValue);
+    rmsnorm_bwd_bwd_kernel<T><<<n_partial, threads, 0, st>>>((const T*)U, Vw, (const T*)dy, (const T*)x, (const T*)w, rstd,
+                                                            (T*)d_dy, (T*)d_x, dw_partial, rows, d);
+  });
+  return int(cudaGetLastError());
+}
+
+extern "C" int bgn_swiglu_bwd_bwd(const void* cg, const void* cu, const void* dy, const void* g, const void* u, void* d_dy,
+                                  void* d_g, void* d_u, long n, int type, cudaStream_t st) {
+  BGN_DISPATCH(type, {
+    if (n % Vec<T>::N) return int(cudaErrorInvalidValue);
+    swiglu_bwd_bwd_kernel<T><<<grid_for(n, 256 * Vec<T>::N), 256, 0, st>>>((const T*)cg, (const T*)cu, (const T*)dy,
+                                                                           (const T*)g, (const T*)u, (T*)d_dy, (T*)d_g,
+                                                                           (T*)d_u, n);
   });
   return int(cudaGetLastError());
 }

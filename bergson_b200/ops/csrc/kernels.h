@@ -63,6 +63,14 @@ int bgn_layernorm_fwd(const void* x, const void* w, const void* b, void* y, floa
 int bgn_layernorm_bwd(const void* dy, const void* x, const void* w, const float* mean,
                       const float* rstd, void* dx, float* dw_partial, float* db_partial,
                       int n_partial, long rows, int d, int type, cudaStream_t stream);
+// Backward of bgn_rmsnorm_bwd: cotangents U (of dx, [rows, d]) and Vw (of dw, [d] fp32) -> d_dy, d_x and
+// per-block partial sums of d_w ([n_partial, d] fp32, n_partial = number of blocks launched).
+int bgn_rmsnorm_bwd_bwd(const void* U, const float* Vw, const void* dy, const void* x, const void* w,
+                        const float* rstd, void* d_dy, void* d_x, float* dw_partial, int n_partial, long rows, int d,
+                        int type, cudaStream_t stream);
+// Backward of bgn_swiglu_bwd: cotangents cg, cu (of dgate, dup) -> d_dy, d_gate, d_up.
+int bgn_swiglu_bwd_bwd(const void* cg, const void* cu, const void* dy, const void* gate, const void* up, void* d_dy,
+                       void* d_gate, void* d_up, long n, int type, cudaStream_t stream);
 // Backward of bgn_layernorm_bwd: cotangents U (of dx, [rows, d], element type), Vw and Sb (of dw and
 // db, [d] fp32) -> d_dy, d_x ([rows, d]) and per-block partial sums of d_w ([n_partial, d] fp32,
 // n_partial = number of blocks launched; d at most 4 packets per thread).

@@ -71,6 +71,31 @@ def rms_norm_ref(x: Tensor, weight: Tensor, eps: float) -> Tensor:
     return (y.to(x.dtype)) * weight
 
 
+class _RMSNormBwdFn(torch.autograd.Function):
+    """``(dy, x, w) -> (dx, dw)`` of RMSNorm with its own backward kernel (the backward of the
+    backward); ``rstd`` is the forward's row statistic of ``x``."""
+
+    @staticmethod
+    def forward(ctx, dy2, x2, weight, rstd):
+        from . import native
+
+        dy2 = dy2.contiguous()
+        dx, dw = native.rmsnorm_bwd(dy2, x2, weight, rstd, True)
+        ctx.save_for_backward(dy2, x2, weight, rstd)
+        return dx, dw
+
+    @staticmethod
+    @torch.autograd.function.once_differentiable
+    def backward(ctx, cu, cw):
+        from . import native
+
+        dy2, x2, weight, rstd = ctx.saved_tensors
+        cu = torch.zeros_like(x2) if cu is None else cu.contiguous()
+        cw = torch.zeros_like(weight) if cw is None else cw
+        d_dy, d_x, d_w = native.rmsnorm_bwd_bwd(cu, cw, dy2, x2, weight, rstd)
+        return d_dy, d_x, d_w, None
+
+
 class _RMSNormFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, weight, eps):
@@ -78,22 +103,29 @@ class _RMSNormFn(torch.autograd.Function):
 
         x2 = x.reshape(-1, x.shape[-1]).contiguous()
         y, rstd = native.rmsnorm_fwd(x2, weight, eps)
-        ctx.save_for_backward(x2, weight, rstd)
+        ctx.save_for_backward(x, weight, rstd)  # the input itself: it keeps its place in the graph
         ctx.shape = x.shape
         return y.view(x.shape)
 
     @staticmethod
     def backward(ctx, dy):
-        from . import native
+        x, weight, rstd = ctx.saved_tensors
+        x2 = x.reshape(-1, x.shape[-1]).contiguous()
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        if not ctx.needs_input_grad[1] and not torch.is_grad_enabled():
+            from . import native
 
-        x2, weight, rstd = ctx.saved_tensors
-        dy2 = dy.reshape(-1, dy.shape[-1]).contiguous()
-        dx, dw = native.rmsnorm_bwd(dy2, x2, weight, rstd, ctx.needs_input_grad[1])
+            dx, _ = native.rmsnorm_bwd(dy2.contiguous(), x2, weight, rstd, False)
+            return dx.view(ctx.shape), None, None
+        dx, dw = _RMSNormBwdFn.apply(dy2, x2, weight, rstd)
         return dx.view(ctx.shape), dw, None
 
 
 def rms_norm(x: Tensor, weight: Tensor, eps: float) -> Tensor:
-    if use_fused(x, weight) and x.dtype in (torch.bfloat16, torch.float16, torch.float32):
+    """RMSNorm on the kernels: forward, backward and the backward of the backward."""
+    d, packet = x.shape[-1], 16 // max(x.element_size(), 1)
+    if (x.is_cuda and x.dtype in (torch.bfloat16, torch.float16, torch.float32) and _kernels_ready(x, weight)
+            and d % packet == 0 and d <= 2048 * packet):
         return _RMSNormFn.apply(x, weight, eps)
     return rms_norm_ref(x, weight, eps)
 
@@ -221,25 +253,49 @@ def swiglu_ref(gate: Tensor, up: Tensor) -> Tensor:
     return F.silu(gate) * up
 
 
+class _SwiGLUBwdFn(torch.autograd.Function):
+    """``(dy, gate, up) -> (dgate, dup)`` with its own backward kernel."""
+
+    @staticmethod
+    def forward(ctx, dy, gate, up):
+        from . import native
+
+        dy, gate, up = dy.contiguous(), gate.contiguous(), up.contiguous()
+        ctx.save_for_backward(dy, gate, up)
+        dg, du = native.swiglu_bwd(dy, gate, up)
+        return dg, du
+
+    @staticmethod
+    @torch.autograd.function.once_differentiable
+    def backward(ctx, cg, cu):
+        from . import native
+
+        dy, gate, up = ctx.saved_tensors
+        cg = torch.zeros_like(gate) if cg is None else cg.contiguous()
+        cu = torch.zeros_like(gate) if cu is None else cu.contiguous()
+        d_dy, d_g, d_u = native.swiglu_bwd_bwd(cg, cu, dy, gate, up)
+        return d_dy, d_g, d_u
+
+
 class _SwiGLUFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, gate, up):
         from . import native
 
-        ctx.save_for_backward(gate, up)
+        ctx.save_for_backward(gate, up)  # the inputs themselves: they keep their place in the graph
         return native.swiglu_fwd(gate.contiguous(), up.contiguous())
 
     @staticmethod
     def backward(ctx, dy):
-        from . import native
-
         gate, up = ctx.saved_tensors
-        dg, du = native.swiglu_bwd(dy.contiguous(), gate.contiguous(), up.contiguous())
-        return dg, du
+        return _SwiGLUBwdFn.apply(dy, gate, up)
 
 
 def swiglu(gate: Tensor, up: Tensor) -> Tensor:
-    if use_fused(gate, up) and gate.dtype in (torch.bfloat16, torch.float16, torch.float32):
+    """``silu(gate) * up`` on the kernels: forward, backward and the backward of the backward."""
+    if (gate.dtype in (torch.bfloat16, torch.float16, torch.float32) and up.dtype == gate.dtype
+            and _kernels_ready(gate, up) and gate.numel() % (16 // gate.element_size()) == 0
+            and gate.shape == up.shape):
         return _SwiGLUFn.apply(gate, up)
     return swiglu_ref(gate, up)
 

@@ -363,3 +363,32 @@ def test_token_cross_entropy_second_order_matches_torch(native, dtype, V):
     tol = 1e-4 if dtype == torch.float32 else 3e-2
     for g, r in zip(got, want):
         assert (g.double() - r).abs().max() <= tol * (r.abs().max() + 1e-6)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_rms_norm_and_swiglu_second_order_match_torch(native, dtype):
+    from bergson_b200 import ops
+
+    torch.manual_seed(0)
+    rows, d = 80, 256
+    x = torch.randn(rows, d, device="cuda").to(dtype).requires_grad_(True)
+    w = (1 + 0.1 * torch.randn(d, device="cuda")).to(dtype).requires_grad_(True)
+    u = torch.randn(rows, d, device="cuda").to(dtype).requires_grad_(True)
+    cot, probe = torch.randn(rows, d, device="cuda"), torch.randn(rows, d, device="cuda")
+
+    def chain(fn, x, w, u, cast):
+        y = fn(x, w, u)
+        gx, gw, gu = torch.autograd.grad((y * cot.to(cast)).sum(), (x, w, u), create_graph=True)
+        inner = (gx * probe.to(cast)).sum() + gw.pow(2).sum() + (gu * probe.to(cast)).sum()
+        return (y, gx, gw, gu) + torch.autograd.grad(inner, (x, w, u))
+
+    def ref(x, w, u):
+        n = x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + 1e-5) * w
+        return torch.nn.functional.silu(n) * u
+
+    with ops.composable():
+        got = chain(lambda x, w, u: ops.swiglu(ops.rms_norm(x, w, 1e-5), u), x, w, u, dtype)
+    want = chain(ref, *(t.detach().double().requires_grad_(True) for t in (x, w, u)), torch.float64)
+    tol = 2e-4 if dtype == torch.float32 else 5e-2
+    for g, r in zip(got, want):
+        assert (g.double() - r).abs().max() <= tol * (r.abs().max() + 1e-6)
