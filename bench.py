@@ -49,6 +49,8 @@ def parse_args():
     ap.add_argument("--seqs", type=int, default=8, help="sequences per rank per step")
     ap.add_argument("--seq-len", type=int, default=2048)
     ap.add_argument("--small", action="store_true", help="4-layer d1024 stand-in for quick checks (not a bench value)")
+    ap.add_argument("--kernel-table", default="", help="after the timed regions, profile one more step of this "
+                    "repository's arm with the torch profiler and write rank 0's per-kernel device times to this file")
     ap.add_argument("--extra", default="query,ekfac,magic",
                     help="comma-separated secondary metrics reported under \"extra\" (query, ekfac; empty for none)")
     return ap.parse_args()
@@ -107,7 +109,7 @@ def run_ours(args, rank, local_rank, world):
     model.get_input_embeddings().requires_grad_(True)
 
     W, K, B, S = args.warmup, args.steps, args.seqs, args.seq_len
-    per_rank = W + 2 * K  # warm-up, device-timed steps, end-to-end steps
+    per_rank = W + 2 * K + (1 if args.kernel_table else 0)  # warm-up, device-timed, end-to-end (+ profiled) steps
     ds = make_dataset(world, per_rank, B, S, spec["vocab_size"])
     batches = allocate_batches(ds["length"], B * S)
     assert len(batches) == per_rank and all(len(b) == B for b in batches), (len(batches), per_rank)
@@ -156,13 +158,23 @@ def run_ours(args, rank, local_rank, world):
         barrier_sync(device)
         w0 = time.perf_counter()
         loss_sum = 0.0
-        for b in batches[W + K :]:
+        for b in batches[W + K : W + 2 * K]:
             losses = computer.step(b)
             loss_sum += float(losses.sum().cpu())  # device -> host read of the step's result
         collector.builder.flush()  # all rows of the timed steps have reached the store
         barrier_sync(device)
         e2e_s = max_over_ranks(time.perf_counter() - w0, device)
         clocks = sampler.stop() if rank == 0 else None
+        if args.kernel_table:  # outside every timed region
+            from torch.profiler import ProfilerActivity, profile
+
+            with profile(activities=[ProfilerActivity.CUDA]) as prof:
+                computer.step(batches[W + 2 * K])
+                torch.cuda.synchronize(device)
+            if rank == 0:
+                with open(args.kernel_table, "w") as f:
+                    f.write(prof.key_averages().table(sort_by="cuda_time_total", row_limit=40,
+                                                      max_name_column_width=100))
     status = attribution.kernel_status(local_rank)
     assert status == 0, f"kernel status {status}"
     if rank == 0:
