@@ -209,3 +209,23 @@ def test_gather_with_copy_and_scatter_forms_on_one_gpu():
         ref = shards[owner][:, :N].float() + 2 * block
         assert (summed.float() - ref).abs().max() <= 3e-2 * ref.abs().max()
     assert int(native.kernel_status(0).item()) == 0
+
+
+def test_peer_barrier_passes_when_signalled_and_gives_up_when_not():
+    """The cross-rank flag barrier with both ranks' flag words on this GPU: it returns cleanly
+    when the other rank's arrival is already recorded, and when it never comes the bounded
+    wait runs out, the status word says so, and the context stays usable."""
+    from bergson_b200.ops import native
+
+    flags = [torch.zeros(8, dtype=torch.int32, device="cuda") for _ in range(2)]
+    ptrs = [f.data_ptr() for f in flags]
+    st = _status()
+    flags[0][1] = 1  # rank 1 "arrived" at epoch 1
+    native.peer_barrier(ptrs, 0, 1, 2_000_000, st)
+    torch.cuda.synchronize()
+    assert int(st.item()) == 0
+    assert int(flags[0][0]) == 1 and int(flags[1][0]) == 1  # rank 0 signalled both ranks
+    native.peer_barrier(ptrs, 0, 2, 200_000, st)  # nobody raises rank 1's word to 2
+    torch.cuda.synchronize()
+    assert int(st.item()) == 4  # kStatusTimeoutFlag
+    assert float(torch.ones(8, device="cuda").sum()) == 8.0
