@@ -219,7 +219,7 @@ class _GatherLinearFn(torch.autograd.Function):
     """``y [T, N] = gather(x_shard) @ W^T`` with the gather inside the GEMM's A loads."""
 
     @staticmethod
-    def forward(ctx, shard: Tensor, weight: Tensor, pub: Published, module, tap, lead, replicated: bool):
+    def forward(ctx, shard: Tensor, weight: Tensor, pub: Published, module, tap, lead):
         from ..ops import native
 
         sp = pub.sp
@@ -227,7 +227,7 @@ class _GatherLinearFn(torch.autograd.Function):
         y, a_proj = pub.gemm(weight, False, taps[0] if taps is not None else None)
         ctx.pub = pub
         ctx.save_for_backward(weight, taps[1] if taps is not None else None, a_proj if taps is not None else None)
-        ctx.sp, ctx.module, ctx.tap, ctx.lead, ctx.replicated = sp, module, tap if taps is not None else None, lead, replicated
+        ctx.sp, ctx.module, ctx.tap, ctx.lead = sp, module, tap if taps is not None else None, lead
         ctx.rows = shard.shape[0]
         return y
 
@@ -241,12 +241,6 @@ class _GatherLinearFn(torch.autograd.Function):
         rows, width = ctx.rows, weight.shape[1]
         if weight.requires_grad:
             raise NotImplementedError("sequence-parallel projections do not produce weight gradients")
-        if ctx.replicated:
-            # Every rank computed the same loss from the same gathered rows: this rank's part of
-            # the gradient is the slice of its own rows (nothing to sum over ranks).
-            mine = g[sp.rank * rows : (sp.rank + 1) * rows]
-            dx, _ = native.gemm(mine, weight, False, True, None, False, None, False, None, cta_group=2, wide=True)
-            return dx, None, None, None, None, None, None
         ptrs, _ = ctx.pub.push_target(rows, width)
         _, g_proj = native.gemm(g, weight, False, True, None, False, None, False, p_out, cta_group=2, wide=True,
                                 d_peer_ptrs=ptrs, d_rows_per_rank=rows, d_slot=sp.rank)
@@ -255,7 +249,7 @@ class _GatherLinearFn(torch.autograd.Function):
             ctx.tap.collect(ctx.module, a_proj, g_proj, torch.Size(ctx.lead))
         # The projections that share this input share one reduce-scatter: the last one to push
         # returns the summed gradient, the others contribute nothing of their own.
-        return ctx.pub.finish_if_last(rows, width), None, None, None, None, None, None
+        return ctx.pub.finish_if_last(rows, width), None, None, None, None, None
 
 
 class _ScatterLinearFn(torch.autograd.Function):
@@ -294,18 +288,18 @@ class _ScatterLinearFn(torch.autograd.Function):
         return dx, None, (g if ctx.has_residual else None), None, None, None, None
 
 
-def gather_linear(pub: Published, module, lead: tuple[int, int], replicated: bool = False) -> Tensor:
+def gather_linear(pub: Published, module, lead: tuple[int, int]) -> Tensor:
     """Column-parallel projection of a published token shard: ``[T, out_local]``."""
     tap = getattr(module, "_tap", None)
     if tap is not None and not (torch.is_grad_enabled() and pub.shard.requires_grad):
         tap = None
     if tap is None:
         _check_hooks(module, None)
-    if torch.is_grad_enabled() and pub.shard.requires_grad and not replicated:
+    if torch.is_grad_enabled() and pub.shard.requires_grad:
         if pub.consumers >= MAX_CONSUMERS:
             raise RuntimeError(f"at most {MAX_CONSUMERS} projections may share one published input")
         pub.consumers += 1
-    return _GatherLinearFn.apply(pub.shard, module.weight, pub, module, tap, lead, replicated)
+    return _GatherLinearFn.apply(pub.shard, module.weight, pub, module, tap, lead)
 
 
 def scatter_linear(x: Tensor, module, sp: SeqParallel, lead: tuple[int, int], residual: Tensor | None = None) -> Tensor:
