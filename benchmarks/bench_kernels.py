@@ -267,6 +267,57 @@ def bench_adamw_multi(small: bool, iters: int):
     return out
 
 
+def bench_second_order(small: bool, iters: int):
+    """Backward-of-backward kernels of the traced (MAGIC) path on GPT-2-sized tensors, against the
+    same quantity from torch's own double-backward formulas."""
+    from bergson_b200.ops import native
+
+    rows, d, ff = (8192, 768, 3072) if small else (32768, 768, 3072)
+    bf = torch.bfloat16
+    out = []
+
+    def torch_ms(fn, inputs, cots):
+        """Time of autograd evaluating the backward of fn's backward."""
+        leaves = [t.detach().requires_grad_(True) for t in inputs]
+        y = fn(*leaves)
+        grads = torch.autograd.grad(y, leaves, torch.ones_like(y), create_graph=True)
+        keep = [(g, c) for g, c in zip(grads, cots) if g is not None and g.requires_grad]
+        gs, cs = [g for g, _ in keep], [c for _, c in keep]
+        return _time(lambda: torch.autograd.grad(gs, leaves, cs, retain_graph=True, allow_unused=True), iters)
+
+    x = torch.randn(rows, d, device="cuda").to(bf)
+    w, b = torch.ones(d, device="cuda", dtype=bf), torch.zeros(d, device="cuda", dtype=bf)
+    dy, cu = torch.randn_like(x), torch.randn_like(x)
+    _, mean, rstd = native.layernorm_fwd(x, w, b, 1e-5)
+    ms = _time(lambda: native.layernorm_bwd_bwd(cu, w, b, dy, x, w, mean, rstd), iters)
+    ref = torch_ms(lambda x, w, b: torch.nn.functional.layer_norm(x, (d,), w, b, 1e-5), [x, w, b], [cu, w.float().to(bf), b])
+    out.append(dict(kernel="layernorm_bwd_bwd", shape=[rows, d], ms=ms, torch_ms=ref, bytes=rows * d * 2 * 5, flops=0))
+
+    h = torch.randn(rows, ff, device="cuda").to(bf)
+    dyh, ch = torch.randn_like(h), torch.randn_like(h)
+    ms = _time(lambda: native.gelu_bwd_bwd(ch, dyh, h, True), iters)
+    ref = torch_ms(lambda h: torch.nn.functional.gelu(h, approximate="tanh"), [h], [ch])
+    out.append(dict(kernel="gelu_bwd_bwd", shape=[rows, ff], ms=ms, torch_ms=ref, bytes=rows * ff * 2 * 5, flops=0))
+
+    s_rows, s_len = (rows // 512) * 12 * 512, 512  # [B * H * S, S] attention rows
+    y = torch.softmax(torch.randn(s_rows, s_len, device="cuda"), -1).to(bf)
+    dys, cs = torch.randn_like(y), torch.randn_like(y)
+    ms = _time(lambda: native.softmax_bwd_bwd(cs, dys, y), iters)
+    z = torch.randn(s_rows, s_len, device="cuda").to(bf)
+    ref = torch_ms(lambda z: torch.softmax(z, -1), [z], [cs])
+    out.append(dict(kernel="softmax_bwd_bwd", shape=[s_rows, s_len], ms=ms, torch_ms=ref, bytes=s_rows * s_len * 2 * 5, flops=0))
+
+    T, V = (4096, 50264) if small else (16384, 50264)
+    logits = torch.randn(T, V, device="cuda").to(bf)
+    tgt = torch.randint(0, 50257, (T,), device="cuda")
+    _, lse = native.ce_fwd(logits, tgt, -100)
+    dloss, c = torch.rand(T, device="cuda"), torch.randn(T, V, device="cuda").to(bf)
+    ms = _time(lambda: native.ce_bwd_bwd(c, logits, tgt, lse, dloss, -100), iters)
+    ref = torch_ms(lambda z: torch.nn.functional.cross_entropy(z.float(), tgt, reduction="none"), [logits], [c])
+    out.append(dict(kernel="ce_bwd_bwd", shape=[T, V], ms=ms, torch_ms=ref, bytes=T * V * 2 * 5, flops=0))
+    return out
+
+
 def bench_slot_reduce(small: bool, iters: int):
     """Owner-side sum of reduce-scatter slots (+ residual), 8 slots of [2048, 8192] bf16."""
     from bergson_b200.ops import native
@@ -337,7 +388,7 @@ def bench_gemm_case(small: bool, iters: int):
 BENCHES = {"proj_right": bench_proj_right, "proj_left_outer": bench_proj_left_outer, "cov_syrk": bench_cov_syrk,
            "tn_gemm": bench_tn_gemm, "ce_fwd": bench_ce, "rmsnorm_fwd": bench_rmsnorm, "linear_gemm": bench_linear_gemm, "ce_bwd": bench_ce_bwd,
            "rmsnorm_bwd": bench_rmsnorm_bwd, "adamw": bench_adamw, "proj_contract": bench_contract, "rotary": bench_rotary,
-           "swiglu_bwd": bench_swiglu, "gemm_case": bench_gemm_case, "adamw_multi": bench_adamw_multi,
+           "swiglu_bwd": bench_swiglu, "gemm_case": bench_gemm_case, "adamw_multi": bench_adamw_multi, "second_order": bench_second_order,
            "slot_reduce": bench_slot_reduce}
 
 

@@ -69,6 +69,10 @@ at::Tensor contract_counters(int device, int64_t n) {
 }
 
 int* status_ptr(const at::Tensor& like) { return status_tensor(like.get_device()).data_ptr<int>(); }
+// Blocks (= rows of partial weight-gradient sums) of the norm backward kernels: narrow rows use
+// small blocks, so more of them are needed to fill the SMs.
+static int64_t partial_blocks(int64_t d) { return d <= 1024 ? 148 * 8 : (d <= 2048 ? 148 * 4 : 148 * 2); }
+
 int* status_ptr_current() { return status_tensor(at::cuda::current_device()).data_ptr<int>(); }
 
 }  // namespace
@@ -92,7 +96,7 @@ std::vector<at::Tensor> rmsnorm_bwd(at::Tensor dy, at::Tensor x, at::Tensor w, a
   at::Tensor partial, dw;
   int n_partial = 0;
   if (need_dw) {
-    n_partial = (int)std::min<int64_t>(x.size(0), 148 * 2);
+    n_partial = (int)std::min<int64_t>(x.size(0), partial_blocks(x.size(1)));
     partial = at::empty({n_partial, x.size(1)}, x.options().dtype(at::kFloat));
   }
   check(bgn_rmsnorm_bwd(dy.data_ptr(), x.data_ptr(), wc.data_ptr(), rstd.data_ptr<float>(), dx.data_ptr(),
@@ -126,7 +130,7 @@ std::vector<at::Tensor> layernorm_bwd(at::Tensor dy, at::Tensor x, at::Tensor w,
   at::Tensor pw, pb, dw, db;
   int n_partial = 0;
   if (need_dw) {
-    n_partial = (int)std::min<int64_t>(x.size(0), 148 * 2);
+    n_partial = (int)std::min<int64_t>(x.size(0), partial_blocks(x.size(1)));
     pw = at::empty({n_partial, x.size(1)}, x.options().dtype(at::kFloat));
     pb = at::empty_like(pw);
   }
@@ -152,7 +156,7 @@ std::vector<at::Tensor> rmsnorm_bwd_bwd(at::Tensor cu, at::Tensor cw, at::Tensor
   auto vw = cw.to(at::kFloat).contiguous();
   TORCH_CHECK(vw.numel() == x.size(1));
   auto d_dy = at::empty_like(x), d_x = at::empty_like(x);
-  const int n_partial = (int)std::min<int64_t>(x.size(0), 148 * 2);
+  const int n_partial = (int)std::min<int64_t>(x.size(0), partial_blocks(x.size(1)));
   auto pw = at::empty({n_partial, x.size(1)}, x.options().dtype(at::kFloat));
   check(bgn_rmsnorm_bwd_bwd(cu.data_ptr(), vw.data_ptr<float>(), dy.data_ptr(), x.data_ptr(), wc.data_ptr(),
                             rstd.data_ptr<float>(), d_dy.data_ptr(), d_x.data_ptr(), pw.data_ptr<float>(), n_partial,
@@ -183,7 +187,7 @@ std::vector<at::Tensor> layernorm_bwd_bwd(at::Tensor cu, at::Tensor cw, at::Tens
   auto vw = cw.to(at::kFloat).contiguous(), sb = cb.to(at::kFloat).contiguous();
   TORCH_CHECK(vw.numel() == x.size(1) && sb.numel() == x.size(1));
   auto d_dy = at::empty_like(x), d_x = at::empty_like(x);
-  const int n_partial = (int)std::min<int64_t>(x.size(0), 148 * 2);
+  const int n_partial = (int)std::min<int64_t>(x.size(0), partial_blocks(x.size(1)));
   auto pw = at::empty({n_partial, x.size(1)}, x.options().dtype(at::kFloat));
   check(bgn_layernorm_bwd_bwd(cu.data_ptr(), vw.data_ptr<float>(), sb.data_ptr<float>(), dy.data_ptr(), x.data_ptr(),
                               wc.data_ptr(), mean.data_ptr<float>(), rstd.data_ptr<float>(), d_dy.data_ptr(),

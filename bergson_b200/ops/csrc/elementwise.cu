@@ -34,6 +34,32 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
   return t;
 }
 
+// Sums N values over the block with one pass through shared memory (`red` holds 33 * N floats);
+// every thread gets all N totals.
+template <int N>
+__device__ __forceinline__ void block_sum_n(float (&v)[N], float* red) {
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = blockDim.x >> 5;
+#pragma unroll
+  for (int j = 0; j < N; ++j) v[j] = warp_sum(v[j]);
+  __syncthreads();  // `red` may still be read from an earlier call
+  if (l == 0) {
+#pragma unroll
+    for (int j = 0; j < N; ++j) red[w * N + j] = v[j];
+  }
+  __syncthreads();
+  if (w == 0) {
+#pragma unroll
+    for (int j = 0; j < N; ++j) {
+      float t = l < nw ? red[l * N + j] : 0.f;
+      t = warp_sum(t);
+      if (l == 0) red[32 * N + j] = t;
+    }
+  }
+  __syncthreads();
+#pragma unroll
+  for (int j = 0; j < N; ++j) v[j] = red[32 * N + j];
+}
+
 __device__ __forceinline__ float block_max(float v, float* red) {
   v = warp_max(v);
   const int w = threadIdx.x >> 5, l = threadIdx.x & 31;
@@ -141,7 +167,7 @@ __global__ void rmsnorm_bwd_bwd_kernel(const T* __restrict__ U, const float* __r
                                        const T* __restrict__ dy, const T* __restrict__ x, const T* __restrict__ w,
                                        const float* __restrict__ rstd, T* __restrict__ d_dy, T* __restrict__ d_x,
                                        float* __restrict__ dw_partial, long rows, int d) {
-  __shared__ float red[32];
+  __shared__ float red[33 * 4];
   constexpr int V = Vec<T>::N;
   constexpr int kMaxPer = 4;
   float dw_acc[kMaxPer][V];
@@ -170,8 +196,9 @@ __global__ void rmsnorm_bwd_bwd_kernel(const T* __restrict__ U, const float* __r
       }
     }
     const float inv_d = 1.f / d;
-    const float b = block_sum(sgx, red) * inv_d, c = block_sum(sux, red) * inv_d;
-    const float mgu = block_sum(sgu, red) * inv_d, mqx = block_sum(sqx, red) * inv_d;
+    float sums[4] = {sgx, sux, sgu, sqx};
+    block_sum_n<4>(sums, red);
+    const float b = sums[0] * inv_d, c = sums[1] * inv_d, mgu = sums[2] * inv_d, mqx = sums[3] * inv_d;
     const float e = mgu - b * c;
     int slot = 0;
     for (int i = threadIdx.x * V; i < d; i += blockDim.x * V, ++slot) {
@@ -323,7 +350,7 @@ __global__ void layernorm_bwd_bwd_kernel(const T* __restrict__ U, const float* _
                                          const float* __restrict__ mean, const float* __restrict__ rstd,
                                          T* __restrict__ d_dy, T* __restrict__ d_x, float* __restrict__ dw_partial,
                                          long rows, int d) {
-  __shared__ float red[32];
+  __shared__ float red[33 * 7];
   constexpr int V = Vec<T>::N;
   constexpr int kMaxPer = 4;
   float dw_acc[kMaxPer][V];
@@ -357,10 +384,10 @@ __global__ void layernorm_bwd_bwd_kernel(const T* __restrict__ U, const float* _
       }
     }
     const float inv_d = 1.f / d;
-    const float a = block_sum(sg, red) * inv_d, b = block_sum(sgx, red) * inv_d;
-    const float mU = block_sum(su, red) * inv_d, c = block_sum(sux, red) * inv_d;
-    const float mgu = block_sum(sgu, red) * inv_d;
-    const float mq = block_sum(sq, red) * inv_d, mqx = block_sum(sqx, red) * inv_d;
+    float sums[7] = {sg, sgx, su, sux, sgu, sq, sqx};
+    block_sum_n<7>(sums, red);
+    const float a = sums[0] * inv_d, b = sums[1] * inv_d, mU = sums[2] * inv_d, c = sums[3] * inv_d;
+    const float mgu = sums[4] * inv_d, mq = sums[5] * inv_d, mqx = sums[6] * inv_d;
     const float e = mgu - a * mU - b * c;
     int slot = 0;
     for (int i = threadIdx.x * V; i < d; i += blockDim.x * V, ++slot) {
