@@ -25,6 +25,7 @@ from torch import Tensor
 
 from ..collector.collector import HookCollectorBase
 from ..utils.logger import get_logger
+from ..utils.streamed_safetensors import StreamedSafetensors
 from ..utils.utils import assert_type, get_device
 from .sharded_computation import ShardedMul, shard_bounds
 
@@ -138,30 +139,57 @@ class LambdaCollector(HookCollectorBase):
         save_file(out, os.path.join(d, f"shard_{self.rank}.safetensors"))
 
 
-def _compute_full_matrix(name: str, shard_path, rank: int, world_size: int) -> Tensor:
-    """Concatenate ``name`` from every shard file (row order = rank order)."""
-    files = [f for f in os.listdir(shard_path) if f.endswith(".safetensors")]
-    assert len(files) == world_size, f"Expected {world_size} shards, found {len(files)} in {shard_path}"
-    device = get_device(rank)
-    parts = []
-    for r in range(world_size):
-        with safe_open(os.path.join(shard_path, f"shard_{r}.safetensors"), framework="pt", device=device) as f:
-            parts.append(f.get_tensor(name))
-    return parts[0] if world_size == 1 else torch.cat(parts, dim=0)
-
-
-def _gather_and_shard_along_dim_0(input_dict, full_shape_per_key, dtype, rank, world_size, device):
+def _gather_and_shard_along_dim_0(input_dict, full_shape_per_key, dtype, rank, world_size, device, sink=None):
     """Every key lives on exactly one rank; sum-reduce (others contribute zeros) and keep
-    this rank's rows."""
+    this rank's rows.  With ``sink`` the shards are handed to ``sink(key, shard)`` on a helper
+    thread (copy to the host and file write overlap the next key's reduction) and nothing is
+    returned; otherwise the shards come back as host tensors."""
     if world_size == 1:
-        return input_dict
+        assert sink is None
+        return {k: v.cpu() for k, v in input_dict.items()}
     out = {}
-    for key, shape in full_shape_per_key.items():
-        t = input_dict[key].to(device=device, dtype=dtype) if key in input_dict else torch.zeros(shape, device=device, dtype=dtype)
-        dist.all_reduce(t, op=dist.ReduceOp.SUM)
-        lo, hi = shard_bounds(shape[0], rank, world_size)
-        out[key] = t[lo:hi].contiguous().cpu()
+    pool = None
+    if sink is not None:
+        from concurrent.futures import ThreadPoolExecutor
+
+        pool = ThreadPoolExecutor(max_workers=2)
+        dev = torch.device(device)
+
+        def deliver(key, shard):
+            if dev.type == "cuda":
+                torch.cuda.set_device(dev)
+            sink(key, shard)
+
+    pending = []
+    try:
+        for key, shape in full_shape_per_key.items():
+            t = (input_dict.pop(key).to(device=device, dtype=dtype) if key in input_dict
+                 else torch.zeros(shape, device=device, dtype=dtype))
+            dist.all_reduce(t, op=dist.ReduceOp.SUM)
+            lo, hi = shard_bounds(shape[0], rank, world_size)
+            shard = t[lo:hi].contiguous()
+            if pool is not None:
+                if shard.is_cuda:
+                    # The helper thread copies on its own stream: order it after the reduction.
+                    shard.record_stream(torch.cuda.current_stream())
+                    ev = torch.cuda.Event()
+                    ev.record()
+                    pending.append(pool.submit(_after_event, ev, deliver, key, shard))
+                else:
+                    pending.append(pool.submit(deliver, key, shard))
+            else:
+                out[key] = shard.cpu()
+        for fut in pending:
+            fut.result()
+    finally:
+        if pool is not None:
+            pool.shutdown(wait=True)
     return out
+
+
+def _after_event(event, fn, *args):
+    event.synchronize()
+    return fn(*args)
 
 
 def compute_eigendecomposition(covariance_path: str, total_processed) -> dict[str, Tensor]:
@@ -180,56 +208,97 @@ def compute_eigendecomposition(covariance_path: str, total_processed) -> dict[st
 
     vecs: dict[str, Tensor] = {}
     vals: dict[str, Tensor] = {}
+    finite: dict[str, Tensor] = {}
+    mine = fair_distribute_by_cost(dims, world)[rank]
+    on_gpu = torch.device(device).type == "cuda"
+    # Every shard file is opened once and this rank's factors are read straight onto the device
+    # (row order = rank order); results stay on the device until they are gathered and written.
+    n_files = sum(f.endswith(".safetensors") for f in os.listdir(covariance_path))
+    assert n_files == world, f"Expected {world} shards, found {n_files} in {covariance_path}"
+    out_dir = os.path.join(os.path.dirname(covariance_path), "eigen_" + os.path.basename(covariance_path))
+    os.makedirs(out_dir, exist_ok=True)
+    layout = {k: ((shard_bounds(m, rank, world)[1] - shard_bounds(m, rank, world)[0], m), out_dtype)
+              for k, m in dims.items()}
+    writer = StreamedSafetensors(os.path.join(out_dir, f"shard_{rank}.safetensors"), layout)
+    parts: dict[str, list[Tensor]] = {k: [] for k in mine}
+    for r in range(world):
+        with safe_open(os.path.join(covariance_path, f"shard_{r}.safetensors"), framework="pt", device=str(device)) as f:
+            for key in mine:
+                parts[key].append(f.get_tensor(key))
 
     def decompose(key: str, stream) -> None:
         ctx = torch.cuda.stream(stream) if stream is not None else nullcontext()
         with ctx:
-            m = _compute_full_matrix(key, covariance_path, rank, world).to(torch.float64) / total
+            rows = parts.pop(key)
+            m = (rows[0] if len(rows) == 1 else torch.cat(rows, dim=0)).to(torch.float64) / total
             m = (m + m.T) / 2
-            if not torch.isfinite(m).all():
-                raise ValueError(f"Covariance matrix for {key} contains NaNs or Infs. Consider using fp32.")
+            finite[key] = torch.isfinite(m).all()  # read once, after all factors are queued
             try:
                 w, q = torch.linalg.eigh(m)
             except Exception as e:
+                if not bool(finite[key]):
+                    raise ValueError(f"Covariance matrix for {key} contains NaNs or Infs. Consider using fp32.") from e
                 raise RuntimeError(f"Eigendecomposition failed for {key}") from e
-            vecs[key] = q.to(out_dtype).cpu().contiguous()
-            vals[key] = w.to(out_dtype).cpu().contiguous()
+            q = q.to(out_dtype).contiguous()  # the solver returns column-major storage
+            vals[key] = w.to(out_dtype)
+            if world == 1:
+                writer.write(key, q)  # copy to the host and file write overlap the other threads' solves
+            else:
+                vecs[key] = q
 
-    mine = fair_distribute_by_cost(dims, world)[rank]
-    if torch.device(device).type == "cuda" and len(mine) > 1:
-        # A dense symmetric eigensolver of a few thousand rows cannot fill the GPU on its own (long
-        # chains of small kernels with host round trips in between): several factors are
-        # decomposed at once, each on its own stream from its own host thread.
-        from concurrent.futures import ThreadPoolExecutor
+    try:
+        if on_gpu and len(mine) > 1:
+            # A dense symmetric eigensolver of a few thousand rows cannot fill the GPU on its own (long
+            # chains of small kernels with host round trips in between): several factors are
+            # decomposed at once, each on its own stream from its own host thread.
+            from concurrent.futures import ThreadPoolExecutor
 
-        workers = min(EIGH_CONCURRENCY, len(mine))
-        # torch loads its dense linear-algebra backend lazily and not thread-safely: trigger that
-        # from this thread before the workers start.
-        torch.linalg.eigh(torch.eye(2, device=device, dtype=torch.float64))
-        main = torch.cuda.current_stream()
-        streams = [torch.cuda.Stream() for _ in range(workers)]
-        for st in streams:
-            st.wait_stream(main)
+            workers = min(EIGH_CONCURRENCY, len(mine))
+            # torch loads its dense linear-algebra backend lazily and not thread-safely: trigger that
+            # from this thread before the workers start.
+            torch.linalg.eigh(torch.eye(2, device=device, dtype=torch.float64))
+            main = torch.cuda.current_stream()
+            streams = [torch.cuda.Stream() for _ in range(workers)]
+            for st in streams:
+                st.wait_stream(main)
 
-        def work(i: int) -> None:
-            torch.cuda.set_device(torch.device(device))
-            for key in mine[i::workers]:
-                decompose(key, streams[i])
+            import threading
 
-        with ThreadPoolExecutor(max_workers=workers) as pool:
-            list(pool.map(work, range(workers)))
-        for st in streams:
-            main.wait_stream(st)
-    else:
-        for key in mine:
-            decompose(key, None)
+            queue = iter(sorted(mine, key=lambda k: -dims[k]))  # largest first, taken as workers free up
+            queue_lock = threading.Lock()
 
-    vecs = _gather_and_shard_along_dim_0(vecs, {k: (m, m) for k, m in dims.items()}, out_dtype, rank, world, device)
-    vals = _gather_and_shard_along_dim_0(vals, {k: (m,) for k, m in dims.items()}, out_dtype, rank, world, device)
+            def work(i: int) -> None:
+                torch.cuda.set_device(torch.device(device))
+                while True:
+                    with queue_lock:
+                        key = next(queue, None)
+                    if key is None:
+                        return
+                    decompose(key, streams[i])
 
-    out_dir = os.path.join(os.path.dirname(covariance_path), "eigen_" + os.path.basename(covariance_path))
-    os.makedirs(out_dir, exist_ok=True)
-    save_file(vecs, os.path.join(out_dir, f"shard_{rank}.safetensors"))
+            with ThreadPoolExecutor(max_workers=workers) as pool:
+                list(pool.map(work, range(workers)))
+            for st in streams:
+                main.wait_stream(st)
+        else:
+            for key in mine:
+                decompose(key, None)
+    except BaseException:
+        writer.abort()
+        raise
+
+    try:
+        bad = [k for k, ok in finite.items() if not bool(ok)]
+        if bad:
+            raise ValueError(f"Covariance matrix for {bad[0]} contains NaNs or Infs. Consider using fp32.")
+        if world > 1:
+            _gather_and_shard_along_dim_0(vecs, {k: (m, m) for k, m in dims.items()}, out_dtype, rank, world, device,
+                                          sink=writer.write)
+        vals = _gather_and_shard_along_dim_0(vals, {k: (m,) for k, m in dims.items()}, out_dtype, rank, world, device)
+    except BaseException:
+        writer.abort()
+        raise
+    writer.close()
     gc.collect()
     get_logger().info(f"Saved eigenvectors to {out_dir}")
     return vals
@@ -246,21 +315,41 @@ def save_uncorrected_eigenvalues(partial_run_path, eigenvalues_a, eigenvalues_g,
     device = get_device(rank)
     total = torch.as_tensor(total_processed).to(device)
     sc = ShardedMul()
-    grid, fa, fg = {}, {}, {}
-    for key, g_shard in eigenvalues_g.items():
-        g_shard = g_shard.to(device)
+    fa, fg = {}, {}
+    a_full_by_key = {}
+    for key in eigenvalues_g:
         a_shard = eigenvalues_a[key].to(device)
         if world_size > 1:
             m = torch.tensor(a_shard.shape[0], device=device)
             dist.all_reduce(m, op=dist.ReduceOp.SUM)
-            a_full = sc.gather_rows(a_shard, int(m.item()))
-        else:
-            a_full = a_shard
-        grid[key] = (torch.outer(g_shard, a_full) * total).cpu().contiguous()
-        scale = total.to(a_full.dtype).sqrt()
-        fa[key] = (a_full * scale).cpu().contiguous()
-        fg[key] = (g_shard * scale).cpu().contiguous()
-    save_file(grid, os.path.join(dirs["eigenvalue_sharded"], f"shard_{rank}.safetensors"))
+            a_shard = sc.gather_rows(a_shard, int(m.item()))
+        a_full_by_key[key] = a_shard
+    # The grids are the large output: each goes to its byte range of the file from a helper thread
+    # while the next one is computed.
+    from concurrent.futures import ThreadPoolExecutor
+
+    layout = {k: ((g.shape[0], a_full_by_key[k].shape[0]), torch.result_type(g, a_full_by_key[k]))
+              for k, g in eigenvalues_g.items()}
+    writer = StreamedSafetensors(os.path.join(dirs["eigenvalue_sharded"], f"shard_{rank}.safetensors"), layout)
+    try:
+        with ThreadPoolExecutor(max_workers=2) as pool:
+            jobs = []
+            for key, g_shard in eigenvalues_g.items():
+                g_shard = g_shard.to(device)
+                a_full = a_full_by_key[key]
+                grid = torch.outer(g_shard, a_full) * total.to(layout[key][1])
+                if grid.is_cuda:
+                    torch.cuda.current_stream().synchronize()  # the helper thread reads it from another stream
+                jobs.append(pool.submit(writer.write, key, grid))
+                scale = total.to(a_full.dtype).sqrt()
+                fa[key] = (a_full * scale).cpu().contiguous()
+                fg[key] = (g_shard * scale).cpu().contiguous()
+            for job in jobs:
+                job.result()
+    except BaseException:
+        writer.abort()
+        raise
+    writer.close()
     save_file(fa, os.path.join(dirs["factor_eig_a"], f"shard_{rank}.safetensors"))
     save_file(fg, os.path.join(dirs["factor_eig_g"], f"shard_{rank}.safetensors"))
     get_logger().info(f"Saved uncorrected eigenvalues to {dirs['eigenvalue_sharded']}")

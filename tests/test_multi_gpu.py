@@ -250,6 +250,16 @@ def test_kfac_factors_two_gpus_match_one(tmp_path):
             assert one[k].shape == two[k].shape
             assert float((one[k] - two[k]).norm() / one[k].norm()) < 2e-3, (sub, k)
             assert float((two[k] - two[k].T).abs().max() / two[k].abs().max()) < 1e-5, (sub, k, "not symmetric")
+    # The eigendecomposition that follows (factors split over the ranks, shards streamed to the
+    # files): the assembled eigenvalue grids and orthonormal eigenvector shards.
+    one, two = (_load_full(tmp_path / n, "eigenvalue_sharded", "cpu") for n in ("one", "two"))
+    assert one.keys() == two.keys() and len(one) > 0
+    for k in one:
+        assert float((one[k] - two[k]).norm() / one[k].norm()) < 1e-2, ("eigenvalue_sharded", k)
+    for sub in ("eigen_activation_sharded", "eigen_gradient_sharded"):
+        for k, q in _load_full(tmp_path / "two", sub, "cpu").items():
+            eye = torch.eye(q.shape[0])
+            assert float((q.float().T @ q.float() - eye).abs().max()) < 1e-3, (sub, k)
 
 
 def _seq_parallel_worker(rank, world, port, out):
