@@ -2,9 +2,10 @@
 (reference ``bergson/query/faiss_index.py:56-409``).
 
 With the optional ``faiss`` package installed the shards are FAISS indices built from
-``index_factory`` (inner-product metric).  Without it, ``Flat`` falls back to exact
-search over fp32 ``.npy`` shards with the same directory layout and API; other factory
-strings then raise.
+``index_factory`` (inner-product metric).  Without it the shards are the in-tree indices of
+``native_ann.py`` (Flat, SQfp16, IVF<n>, PQ<m> and their combinations; searched with matrix
+products on the store's device) behind the same directory layout and API; factory strings
+that neither implements raise.
 """
 
 from __future__ import annotations
@@ -19,6 +20,7 @@ import torch
 from ..config import FaissConfig
 from ..data import column_offsets, load_gradients
 from ..utils.utils import numpy_to_tensor
+from .native_ann import NativeIndex, parse_factory
 
 try:
     import faiss  # type: ignore
@@ -62,7 +64,12 @@ class FaissIndex:
                     idx = faiss.index_cpu_to_all_gpus(idx)
                 self.shards.append(idx)
                 self.sizes.append(idx.ntotal)
-            else:
+            elif self.backend == "native":
+                idx = NativeIndex.load(self.path / str(i), device="cpu" if mmap_index else device, mmap=mmap_index)
+                idx.nprobe = self.nprobe
+                self.shards.append(idx)
+                self.sizes.append(idx.ntotal)
+            else:  # exact fp32 rows written by earlier versions
                 arr = np.load(self.path / f"{i}.npy", mmap_mode="r" if mmap_index else None)
                 self.shards.append(arr)
                 self.sizes.append(arr.shape[0])
@@ -80,9 +87,8 @@ class FaissIndex:
             sizes = json.load(f)["grad_sizes"]
         n = mm.shape[0]
         per = math.ceil(n / cfg.num_shards)
-        backend = "faiss" if HAVE_FAISS else "flat-npy"
-        if not HAVE_FAISS and cfg.index_factory != "Flat":
-            raise ImportError(f"index_factory={cfg.index_factory!r} needs the faiss package; only 'Flat' works without it.")
+        backend = "faiss" if HAVE_FAISS else "native"
+        factory = None if HAVE_FAISS else parse_factory(cfg.index_factory)  # raises for unsupported strings
         for s in range(cfg.num_shards):
             lo, hi = s * per, min((s + 1) * per, n)
             parts = [_prepare(mm[a : min(a + cfg.batch_size, hi)], sizes, device, unit_norm, h_inv)
@@ -95,7 +101,11 @@ class FaissIndex:
                 idx.add(x)
                 faiss.write_index(idx, str(faiss_path / f"{s}.faiss"))
             else:
-                np.save(faiss_path / f"{s}.npy", x)
+                idx = NativeIndex(x.shape[1], factory, device)
+                if factory.needs_training:
+                    idx.train(x if cfg.max_train_examples is None else x[: cfg.max_train_examples])
+                idx.add(x)
+                idx.save(faiss_path / str(s))
         with open(faiss_path / "config.yaml", "w") as f:
             json.dump({"ordered_modules": list(sizes), "num_shards": cfg.num_shards, "backend": backend,
                        "index_factory": cfg.index_factory, "nprobe": cfg.nprobe}, f)
@@ -107,7 +117,7 @@ class FaissIndex:
         all_d, all_i, base = [], [], 0
         for shard, size in zip(self.shards, self.sizes):
             kk = min(k, size)
-            if self.backend == "faiss":
+            if self.backend in ("faiss", "native"):
                 d, i = shard.search(-q if reverse else q, kk)
                 d = -d if reverse else d
             else:

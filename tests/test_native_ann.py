@@ -1,0 +1,131 @@
+"""In-tree nearest-neighbour indices: every factory against exact search on clustered data."""
+
+import numpy as np
+import pytest
+import torch
+
+from bergson_b200.query.native_ann import Factory, NativeIndex, parse_factory
+
+
+def _clustered(n=3000, d=32, clusters=24, seed=0):
+    g = np.random.default_rng(seed)
+    centres = g.normal(size=(clusters, d)).astype(np.float32) * 4
+    x = centres[g.integers(0, clusters, n)] + g.normal(size=(n, d)).astype(np.float32)
+    x /= np.linalg.norm(x, axis=1, keepdims=True)
+    q = x[g.choice(n, 40, replace=False)] + 0.05 * g.normal(size=(40, d)).astype(np.float32)
+    return x, q.astype(np.float32)
+
+
+def _exact(x, q, k):
+    s = q @ x.T
+    order = np.argsort(-s, axis=1)[:, :k]
+    return np.take_along_axis(s, order, 1), order
+
+
+def _recall(found, truth):
+    return np.mean([len(set(f) & set(t)) / len(t) for f, t in zip(found, truth)])
+
+
+def test_parse_factory():
+    assert parse_factory("Flat") == Factory(0, "fp32")
+    assert parse_factory("IVF1024,SQfp16") == Factory(1024, "fp16")
+    assert parse_factory("IVF1,SQfp16") == Factory(1, "fp16")
+    assert parse_factory("IVF64,PQ8") == Factory(64, "pq", 8)
+    assert parse_factory("PQ4x8") == Factory(0, "pq", 4)
+    with pytest.raises(ValueError, match="not implemented"):
+        parse_factory("HNSW32")
+
+
+@pytest.mark.parametrize("spec", ["Flat", "SQfp16", "IVF1,SQfp16"])
+def test_exhaustive_factories_equal_exact_search(spec):
+    x, q = _clustered()
+    idx = NativeIndex(x.shape[1], parse_factory(spec))
+    assert idx.is_trained
+    idx.add(x)
+    d, i = idx.search(q, 10)
+    ed, ei = _exact(x, q, 10)
+    tol = 1e-5 if spec == "Flat" else 2e-3
+    np.testing.assert_allclose(d, ed, atol=tol)
+    assert _recall(i, ei) > (0.999 if spec == "Flat" else 0.97)
+
+
+def test_ivf_all_lists_probed_is_exact_and_few_probes_keep_recall(tmp_path):
+    x, q = _clustered()
+    idx = NativeIndex(x.shape[1], parse_factory("IVF16,Flat"))
+    with pytest.raises(RuntimeError):
+        idx.add(x)
+    idx.train(x[:2000])
+    idx.add(x)
+    with pytest.raises(RuntimeError):
+        idx.add(x)
+    assert idx.offsets[-1] == len(x) and sorted(idx.ids.tolist()) == list(range(len(x)))
+    ed, ei = _exact(x, q, 10)
+    idx.nprobe = 16
+    d, i = idx.search(q, 10)
+    np.testing.assert_allclose(d, ed, atol=1e-5)
+    assert _recall(i, ei) > 0.999
+    idx.nprobe = 4
+    d4, i4 = idx.search(q, 10)
+    assert _recall(i4, ei) > 0.85
+    assert (np.diff(d4, axis=1) <= 1e-7).all()  # descending
+    # files: reloaded in memory and memory-mapped give the same answers
+    idx.save(tmp_path / "0")
+    for mmap in (False, True):
+        back = NativeIndex.load(tmp_path / "0", mmap=mmap)
+        back.nprobe = 4
+        d5, i5 = back.search(q, 10)
+        np.testing.assert_array_equal(i5, i4)
+        np.testing.assert_allclose(d5, d4, atol=1e-6)
+
+
+def test_fewer_candidates_than_k_are_padded():
+    x, q = _clustered(n=200, clusters=8)
+    idx = NativeIndex(x.shape[1], parse_factory("IVF32"))
+    idx.train(x)
+    idx.add(x)
+    idx.nprobe = 1
+    d, i = idx.search(q, 50)
+    assert d.shape == (40, 50) and (i == -1).any()
+    assert np.isneginf(d[i == -1]).all() and (i[np.isfinite(d)] >= 0).all()
+
+
+@pytest.mark.parametrize("spec", ["PQ8", "IVF8,PQ8"])
+def test_product_quantiser_ranks_the_true_neighbour_high(spec):
+    x, q = _clustered()
+    idx = NativeIndex(x.shape[1], parse_factory(spec))
+    idx.train(x)
+    idx.add(x)
+    idx.nprobe = 8
+    assert idx.vectors.dtype == torch.uint8 and idx.vectors.shape == (len(x), 8)
+    d, i = idx.search(q, 10)
+    _, ei = _exact(x, q, 100)
+    inside = np.mean([len(set(f) & set(t)) / len(f) for f, t in zip(i, ei)])  # found top-10 within the true top-100
+    assert inside > 0.9, inside
+    ed = np.take_along_axis(q @ x.T, np.maximum(i, 0), 1)
+    assert np.abs(d - ed).max() < 0.25  # scores are those of the decoded rows
+
+
+def test_attributor_over_ivf_shards(tmp_path):
+    import json
+
+    from bergson_b200.config import FaissConfig
+    from bergson_b200.query.faiss_index import HAVE_FAISS, FaissIndex
+
+    if HAVE_FAISS:
+        pytest.skip("the faiss package provides these factories")
+    x, q = _clustered(n=1200)
+    store = tmp_path / "store"
+    store.mkdir()
+    x.astype(np.float16).tofile(store / "gradients.bin")
+    with open(store / "info.json", "w") as f:
+        json.dump({"grad_sizes": {"w": x.shape[1]}, "num_grads": len(x), "base_dtype": "float16"}, f)
+    cfg = FaissConfig(index_factory="IVF8,SQfp16", num_shards=3, nprobe=8)
+    FaissIndex.create_index(store, tmp_path / "ann", cfg, "cpu", unit_norm=True, h_inv={})
+    idx = FaissIndex(tmp_path / "ann")
+    assert idx.ntotal == len(x) and idx.backend == "native"
+    d, i = idx.search(q, 5)
+    ed, ei = _exact(x, q, 5)
+    assert _recall(i, ei) > 0.95
+    dr, ir = idx.search(q, 5, reverse=True)
+    _, er = _exact(x, -q, 5)
+    assert _recall(ir, er) > 0.95 and (dr[:, 0] <= d[:, 0]).all()
