@@ -44,6 +44,25 @@ def bank_loss_cache_key(run_cfg: ValidationConfig, multi_query: bool, num_subset
     return f"losses_{hashlib.sha256(json.dumps(ident, sort_keys=True, default=str).encode()).hexdigest()[:16]}.pt"
 
 
+def _load_banked_model(run_cfg: ValidationConfig, out_dir: str, device) -> torch.nn.Module:
+    """A model banked by ``save_models``: a full checkpoint, or -- when the run trained an
+    adapter -- a directory holding only the adapter, which has to be applied to the run's base
+    model (pointing a checkpoint loader at such a directory would give the bare base model)
+    (reference ``bergson/validate.py:74-85``)."""
+    from .models import load_model
+
+    if os.path.isfile(os.path.join(out_dir, "adapter_config.json")):
+        try:
+            from peft import PeftModel
+        except ImportError as e:
+            raise ImportError(f"{out_dir} holds an adapter only; loading it needs the peft package") from e
+        base = load_model(run_cfg.model, dtype=torch.float32, device=device)
+        return PeftModel.from_pretrained(base, out_dir).to(device)
+    if not os.path.isdir(out_dir):
+        raise FileNotFoundError(f"no banked model at {out_dir} (was the run made with save_models?)")
+    return load_model(out_dir, dtype=torch.float32, device=device)
+
+
 def per_doc_query_losses(forward: Callable, query_stream: DataStream, num_docs: int) -> torch.Tensor:
     """Mean CE of each query document.  ``forward(input_ids)`` returns logits.  Token losses
     are scattered by the document id of the *label* token and reduced over ranks."""
@@ -253,7 +272,7 @@ def evaluate_retrained(run_cfg: ValidationConfig, retrained_dir, *, score_path: 
         subsets = [torch.tensor(s, dtype=torch.long) for s in json.load(f)]
 
     def losses_of(model_dir: str) -> torch.Tensor:
-        m = load_model(model_dir, dtype=torch.float32, device=device)
+        m = _load_banked_model(run_cfg, model_dir, device)
         m.eval()
         return per_doc_query_losses(lambda x: m(x).logits, qstream, len(query_ds)).cpu()
 
