@@ -129,3 +129,28 @@ def test_attributor_over_ivf_shards(tmp_path):
     dr, ir = idx.search(q, 5, reverse=True)
     _, er = _exact(x, -q, 5)
     assert _recall(ir, er) > 0.95 and (dr[:, 0] <= d[:, 0]).all()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("spec", ["Flat", "IVF64,SQfp16", "IVF16,PQ16"])
+def test_indices_on_the_gpu(spec, tmp_path):
+    if not torch.cuda.is_available():
+        pytest.skip("needs a GPU")
+    x, q = _clustered(n=20000, d=64, clusters=64, seed=2)
+    idx = NativeIndex(x.shape[1], parse_factory(spec), device="cuda")
+    if idx.factory.needs_training:
+        idx.train(x)
+    idx.add(x)
+    idx.nprobe = 16
+    assert idx.vectors.is_cuda
+    d, i = idx.search(q, 10)
+    _, truth = _exact(x, q, 100 if "PQ" in spec else 10)
+    if "PQ" in spec:
+        assert np.mean([len(set(f) & set(t)) / len(f) for f, t in zip(i, truth)]) > 0.8
+    else:
+        assert _recall(i, truth) > (0.999 if spec == "Flat" else 0.9)
+    idx.save(tmp_path / "0")
+    back = NativeIndex.load(tmp_path / "0", device="cuda")
+    back.nprobe = 16
+    d2, i2 = back.search(q, 10)
+    np.testing.assert_array_equal(i2, i)
