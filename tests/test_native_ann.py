@@ -132,7 +132,7 @@ def test_attributor_over_ivf_shards(tmp_path):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("spec", ["Flat", "IVF64,SQfp16", "IVF16,PQ16"])
+@pytest.mark.parametrize("spec", ["Flat", "IVF64,SQfp16", "IVF16,PQ32"])
 def test_indices_on_the_gpu(spec, tmp_path):
     if not torch.cuda.is_available():
         pytest.skip("needs a GPU")
