@@ -102,6 +102,8 @@ class NativeIndex:
         self.offsets = np.zeros(1, np.int64)  # [nlist + 1] list boundaries
         self.ntotal = 0
         self.nprobe = 10
+        self.dense_scan: bool | None = None  # None: chosen per search from the number of probed lists
+        self._row_list: Tensor | None = None
         if factory.storage == "pq" and dim % factory.pq_m:
             raise ValueError(f"PQ{factory.pq_m} needs the dimension ({dim}) to be a multiple of {factory.pq_m}")
 
@@ -182,6 +184,24 @@ class NativeIndex:
         idx = v.long()  # [r, m]
         return torch.stack([self.codebooks[j][idx[:, j]] for j in range(m)], 1).reshape(v.shape[0], self.dim)
 
+    def _scores(self, q: Tensor, lo: int, hi: int) -> Tensor:
+        """fp32 inner products of ``q`` with stored rows [lo, hi).  16-bit rows on a GPU go through
+        the tensor-core score GEMM (16-bit operands, fp32 accumulation and output) without being
+        widened first; everything else is an fp32 product with the decoded rows."""
+        v = self.vectors
+        if self.factory.storage == "fp16" and isinstance(v, Tensor) and v.is_cuda and self.dim % 8 == 0:
+            from ..ops import attribution
+
+            return attribution.score_rows(q, v[lo:hi], torch.float16, False)[0]
+        return q @ self._rows(lo, hi).T
+
+    def _row_lists(self) -> Tensor:
+        """Inverted list of every stored row (rows are sorted by list)."""
+        if self._row_list is None:
+            counts = torch.from_numpy(np.diff(self.offsets)).to(self.device)
+            self._row_list = torch.repeat_interleave(torch.arange(len(counts), device=self.device), counts)
+        return self._row_list
+
     def _ids(self, lo: int, hi: int) -> Tensor:
         i = self.ids[lo:hi]
         if not isinstance(i, Tensor):
@@ -219,22 +239,39 @@ class NativeIndex:
             step = max(1, (64 << 20) // max(nq, 1))  # bound the score tile to 64M entries
             for lo in range(0, self.ntotal, step):
                 hi = min(lo + step, self.ntotal)
-                merge(None, q @ self._rows(lo, hi).T, self._ids(lo, hi))
+                merge(None, self._scores(q, lo, hi), self._ids(lo, hi))
         else:
             nprobe = max(1, min(self.nprobe, nlist))
             coarse = q @ self.centroids.T  # [nq, nlist]
             probed = coarse.topk(nprobe, dim=1).indices
             hit = torch.zeros(nq, nlist, dtype=torch.bool, device=self.device)
             hit.scatter_(1, probed, True)
-            for l in hit.any(0).nonzero().flatten().tolist():
-                lo, hi = int(self.offsets[l]), int(self.offsets[l + 1])
-                if hi == lo:
-                    continue
-                rows = hit[:, l].nonzero().flatten()
-                s = q[rows] @ self._rows(lo, hi).T
-                if self.factory.storage == "pq":
-                    s = s + coarse[rows, l][:, None]  # stored rows are residuals to the centroid
-                merge(rows, s, self._ids(lo, hi))
+            pq = self.factory.storage == "pq"
+            dense = self.dense_scan if self.dense_scan is not None else nq * nprobe >= nlist
+            if dense:
+                # Most lists are probed by some query: one pass over all rows in large tiles, with the
+                # (query, row) pairs whose list the query does not probe masked out -- the same
+                # candidates as the per-list loop below without its many small launches.
+                row_list = self._row_lists()
+                step = max(1, (64 << 20) // max(nq, 1))
+                for lo in range(0, self.ntotal, step):
+                    hi = min(lo + step, self.ntotal)
+                    lists = row_list[lo:hi]
+                    s = self._scores(q, lo, hi)
+                    if pq:
+                        s = s + coarse[:, lists]
+                    merge(None, s.masked_fill_(~hit[:, lists], float("-inf")), self._ids(lo, hi))
+            else:
+                for l in hit.any(0).nonzero().flatten().tolist():
+                    lo, hi = int(self.offsets[l]), int(self.offsets[l + 1])
+                    if hi == lo:
+                        continue
+                    rows = hit[:, l].nonzero().flatten()
+                    s = self._scores(q[rows], lo, hi)
+                    if pq:
+                        s = s + coarse[rows, l][:, None]  # stored rows are residuals to the centroid
+                    merge(rows, s, self._ids(lo, hi))
+        best_i = best_i.masked_fill(torch.isneginf(best_d), -1)
         return best_d.cpu().numpy(), best_i.cpu().numpy()
 
     # ---------------------------------------------------------------- files

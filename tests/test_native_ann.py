@@ -154,3 +154,21 @@ def test_indices_on_the_gpu(spec, tmp_path):
     back.nprobe = 16
     d2, i2 = back.search(q, 10)
     np.testing.assert_array_equal(i2, i)
+
+
+@pytest.mark.parametrize("spec", ["IVF16,Flat", "IVF16,SQfp16", "IVF8,PQ8"])
+def test_masked_scan_and_per_list_loop_find_the_same_neighbours(spec):
+    x, q = _clustered()
+    idx = NativeIndex(x.shape[1], parse_factory(spec))
+    idx.train(x)
+    idx.add(x)
+    idx.nprobe = 3
+    idx.dense_scan = False
+    d0, i0 = idx.search(q, 10)
+    idx.dense_scan = True
+    d1, i1 = idx.search(q, 10)
+    np.testing.assert_allclose(d1, d0, atol=1e-5)
+    assert np.mean(i0 == i1) > 0.99  # equal scores may swap places
+    idx.nprobe, idx.dense_scan = 1, True
+    d, i = idx.search(q[:3], 2000)  # more than one list holds: padded the same way
+    assert (i == -1).any() and np.isneginf(d[i == -1]).all() and (i[np.isfinite(d)] >= 0).all()
