@@ -1,0 +1,102 @@
+"""Attributor: tracing a backward pass as the query, reverse search, curvature on one or both
+sides, and approximate indices behind the same calls."""
+
+import pytest
+import torch
+
+from bergson_b200 import Attributor, GradientProcessor, InMemoryCollector, collect_gradients
+from bergson_b200.collector.collector import CollectorComputer
+from bergson_b200.config import FaissConfig, IndexConfig
+from bergson_b200.data import allocate_batches
+
+from .helpers import tiny_dataset, tiny_model
+
+
+@pytest.fixture(scope="module")
+def store(tmp_path_factory):
+    tmp = tmp_path_factory.mktemp("attr")
+    torch.manual_seed(0)
+    model = tiny_model("gpt_neox")
+    model.requires_grad_(False)
+    model.get_input_embeddings().requires_grad_(True)
+    ds = tiny_dataset(n=12, length=12)
+    cfg = IndexConfig(run_path=str(tmp / "idx"), projection_dim=4, token_batch_size=48)
+    cfg.partial_run_path.mkdir(parents=True)
+    batches = allocate_batches(ds["length"], 48)
+    # one pass that also accumulates the gradient autocorrelation (the dense curvature estimate) ...
+    proc = GradientProcessor(projection_dim=4)
+    coll = InMemoryCollector(model=model.base_model, data=ds, cfg=cfg, processor=proc, skip_hessians=False)
+    CollectorComputer(model=model, data=ds, collector=coll, batches=batches, cfg=cfg).run_with_collector_hooks("mem")
+    # ... and the store on disk, with that processor saved beside it
+    collect_gradients(model, ds, proc, cfg, batches=batches)
+    proc.save(cfg.partial_run_path)
+    return model, ds, cfg.partial_run_path
+
+
+def _trace(attr, model, ds, i, k, **kw):
+    x = torch.tensor(ds[i]["input_ids"])[None]
+    with attr.trace(model.base_model, k, **kw) as result:
+        model(x, labels=x).loss.backward()
+    model.zero_grad()
+    return result
+
+
+def test_a_document_finds_itself(store):
+    model, ds, path = store
+    attr = Attributor(path, device="cpu", unit_norm=True)
+    for i in (0, 5):
+        r = _trace(attr, model, ds, i, 5)
+        assert r.indices.shape == (1, 5) and int(r.indices[0, 0]) == i and float(r.scores[0, 0]) > 0.99
+        assert (r.scores[0, :-1] >= r.scores[0, 1:]).all()
+    with pytest.raises(ValueError, match="backward"):
+        with attr.trace(model.base_model, 3):
+            pass
+    fresh = attr.trace(model.base_model, 3)
+    with fresh as result:
+        with pytest.raises(ValueError, match="context"):
+            result.scores
+        x = torch.tensor(ds[0]["input_ids"])[None]
+        model(x, labels=x).loss.backward()
+    model.zero_grad()
+
+
+def test_reverse_returns_the_least_similar(store):
+    model, ds, path = store
+    attr = Attributor(path, device="cpu", unit_norm=True)
+    top = _trace(attr, model, ds, 0, 5)
+    low = _trace(attr, model, ds, 0, 5, reverse=True)
+    assert float(low.scores[0, 0]) < float(top.scores[0, 0])
+    assert int(top.indices[0, 0]) == 0 and 0 not in low.indices[0].tolist()
+    assert (low.scores[0, :-1] <= low.scores[0, 1:]).all()
+    everything = _trace(attr, model, ds, 0, None)
+    assert sorted(everything.indices[0].tolist()) == list(range(len(ds)))
+    assert low.indices[0, 0] == everything.indices[0, -1]
+
+
+@pytest.mark.parametrize("unit_norm", [True, False])
+def test_curvature_on_both_sides_or_on_the_query_only(store, unit_norm):
+    """unit_norm: H^-1/2 on queries and rows, then cosine; otherwise H^-1 on the query only."""
+    model, ds, path = store
+    attr = Attributor(path, device="cpu", unit_norm=unit_norm, hessian_path=path)
+    assert attr.preconditioner is not None
+    r = _trace(attr, model, ds, 0, 5)
+    assert int(r.indices[0, 0]) == 0
+    if unit_norm:
+        assert float(r.scores[0, 0]) > 0.9
+    plain = _trace(Attributor(path, device="cpu", unit_norm=unit_norm), model, ds, 0, 5)
+    assert not torch.allclose(plain.scores, r.scores)
+
+
+@pytest.mark.parametrize("factory", ["Flat", "IVF2,SQfp16"])
+def test_approximate_indices_answer_the_same_calls(store, factory):
+    model, ds, path = store
+    exact = _trace(Attributor(path, device="cpu", unit_norm=True), model, ds, 3, 4)
+    attr = Attributor(path, device="cpu", unit_norm=True, faiss_cfg=FaissConfig(index_factory=factory, nprobe=2))
+    r = _trace(attr, model, ds, 3, 4)
+    assert r.indices[0].tolist() == exact.indices[0].tolist()
+    torch.testing.assert_close(r.scores.float(), exact.scores.float(), atol=2e-3, rtol=0)
+    low = _trace(attr, model, ds, 3, 4, reverse=True)
+    assert float(low.scores[0, 0]) < float(r.scores[0, 0]) and 3 not in low.indices[0].tolist()
+    # the index was written beside the store and is reused by the next Attributor
+    again = Attributor(path, device="cpu", unit_norm=True, faiss_cfg=FaissConfig(index_factory=factory, nprobe=2))
+    assert again.faiss_index.ntotal == len(ds)
