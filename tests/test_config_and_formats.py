@@ -162,3 +162,38 @@ def test_step_state_protocol(tmp_path):
     assert (out / "f").read_text() == "newer" and not out.with_name("step.superseded").exists()
     with pytest.raises(FileNotFoundError):
         promote_step(out)
+
+
+def test_interrupted_promotion_loses_nothing(tmp_path, monkeypatch):
+    """A crash between parking the old output and renaming the new one into place leaves both
+    on disk; the next run starts the step over from a clean slate."""
+    import bergson_b200.utils.step_state as ss
+
+    out = tmp_path / "step"
+    partial_path(out).mkdir()
+    (partial_path(out) / "old").write_text("1")
+    promote_step(out)
+    partial_path(out).mkdir()
+    (partial_path(out) / "new").write_text("2")
+    real = ss.Path.rename
+    calls = {"n": 0}
+
+    def crash_after_first(self, target):
+        calls["n"] += 1
+        result = real(self, target)
+        if calls["n"] == 1:
+            raise RuntimeError("crash in the middle of the swap")
+        return result
+
+    monkeypatch.setattr(ss.Path, "rename", crash_after_first)
+    with pytest.raises(RuntimeError):
+        promote_step(out)
+    monkeypatch.setattr(ss.Path, "rename", real)
+    assert (out.with_name("step.superseded") / "old").exists() and (partial_path(out) / "new").exists()
+    assert step_state(out) == "partial"
+    assert prepare_step(out, resume=True)
+    assert not out.with_name("step.superseded").exists() and not partial_path(out).exists()
+    # an unrelated neighbour's partial output is never touched
+    other = partial_path(tmp_path / "other")
+    other.mkdir()
+    assert prepare_step(out, resume=False) and other.exists()
