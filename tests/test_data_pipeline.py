@@ -108,3 +108,17 @@ def test_epochs_are_shuffled_independently_and_reproducibly():
     assert sorted(single) == list(range(N)) and single != list(range(N))
     with pytest.raises(AssertionError):
         shuffled_epochs(base, seed=0, num_epochs=0)
+
+
+def test_over_long_documents_warn_and_then_fail_to_pack(tmp_path):
+    import warnings
+
+    from bergson_b200.data import allocate_batches
+
+    with pytest.warns(UserWarning, match="longer than (the model can handle|token_batch_size)"):
+        ds, _ = _pretok(tmp_path, {"input_ids": [[1] * 40, [2] * 5]}, truncation=False)
+    with pytest.raises(RuntimeError, match="too long"):
+        allocate_batches(ds["length"], 32)
+    with warnings.catch_warnings():
+        warnings.simplefilter("error")  # documents that fit do not warn
+        _pretok(tmp_path / "ok", {"input_ids": [[1] * 30, [2] * 5]}, truncation=False)
