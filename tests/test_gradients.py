@@ -138,3 +138,54 @@ def test_jl_inner_products_are_preserved_in_expectation():
         R = create_projection_matrix(f"t{t}/right", 8, 40, torch.float32, torch.device("cpu"), "rademacher")
         est.append(((L @ g1 @ R.T) * (L @ g2 @ R.T)).sum())
     assert abs(torch.stack(est).mean() / exact - 1) < 0.15
+
+
+def _mean_ratio(o, i, p, ptype, trials=200, seed=7):
+    g = torch.Generator().manual_seed(seed)
+    g1 = torch.randn(o, i, generator=g)
+    g2 = g1 + 0.3 * torch.randn(o, i, generator=g)
+    true = float((g1 * g2).sum())
+    acc = 0.0
+    cpu = torch.device("cpu")
+    for t in range(trials):
+        L = create_projection_matrix(f"s{t}/left", p, o, torch.float32, cpu, ptype)
+        R = create_projection_matrix(f"s{t}/right", p, i, torch.float32, cpu, ptype)
+        acc += float(((L @ g1 @ R.T) * (L @ g2 @ R.T)).sum())
+    return acc / trials / true
+
+
+@pytest.mark.parametrize("ptype", ["rademacher", "normal"])
+def test_projection_scale_is_the_same_for_every_module_shape(ptype):
+    """Modules are summed into one score: a shape-dependent scale would reweight attention
+    against MLP layers."""
+    square, wide = _mean_ratio(32, 32, 16, ptype), _mean_ratio(32, 128, 16, ptype)
+    assert square == pytest.approx(1.0, rel=0.15) and wide == pytest.approx(1.0, rel=0.15)
+    A = create_projection_matrix("variance", 64, 256, torch.float32, torch.device("cpu"), ptype)
+    assert A.pow(2).mean().item() == pytest.approx(1 / 64, rel=0.1)  # entry variance 1 / output dim
+    assert (A.T @ A).diagonal().mean().item() == pytest.approx(1.0, rel=0.1)
+
+
+def test_one_matrix_per_module_summed_is_unbiased():
+    """The global projection applies one independent matrix per module and adds the results."""
+    dims, p = [64, 256], 32
+    g = torch.Generator().manual_seed(11)
+    xs = [torch.randn(d, generator=g) for d in dims]
+    ys = [x + 0.3 * torch.randn(d, generator=g) for x, d in zip(xs, dims)]
+    true = sum(float((x * y).sum()) for x, y in zip(xs, ys))
+    acc = 0.0
+    for t in range(200):
+        for k, d in enumerate(dims):
+            R = create_projection_matrix(f"g{k}_{t}", p, d, torch.float32, torch.device("cpu"), "rademacher")
+            acc += float(((xs[k] @ R.T) * (ys[k] @ R.T)).sum())
+    assert acc / 200 / true == pytest.approx(1.0, rel=0.15)
+
+
+def test_processor_saved_before_the_scale_option_loads_row_normalised(tmp_path):
+    import yaml
+
+    GradientProcessor(projection_dim=8).save(tmp_path)
+    cfg = yaml.safe_load((tmp_path / "processor_config.yaml").read_text())
+    assert cfg["projection_scale"] == "jl"
+    del cfg["projection_scale"]
+    (tmp_path / "processor_config.yaml").write_text(yaml.safe_dump(cfg))
+    assert GradientProcessor.load(tmp_path).projection_scale == "row_norm"
