@@ -68,3 +68,25 @@ def test_force_math_sdp_build_matches_default(tmp_path):
         torch.backends.cuda.enable_mem_efficient_sdp(mem)
     a, b = np.asarray(load_gradients(tmp_path / "default")), np.asarray(load_gradients(tmp_path / "math"))
     np.testing.assert_allclose(a, b, rtol=1e-4, atol=1e-6)
+
+
+def test_per_query_columns_are_saved_one_by_one_and_reused(tmp_path):
+    """Each query's backward sweep is written as soon as it finishes; a later run over the same
+    directory loads the finished columns instead of replaying them, and a padded query batch
+    still yields one column per real query."""
+    q3 = "synthetic:zipf?n=3&len=12&vocab=256&seed=1&min_len=12"  # 3 queries, batches of 4: one pad row
+    base = ["--model", MODEL, "--data.dataset", TRAIN, "--query.dataset", q3, "--batch_size", "4", "--lr", "1e-3",
+            "--nproc_per_node", "1", "--query_method", "none"]
+    run("magic", tmp_path / "r", *base)
+    files = sorted((tmp_path / "r" / "per_query").glob("q*.pt"))
+    assert [f.name for f in files] == ["q0.pt", "q1.pt", "q2.pt"]
+    first = load_scores(tmp_path / "r" / "scores")[:].astype(np.float64)
+    assert first.shape == (8, 3) and not np.allclose(first[:, 0], first[:, 1])
+    cols = [torch.load(f, weights_only=True) for f in files]
+    np.testing.assert_allclose(first, torch.stack(cols, -1).numpy().astype(np.float64), rtol=1e-3, atol=1e-9)
+    # mark a cached column: the second run must pick it up unchanged instead of recomputing it
+    torch.save(cols[1] * 0 + 7.0, files[1])
+    run("magic", tmp_path / "r", *base, "--resume", "true", "--overwrite", "true")
+    again = load_scores(tmp_path / "r" / "scores")[:].astype(np.float64)
+    assert np.allclose(again[:, 1], 7.0, rtol=1e-2)
+    np.testing.assert_allclose(again[:, [0, 2]], first[:, [0, 2]], rtol=1e-3, atol=1e-9)
