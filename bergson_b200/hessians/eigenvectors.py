@@ -25,7 +25,7 @@ from torch import Tensor
 
 from ..collector.collector import HookCollectorBase
 from ..utils.logger import get_logger
-from ..utils.streamed_safetensors import StreamedSafetensors
+from ..utils.streamed_safetensors import StreamedSafetensors, save_tensors
 from ..utils.utils import assert_type, get_device
 from .sharded_computation import ShardedMul, shard_bounds
 
@@ -133,10 +133,10 @@ class LambdaCollector(HookCollectorBase):
             if sc.dist:
                 dist.all_reduce(full, op=dist.ReduceOp.SUM)
             lo, hi = sc.shard_bounds(full.shape[0])
-            out[name] = full[lo:hi].contiguous().cpu()
+            out[name] = full[lo:hi].contiguous()
         d = os.path.join(self.path, self.output_subdir)
         os.makedirs(d, exist_ok=True)
-        save_file(out, os.path.join(d, f"shard_{self.rank}.safetensors"))
+        save_tensors(out, os.path.join(d, f"shard_{self.rank}.safetensors"))
 
 
 def _gather_and_shard_along_dim_0(input_dict, full_shape_per_key, dtype, rank, world_size, device, sink=None):

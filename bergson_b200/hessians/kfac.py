@@ -25,11 +25,11 @@ from dataclasses import dataclass
 import torch
 import torch.distributed as dist
 import torch.nn as nn
-from safetensors.torch import save_file
 from torch import Tensor
 
 from ..collector.collector import HookCollectorBase
 from ..ops import attribution
+from ..utils.streamed_safetensors import save_tensors
 from ..utils.utils import assert_type
 from .sharded_computation import ShardedMul
 
@@ -285,8 +285,9 @@ class _FactorCollector(HookCollectorBase):
         os.makedirs(a_dir, exist_ok=True)
         os.makedirs(g_dir, exist_ok=True)
         self.logger.info(f"Saving sharded covariance matrices to {a_dir} and {g_dir}")
-        save_file({k: v.cpu() for k, v in A.items()}, os.path.join(a_dir, f"shard_{self.rank}.safetensors"))
-        save_file({k: v.cpu() for k, v in S.items()}, os.path.join(g_dir, f"shard_{self.rank}.safetensors"))
+        # Written straight from the device, tensor by tensor, through pinned staging buffers.
+        save_tensors({k: v.contiguous() for k, v in A.items()}, os.path.join(a_dir, f"shard_{self.rank}.safetensors"))
+        save_tensors({k: v.contiguous() for k, v in S.items()}, os.path.join(g_dir, f"shard_{self.rank}.safetensors"))
 
 
 @dataclass(kw_only=True)

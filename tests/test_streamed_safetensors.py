@@ -41,3 +41,36 @@ def test_missing_or_wrong_tensor_is_an_error(tmp_path):
     with pytest.raises(RuntimeError, match="never written"):
         w.close()
     assert not path.exists() and not (tmp_path / "y.safetensors.partial").exists()
+
+
+def test_save_tensors_matches_save_file(tmp_path):
+    from bergson_b200.utils.streamed_safetensors import save_tensors
+
+    g = torch.Generator().manual_seed(1)
+    tensors = {f"t{i}": torch.randn(17 + i, 9, generator=g) for i in range(7)}
+    tensors["wide"] = torch.randn(3, 5, generator=g).to(torch.bfloat16)
+    for threads in (1, 4):
+        save_tensors(tensors, str(tmp_path / f"x{threads}.safetensors"), threads=threads)
+        back = load_file(str(tmp_path / f"x{threads}.safetensors"))
+        assert all(torch.equal(back[k], v) for k, v in tensors.items()) and set(back) == set(tensors)
+
+
+@pytest.mark.gpu
+def test_device_tensors_go_through_pinned_staging(tmp_path):
+    if not torch.cuda.is_available():
+        pytest.skip("needs a GPU")
+    from bergson_b200.utils import streamed_safetensors as ss
+
+    g = torch.Generator("cuda").manual_seed(2)
+    # larger than one staging chunk, odd sizes, a strided view, several dtypes
+    tensors = {"big": torch.randn(3000, 3001, device="cuda", generator=g),
+               "bf": torch.randn(1025, 513, device="cuda", generator=g).to(torch.bfloat16),
+               "view": torch.randn(64, 200, device="cuda", generator=g)[:, ::2].contiguous(),
+               "idx": torch.arange(1000, device="cuda"), "host": torch.randn(5, 5)}
+    assert tensors["big"].numel() * 4 > 2 * ss._CHUNK
+    for threads in (1, 3):
+        ss.save_tensors(tensors, str(tmp_path / f"d{threads}.safetensors"), threads=threads)
+        back = load_file(str(tmp_path / f"d{threads}.safetensors"))
+        for k, v in tensors.items():
+            assert torch.equal(back[k], v.cpu()), k
+    assert 0 < ss._n_slots <= ss._MAX_SLOTS and ss._free_slots.qsize() == ss._n_slots  # every slot was returned
