@@ -9,13 +9,13 @@ from pathlib import Path
 import torch
 import torch.distributed as dist
 from safetensors import safe_open
-from safetensors.torch import save_file
 
 from ..config import DistributedConfig
 from ..distributed import init_dist, launch_distributed_run
 from ..hessians.eigenvectors import compute_eigendecomposition
 from ..utils.logger import get_logger
 from ..utils.step_state import partial_path, prepare_step, promote_step
+from ..utils.streamed_safetensors import save_tensors
 from ..utils.utils import get_device
 from .precompute_checkpoints import DOCUMENTS_PROCESSED_FILENAME
 
@@ -44,7 +44,7 @@ def _sum_my_shard(in_paths: list[Path], out_path: Path, device: str, divisor: fl
         for v in acc.values():
             v.div_(divisor)
     out_path.parent.mkdir(parents=True, exist_ok=True)
-    save_file({k: v.cpu() for k, v in acc.items()}, str(out_path))
+    save_tensors(acc, str(out_path))  # straight from the device when the sums live there
 
 
 def _sum_dirs_worker(rank, local_rank, world_size, input_dirs: list[Path], output_dir: Path, divisor: float) -> None:
