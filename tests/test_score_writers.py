@@ -75,3 +75,34 @@ def test_streaming_writer_resumes_an_existing_store(tmp_path):
     fresh = MemmapSequenceScoreWriter(tmp_path, 3, 2, dtype=torch.float32, distributed=False, overwrite=True)
     fresh.flush()
     assert not np.asarray(load_scores(tmp_path).mmap["written_0"]).any()
+
+
+def _rank0_saves(rank, local_rank, world, out_dir):
+    """Only rank 0 saves; then every rank meets at a barrier.  A collective hidden inside the
+    savers would pair with that barrier on the other rank and leave the group out of step."""
+    from pathlib import Path
+
+    import torch.distributed as dist
+
+    from bergson_b200.distributed import init_dist
+    from bergson_b200.score.score_writer import save_token_scores
+
+    init_dist(rank, local_rank, world)
+    if rank == 0:
+        save_sequence_scores(Path(out_dir) / "seq", np.arange(8, dtype=np.float32)[:, None])
+        save_token_scores(Path(out_dir) / "tok", np.arange(8, dtype=np.float32)[:, None], np.array([0, 3, 8], dtype=np.int64))
+    dist.barrier()
+    t = torch.tensor([float(rank)])
+    dist.all_reduce(t)
+    assert float(t) == 1.0  # the group is still in step
+
+
+def test_one_shot_savers_are_not_collective(tmp_path):
+    from bergson_b200.config import DistributedConfig
+    from bergson_b200.distributed import launch_distributed_run
+
+    launch_distributed_run("savers", _rank0_saves, [str(tmp_path)], DistributedConfig(nproc_per_node=2))
+    seq = load_scores(tmp_path / "seq")
+    assert seq.is_written() and np.asarray(seq[:]).ravel().tolist() == list(range(8))
+    tok = load_scores(tmp_path / "tok")
+    assert tok.is_written() and tok.offsets.tolist() == [0, 3, 8] and np.asarray(tok[3:8]).ravel().tolist() == [3, 4, 5, 6, 7]
