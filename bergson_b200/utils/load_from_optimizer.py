@@ -11,6 +11,7 @@ moments in the same layout (reference ``bergson/utils/load_from_optimizer.py``).
 from __future__ import annotations
 
 import re
+from enum import Enum
 from pathlib import Path
 
 import torch
@@ -59,6 +60,30 @@ def _second_moment(entry) -> tuple[str, object] | None:
     if isinstance(bnb, dict) and "state2" in bnb:
         return "adam", bnb["state2"]
     return None
+
+
+class OptimizerStateFormat(Enum):
+    """How one parameter's second moment is stored: a full tensor (Adam, 8-bit Adam, Adafactor's 1-D
+    parameters) or Adafactor's row / column factors."""
+
+    UNFACTORED = 1
+    FACTORED = 2
+
+
+def get_optimizer_state_format(param_state) -> OptimizerStateFormat | None:
+    """Format of one optimizer-state entry, None when it carries no second moment."""
+    sm = _second_moment(param_state)
+    if sm is None:
+        return None
+    return OptimizerStateFormat.UNFACTORED if sm[0] == "adam" else OptimizerStateFormat.FACTORED
+
+
+def get_unfactored_second_moment(state: dict) -> torch.Tensor:
+    """The full second-moment tensor of an UNFACTORED entry."""
+    sm = _second_moment(state)
+    if sm is None or sm[0] != "adam":
+        raise KeyError("entry has no unfactored second moment (exp_avg_sq / 8-bit state2)")
+    return sm[1]  # type: ignore[return-value]
 
 
 def _base_model_prefix(model) -> str:
@@ -133,6 +158,49 @@ def _bias_moment(layer_name: str, index_to_name: dict[int, str], state: dict, in
     return None
 
 
+def get_normalizers(optimizer_state: dict, target_param_index_to_name: dict[int, str], target_modules: set[str] | None,
+                    adapter_suffix: str, include_bias: bool, device, base_prefix: str = "", model=None) -> dict[str, Normalizer]:
+    """Normalisers of every ``<layer>.weight`` entry of ``optimizer_state["state"]``, keyed by the
+    module name relative to the base model (+ ``adapter_suffix``).  An entry's recorded
+    ``param_name`` wins over its positional index; ``model`` (optional) tells which layers store
+    their weight transposed."""
+    index_to_name = target_param_index_to_name
+    out: dict[str, Normalizer] = {}
+    for idx, entry in optimizer_state["state"].items():
+        name = (entry.get("param_name") if isinstance(entry, dict) else None) or index_to_name.get(int(idx))
+        if name is None or not name.endswith(".weight"):
+            continue
+        layer = name.removesuffix(".weight")
+        module_name = layer.removeprefix("base_model.").removeprefix(base_prefix) + adapter_suffix
+        if target_modules is not None and module_name not in target_modules:
+            continue
+        sm = _second_moment(entry)
+        if sm is None:
+            print("Unrecognized format, skipping normalizer for param_idx", idx)
+            continue
+        bias = _bias_moment(layer, index_to_name, optimizer_state["state"], include_bias)
+        bias = bias.to(device) if bias is not None else None
+        try:
+            module = model.get_submodule(layer) if model is not None else None
+        except AttributeError:
+            module = None
+        transposed = module is not None and isinstance(module, LayerAdapter.supported_modules) and \
+            LayerAdapter.weight_transposed(module)
+        if sm[0] == "adam":
+            v = sm[1]
+            if v.ndim != 2:
+                continue
+            out[module_name] = AdamNormalizer((v.T.contiguous() if transposed else v).to(device), bias)
+        else:
+            row, col = sm[1]
+            if row.ndim != 1 or col is None:
+                continue
+            if transposed:  # factored over the stored [in, out] layout
+                row, col = col, row
+            out[module_name] = AdafactorNormalizer(row.to(device), col.to(device), bias)
+    return out
+
+
 def load_from_optimizer(model, optimizer_state: str, include_bias: bool = False,
                         target_modules: set[str] | None = None) -> dict[str, Normalizer]:
     """Normalisers for every Linear whose weight has second moments in the checkpoint."""
@@ -151,39 +219,8 @@ def load_from_optimizer(model, optimizer_state: str, include_bias: bool = False,
         index_to_name = optimizer_param_index_to_name(opt, model)
         base_prefix = _base_model_prefix(model)
     device = next(model.parameters()).device
-    out: dict[str, Normalizer] = {}
-    for idx, entry in opt["state"].items():
-        name = (entry.get("param_name") if isinstance(entry, dict) else None) or index_to_name.get(int(idx))
-        if name is None or not name.endswith(".weight"):
-            continue
-        layer = name.removesuffix(".weight")
-        module_name = layer.removeprefix("base_model.").removeprefix(base_prefix) + adapter_suffix
-        if target_modules is not None and module_name not in target_modules:
-            continue
-        sm = _second_moment(entry)
-        if sm is None:
-            print("Unrecognized format, skipping normalizer for param_idx", idx)
-            continue
-        bias = _bias_moment(layer, index_to_name, opt["state"], include_bias)
-        bias = bias.to(device) if bias is not None else None
-        try:
-            module = model.get_submodule(layer)
-        except AttributeError:
-            module = None
-        transposed = module is not None and isinstance(module, LayerAdapter.supported_modules) and \
-            LayerAdapter.weight_transposed(module)
-        if sm[0] == "adam":
-            v = sm[1]
-            if v.ndim != 2:
-                continue
-            out[module_name] = AdamNormalizer((v.T.contiguous() if transposed else v).to(device), bias)
-        else:
-            row, col = sm[1]
-            if row.ndim != 1 or col is None:
-                continue
-            if transposed:  # factored over the stored [in, out] layout
-                row, col = col, row
-            out[module_name] = AdafactorNormalizer(row.to(device), col.to(device), bias)
+    out = get_normalizers(opt, index_to_name, target_modules, adapter_suffix, include_bias, device,
+                          base_prefix=base_prefix, model=model)
     assert out, (f"No optimizer second moments found in '{optimizer_state}'. Ensure the checkpoint was saved from "
                  "an Adam-family or Adafactor optimizer.")
     kinds = ", ".join(sorted({type(n).__name__ for n in out.values()}))

@@ -28,3 +28,21 @@ def extract_peft_target_modules(model) -> set[str]:
             except AttributeError:
                 print(f"Adapter parameter '{candidate}' not found in the model.")
     return out
+
+
+def detect_peft_modules(model) -> set[str]:
+    """Like ``extract_peft_target_modules`` but strict: an adapter parameter without a matching
+    sub-module is an error rather than a printed note (reference ``bergson/utils/peft.py:5-30``)."""
+    from peft import get_peft_model_state_dict
+
+    out: set[str] = set()
+    state = get_peft_model_state_dict(model)
+    for adapter in model.peft_config:
+        for name in state:
+            candidate = f"{name.removesuffix('.weight')}.{adapter}".removeprefix("base_model.")
+            try:
+                model.get_submodule(candidate)
+            except AttributeError as e:
+                raise RuntimeError(f"Adapter parameter '{candidate}' not found in the model.") from e
+            out.add(candidate)
+    return out

@@ -69,3 +69,54 @@ def ensure_exported(trainer, state, run_path: str, cfg=None) -> list[tuple[int, 
             export_checkpoint(trainer, state, path, dst, cfg)
         out.append((step, dst))
     return out
+
+
+def sorted_dcp_checkpoints(checkpoints_dir: str | Path) -> list[tuple[int, Path]]:
+    """``(step, path)`` of every ``step_<i>[.ckpt]`` directory, ascending
+    (reference ``bergson/utils/trainer_export.py:26-39``)."""
+    checkpoints_dir = Path(checkpoints_dir)
+    if not checkpoints_dir.is_dir():
+        raise NotADirectoryError(f"{checkpoints_dir} is not a directory")
+    found = []
+    for entry in checkpoints_dir.iterdir():
+        stem = entry.name.removesuffix(".ckpt").removeprefix("step_")
+        if entry.is_dir() and entry.name.startswith("step_") and stem.isdigit():
+            found.append((int(stem), entry))
+    return sorted(found, key=lambda pair: pair[0])
+
+
+def export_checkpoints(run_path: str | Path, out_dir: str | Path | None = None, *, training_cfg=None,
+                       steps: list[int] | None = None, overwrite: bool = False) -> list[Path]:
+    """Export the trainer checkpoints of a finished run to ``checkpoint-<i>/`` directories (model
+    in ``save_pretrained`` layout, ``optimizer.pt`` copied along), in step order, without a
+    trainer in hand: model and state are rebuilt from the run's recorded config
+    (reference ``bergson/utils/trainer_export.py:42-113``).  ``out_dir`` defaults to the run
+    directory itself, where ``ensure_exported`` and the SOURCE pipeline look."""
+    from ..approx_unrolling.train_cfg_io import load_training_config
+    from ..magic.trainer import prepare_trainer
+
+    run_path = Path(run_path)
+    out_dir = Path(out_dir) if out_dir is not None else run_path
+    cfg = training_cfg if training_cfg is not None else load_training_config(run_path)
+    available = [(s, p) for s, p in sorted_dcp_checkpoints(run_path / "checkpoints") if (p / ".metadata").exists()]
+    if not available:
+        raise FileNotFoundError(f"No complete step_<i>.ckpt directories under {run_path / 'checkpoints'}; "
+                                "train with a save_mode that writes checkpoints.")
+    if steps is not None:
+        by_step = dict(available)
+        missing = [s for s in steps if s not in by_step]
+        if missing:
+            raise FileNotFoundError(f"Requested steps {missing} were not saved; available: {[s for s, _ in available]}")
+        available = [(s, by_step[s]) for s in sorted(steps)]
+    clashes = [out_dir / f"checkpoint-{s}" for s, _ in available if (out_dir / f"checkpoint-{s}").exists()]
+    if clashes and not overwrite:
+        raise FileExistsError(f"{[str(c) for c in clashes]} already exist; pass overwrite=True.")
+    trainer, state, _ = prepare_trainer(cfg, rank=0, schedule=lambda step: 0.0)
+    exported = []
+    for step, ckpt in available:
+        dst = out_dir / f"checkpoint-{step}"
+        if dst.exists():
+            shutil.rmtree(dst)
+        export_checkpoint(trainer, state, str(ckpt), str(dst), cfg)
+        exported.append(dst)
+    return exported

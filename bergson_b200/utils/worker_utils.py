@@ -169,6 +169,13 @@ def _load_hf_model(cfg: ModelConfig, dtype, device, device_map_auto: bool, model
     return model, target_modules
 
 
+def extract_peft_target_modules(model) -> set[str]:
+    """Adapter module names of a PEFT model (needs the optional ``peft`` package)."""
+    from .peft import extract_peft_target_modules as impl
+
+    return impl(model)
+
+
 def estimate_advantage(ds: Dataset, cfg: DataConfig):
     """Dr. GRPO advantage: reward minus the mean reward of rollouts sharing the prompt."""
     import pandas as pd

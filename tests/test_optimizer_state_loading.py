@@ -141,3 +141,24 @@ def test_missing_files_and_empty_states(tmp_path):
     torch.save({"state": {0: {"momentum_buffer": torch.rand(6, 4)}}, "param_groups": [{"params": [0]}]}, tmp_path / "sgd.pt")
     with pytest.raises(AssertionError, match="No optimizer second moments"):
         load_from_optimizer(model, str(tmp_path / "sgd.pt"))
+
+
+def test_entry_format_helpers():
+    from bergson_b200.utils.load_from_optimizer import (
+        OptimizerStateFormat, get_normalizers, get_optimizer_state_format, get_unfactored_second_moment)
+
+    v = torch.rand(6, 4)
+    assert get_optimizer_state_format({"exp_avg_sq": v}) is OptimizerStateFormat.UNFACTORED
+    assert get_optimizer_state_format({"exp_avg_sq_row": torch.rand(6), "exp_avg_sq_col": torch.rand(4)}) is OptimizerStateFormat.FACTORED
+    bnb = {"__bnb_optimizer_quant_state__": {"state2": v}}
+    assert get_optimizer_state_format(bnb) is OptimizerStateFormat.UNFACTORED
+    assert get_optimizer_state_format({"momentum_buffer": v}) is None and get_optimizer_state_format("nope") is None
+    assert get_unfactored_second_moment({"exp_avg_sq": v}) is v and get_unfactored_second_moment(bnb) is v
+    with pytest.raises(KeyError):
+        get_unfactored_second_moment({"exp_avg_sq_row": torch.rand(6)})
+    sd = {"state": {0: {"exp_avg_sq": v}, 1: {"exp_avg_sq": torch.rand(6)}, 2: {"exp_avg_sq": torch.rand(3, 6), "param_name": "model.out.weight"}}}
+    names = {0: "model.fc.weight", 1: "model.fc.bias", 2: "ignored.by.param_name"}
+    got = get_normalizers(sd, names, None, ".default", True, "cpu", base_prefix="model.")
+    assert set(got) == {"fc.default", "out.default"}  # relative to the base model, adapter suffix appended
+    torch.testing.assert_close(got["fc.default"].bias_avg_sq, sd["state"][1]["exp_avg_sq"])
+    assert set(get_normalizers(sd, names, {"out.default"}, ".default", False, "cpu", base_prefix="model.")) == {"out.default"}
