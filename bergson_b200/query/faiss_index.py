@@ -13,6 +13,7 @@ from __future__ import annotations
 import json
 import math
 from pathlib import Path
+from typing import Protocol
 
 import numpy as np
 import torch
@@ -31,6 +32,76 @@ except ImportError:  # pragma: no cover - depends on the environment
     HAVE_FAISS = False
 
 
+class Index(Protocol):
+    """What a shard has to offer, whichever backend built it."""
+
+    def search(self, x: np.ndarray, k: int) -> tuple[np.ndarray, np.ndarray]: ...
+
+    @property
+    def ntotal(self) -> int: ...
+
+    def train(self, x: np.ndarray) -> None: ...
+
+    def add(self, x: np.ndarray) -> None: ...
+
+
+def validate_ram(batch: np.ndarray, max_shard_size: int) -> None:
+    """Refuse to build when the largest shard (``max_shard_size`` rows of the width and type of
+    ``batch``, widened to fp32 for the index) cannot fit into the memory that is free now."""
+    import psutil
+
+    free_gb = psutil.virtual_memory().available / 2**30
+    per_row = max(batch.nbytes / max(batch.shape[0], 1), 4 * batch.shape[1])
+    need_gb = max_shard_size * per_row / 2**30
+    print(f"Largest index shard needs about {need_gb:.2f} GB of host memory; {free_gb:.2f} GB are free")
+    assert need_gb <= free_gb, "Not enough RAM to build index."
+
+
+def normalize_grads(grads: np.ndarray, device: str, batch_size: int) -> np.ndarray:
+    """Rows scaled to unit norm (zero rows stay zero), ``batch_size`` rows at a time on ``device``."""
+    out = np.empty(grads.shape, dtype=np.float32)
+    for lo in range(0, grads.shape[0], batch_size):
+        out[lo : lo + batch_size] = _prepare(grads[lo : lo + batch_size], {}, device, True, {})
+    return out
+
+
+def gradients_loader(root_dir: Path):
+    """``(memory-mapped gradients, module names)`` for the store under ``root_dir``, or for each
+    ``*shard*`` sub-directory (in name order) when the store was written in several parts."""
+    root_dir = Path(root_dir)
+
+    def one(d: Path):
+        with open(d / "info.json") as f:
+            return load_gradients(d), list(json.load(f)["grad_sizes"])
+
+    if (root_dir / "info.json").exists():
+        yield one(root_dir)
+    else:
+        for path in sorted(root_dir.iterdir()):
+            if path.is_dir() and "shard" in path.name:
+                yield one(path)
+
+
+def index_to_device(index, device: str):
+    """The shard on ``device``: an in-tree index moves its tensors, a FAISS index is cloned to the
+    GPUs (``cuda`` = all visible ones, ``cuda:<i>`` = that one) or left alone for ``cpu``."""
+    if isinstance(index, NativeIndex):
+        dev = torch.device(device)
+        if index.device != dev:
+            for name in ("vectors", "ids", "centroids", "codebooks"):
+                t = getattr(index, name)
+                if isinstance(t, torch.Tensor):
+                    setattr(index, name, t.to(dev))
+            index._row_list = None
+            index.device = dev
+        return index
+    if device == "cpu" or faiss is None or not hasattr(faiss, "index_cpu_to_all_gpus"):
+        return index
+    if ":" in device:
+        return faiss.index_cpu_to_gpu(faiss.StandardGpuResources(), int(device.split(":")[1]), index)
+    return faiss.index_cpu_to_all_gpus(index)
+
+
 def _prepare(block: np.ndarray, sizes: dict[str, int], device, unit_norm: bool, h_inv: dict) -> np.ndarray:
     x = numpy_to_tensor(np.ascontiguousarray(block)).to(device=device, dtype=torch.float32)
     if h_inv:
@@ -40,6 +111,25 @@ def _prepare(block: np.ndarray, sizes: dict[str, int], device, unit_norm: bool, 
     if unit_norm:
         x = torch.nan_to_num(x / x.norm(dim=1, keepdim=True), nan=0.0, posinf=0.0, neginf=0.0)
     return x.cpu().numpy()
+
+
+class _Concatenated:
+    """Row-wise concatenation of several memory-mapped stores, sliced like one array."""
+
+    def __init__(self, parts: list):
+        self.parts = parts
+        self.starts = np.cumsum([0] + [p.shape[0] for p in parts])
+        self.shape = (int(self.starts[-1]), parts[0].shape[1])
+
+    def __getitem__(self, key):
+        assert isinstance(key, slice) and key.step in (None, 1)
+        lo, hi, _ = key.indices(self.shape[0])
+        out = []
+        for p, s in zip(self.parts, self.starts[:-1]):
+            a, b = max(lo - s, 0), min(hi - s, p.shape[0])
+            if a < b:
+                out.append(np.asarray(p[a:b]))
+        return np.concatenate(out) if out else np.zeros((0, self.shape[1]), self.parts[0].dtype)
 
 
 class FaissIndex:
@@ -60,8 +150,8 @@ class FaissIndex:
                 idx = faiss.read_index(str(self.path / f"{i}.faiss"), flags)
                 if hasattr(idx, "nprobe"):
                     idx.nprobe = self.nprobe
-                if device != "cpu" and not mmap_index and hasattr(faiss, "index_cpu_to_all_gpus"):
-                    idx = faiss.index_cpu_to_all_gpus(idx)
+                if device != "cpu" and not mmap_index:
+                    idx = index_to_device(idx, device)
                 self.shards.append(idx)
                 self.sizes.append(idx.ntotal)
             elif self.backend == "native":
@@ -82,11 +172,17 @@ class FaissIndex:
     @staticmethod
     def create_index(index_path: Path, faiss_path: Path, cfg: FaissConfig, device: str, unit_norm: bool, h_inv: dict):
         faiss_path.mkdir(parents=True, exist_ok=True)
-        mm = load_gradients(index_path)
-        with open(Path(index_path) / "info.json") as f:
+        parts = list(gradients_loader(Path(index_path)))
+        if not parts:
+            raise FileNotFoundError(f"No gradient store under {index_path}")
+        info_dir = Path(index_path) if (Path(index_path) / "info.json").exists() else \
+            sorted(p for p in Path(index_path).iterdir() if p.is_dir() and "shard" in p.name)[0]
+        with open(info_dir / "info.json") as f:
             sizes = json.load(f)["grad_sizes"]
+        mm = parts[0][0] if len(parts) == 1 else _Concatenated([m for m, _ in parts])
         n = mm.shape[0]
         per = math.ceil(n / cfg.num_shards)
+        validate_ram(np.asarray(mm[: min(n, 16)]), per)
         backend = "faiss" if HAVE_FAISS else "native"
         factory = None if HAVE_FAISS else parse_factory(cfg.index_factory)  # raises for unsupported strings
         for s in range(cfg.num_shards):

@@ -172,3 +172,39 @@ def test_masked_scan_and_per_list_loop_find_the_same_neighbours(spec):
     idx.nprobe, idx.dense_scan = 1, True
     d, i = idx.search(q[:3], 2000)  # more than one list holds: padded the same way
     assert (i == -1).any() and np.isneginf(d[i == -1]).all() and (i[np.isfinite(d)] >= 0).all()
+
+
+def test_store_helpers_and_multi_part_stores(tmp_path):
+    import json
+
+    from bergson_b200.config import FaissConfig
+    from bergson_b200.query.faiss_index import (
+        HAVE_FAISS, FaissIndex, gradients_loader, index_to_device, normalize_grads, validate_ram)
+
+    x, q = _clustered(n=900)
+    unit = normalize_grads(np.vstack([3 * x[:5], np.zeros((1, x.shape[1]), np.float32)]), "cpu", batch_size=4)
+    np.testing.assert_allclose(np.linalg.norm(unit[:5], axis=1), 1.0, rtol=1e-5)
+    assert np.abs(unit[5]).sum() == 0  # a zero row stays zero instead of becoming NaN
+    validate_ram(x[:8], 1000)
+    with pytest.raises(AssertionError, match="Not enough RAM"):
+        validate_ram(x[:8], 10**15)
+    # a store written in three parts: the loader yields them in order and the index spans all of them
+    root = tmp_path / "store"
+    for i, rows in enumerate(np.array_split(x, 3)):
+        d = root / f"shard_{i}"
+        d.mkdir(parents=True)
+        rows.astype(np.float16).tofile(d / "gradients.bin")
+        (d / "info.json").write_text(json.dumps({"grad_sizes": {"w": x.shape[1]}, "num_grads": len(rows), "base_dtype": "float16"}))
+    parts = list(gradients_loader(root))
+    assert [m.shape[0] for m, _ in parts] == [300, 300, 300] and parts[0][1] == ["w"]
+    if HAVE_FAISS:
+        return
+    FaissIndex.create_index(root, tmp_path / "ann", FaissConfig(index_factory="IVF4,SQfp16", num_shards=2, nprobe=4), "cpu",
+                            unit_norm=False, h_inv={})
+    idx = FaissIndex(tmp_path / "ann")
+    assert idx.ntotal == 900
+    _, i = idx.search(q, 5)
+    _, truth = _exact(x.astype(np.float16).astype(np.float32), q, 5)
+    assert _recall(i, truth) > 0.95
+    shard = index_to_device(idx.shards[0], "cpu")
+    assert shard is idx.shards[0] and shard.device == torch.device("cpu")
