@@ -164,3 +164,22 @@ def launch_distributed_run(process_name: str, worker, const_worker_args: list[An
             failed = p.exitcode
     if failed is not None:
         raise RuntimeError(f"{process_name} child exited with code {failed}")
+
+
+def simple_dist_worker(rank: int, local_rank: int, world_size: int, dataset, worker) -> None:
+    """One rank of ``dist_main``: join the process group, then ``worker(rank, world_size, dataset)``
+    (the launcher tears the group down afterwards)."""
+    init_dist(rank, local_rank, world_size)
+    worker(rank, world_size, dataset)
+
+
+def dist_main(dataset, worker, nproc: int | None = None) -> None:
+    """Run ``worker(rank, world_size, dataset)`` once per visible GPU (``nproc`` overrides the
+    count); a single device runs it in this process, which keeps a debugger attached
+    (reference ``bergson/distributed.py:215-250``).  ``worker`` must be importable by the
+    spawned children (a module-level function)."""
+    world = nproc if nproc is not None else torch.cuda.device_count()
+    if world <= 1:
+        worker(0, 1, dataset)
+        return
+    launch_distributed_run("dist_main", simple_dist_worker, [dataset, worker], DistributedConfig(nproc_per_node=world))

@@ -59,3 +59,32 @@ def test_parents_wait_for_the_capped_build(tmp_path):
     port = find_free_port()
     mp.spawn(_node_parent, args=(2, port, tmp_path / "run.part", tmp_path / "run"), nprocs=2, join=True)
     assert (tmp_path / "run" / "config.yaml").read_text() == "data"
+
+
+def _count_rows(rank, world, dataset):
+    import json
+
+    import torch
+    import torch.distributed as dist
+
+    mine = torch.tensor([float(len(dataset["rows"][rank::world]))])
+    dist.all_reduce(mine)
+    with open(f"{dataset['out']}/rank{rank}.json", "w") as f:
+        json.dump({"world": world, "total": float(mine)}, f)
+
+
+def _single(rank, world, dataset):
+    dataset["seen"].append((rank, world))
+
+
+def test_dist_main_runs_a_worker_per_rank(tmp_path):
+    import json
+
+    from bergson_b200.distributed import dist_main
+
+    seen = {"seen": []}
+    dist_main(seen, _single, nproc=1)  # one device: in this process, no process group
+    assert seen["seen"] == [(0, 1)]
+    dist_main({"rows": list(range(7)), "out": str(tmp_path)}, _count_rows, nproc=2)
+    got = [json.load(open(tmp_path / f"rank{r}.json")) for r in range(2)]
+    assert got == [{"world": 2, "total": 7.0}] * 2
