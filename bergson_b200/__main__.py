@@ -8,6 +8,17 @@ import os
 import sys
 
 
+class Main:
+    """A parsed command line: ``Main(command).execute()`` runs it
+    (reference ``bergson/__main__.py:30-53``)."""
+
+    def __init__(self, command):
+        self.command = command
+
+    def execute(self):
+        self.command.execute()
+
+
 def run_config(config_path: str, registry: dict[str, type]) -> None:
     from .config.config_io import parse_steps, read_config, save_pipeline_config
 
@@ -34,7 +45,7 @@ def main(argv: list[str] | None = None):
     if config_path is not None:
         run_config(config_path, COMMANDS)
         return
-    parse_command(COMMANDS, args, prog="bergson").execute()
+    Main(parse_command(COMMANDS, args, prog="bergson")).execute()
 
 
 if __name__ == "__main__":

@@ -295,3 +295,17 @@ def run_magic(run_cfg: TrainingConfig, *, score_path: str = ""):
         flag.touch()
     launch_distributed_run("run_magic", worker, [train_ds, query_ds, train_n, query_n, run_cfg, score_path],
                            run_cfg.distributed)
+
+
+def main(argv: list[str] | None = None) -> None:
+    """``python -m bergson_b200.magic.cli <run_path> --flags``: the ``magic`` command on its own
+    (reference ``bergson/magic/cli.py:679-685``)."""
+    import sys
+
+    from ..__main__ import main as run_command
+
+    run_command(["magic", *(sys.argv[1:] if argv is None else argv)])
+
+
+if __name__ == "__main__":
+    main()
