@@ -151,6 +151,23 @@ class TrainerState:
                             {k: mv(b) for k, b in self.buffers.items()}, self.batch_index,
                             self.cuda_rng_state.clone(), self.cpu_rng_state.clone())
 
+    @contextmanager
+    def activate(self, model: nn.Module):
+        """Run ``model`` with this state's parameters and buffers in place of its own and with
+        this state's random-number streams; yields the tensors acting as parameters (their
+        autograd history intact, so gradients taken inside reach the state).  The model's own
+        parameters and the ambient random state come back on exit
+        (reference ``bergson/magic/trainer.py:302-310``)."""
+        from .swap import swap_parameters
+
+        ambient = rng_snapshot()
+        rng_restore((self.cpu_rng_state, self.cuda_rng_state))
+        try:
+            with swap_parameters(model, self.params, self.buffers, strict=True) as active:
+                yield active
+        finally:
+            rng_restore(ambient)
+
     def state_dict(self) -> dict:
         """Flat dict: parameter and buffer names, ``.batch_index``, ``.cuda_rng_state``,
         ``.cpu_rng_state`` and ``opt_state/<path>`` leaves."""

@@ -141,7 +141,7 @@ class FaissIndex:
             meta = json.load(f)
         self.ordered_modules = meta["ordered_modules"]
         self.backend = meta.get("backend", "faiss")
-        self.nprobe = meta.get("nprobe", 10)
+        self._nprobe = meta.get("nprobe", 10)
         self.shards = []
         self.sizes = []
         for i in range(meta["num_shards"]):
@@ -168,6 +168,18 @@ class FaissIndex:
     @property
     def ntotal(self) -> int:
         return int(sum(self.sizes))
+
+    @property
+    def nprobe(self) -> int:
+        """Inverted lists probed per query; setting it reaches every shard that has lists."""
+        return self._nprobe
+
+    @nprobe.setter
+    def nprobe(self, value: int) -> None:
+        self._nprobe = int(value)
+        for shard in self.shards:
+            if hasattr(shard, "nprobe"):
+                shard.nprobe = self._nprobe
 
     @staticmethod
     def create_index(index_path: Path, faiss_path: Path, cfg: FaissConfig, device: str, unit_norm: bool, h_inv: dict):

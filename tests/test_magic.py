@@ -207,3 +207,32 @@ def test_lazy_gather_matches_functional_call_to_second_order():
             torch.testing.assert_close(a, b, rtol=1e-6, atol=1e-9)
     # The module's own parameters are back in place.
     assert all(isinstance(p, torch.nn.Parameter) for p in model.parameters())
+
+
+def test_state_activation_swaps_parameters_and_random_streams():
+    trainer, state, data, ds = _setup(n=4, bs=2)
+    model = trainer.model
+    own = {k: p.detach().clone() for k, p in model.named_parameters()}
+    shifted = state.to("cpu")
+    for p in shifted.params.values():
+        p.add_(0.5)
+    shifted.params = {k: p.requires_grad_(True) for k, p in shifted.params.items()}
+    x = torch.tensor(ds["input_ids"][:2])
+    before = torch.random.get_rng_state()
+    with shifted.activate(model) as params:
+        assert set(params) == set(shifted.params)
+        loss = model(x, labels=x).loss
+        grads = torch.autograd.grad(loss, list(params.values()), allow_unused=True)
+        assert any(g is not None and g.abs().sum() > 0 for g in grads)  # gradients reach the state's tensors
+        assert torch.equal(torch.random.get_rng_state(), shifted.cpu_rng_state)
+        torch.rand(3)  # consuming randomness inside must not leak out
+    assert torch.equal(torch.random.get_rng_state(), before)
+    for k, p in model.named_parameters():
+        assert torch.equal(p, own[k]) and isinstance(p, torch.nn.Parameter)
+    plain = model(x, labels=x).loss
+    assert not torch.allclose(plain, loss.detach().to(plain.dtype))
+    with pytest.raises(KeyError):
+        partial = shifted.to("cpu")
+        partial.params.pop(next(iter(partial.params)))
+        with partial.activate(model):
+            pass

@@ -208,3 +208,27 @@ def test_store_helpers_and_multi_part_stores(tmp_path):
     assert _recall(i, truth) > 0.95
     shard = index_to_device(idx.shards[0], "cpu")
     assert shard is idx.shards[0] and shard.device == torch.device("cpu")
+
+
+def test_nprobe_can_be_changed_after_loading(tmp_path):
+    import json
+
+    from bergson_b200.config import FaissConfig
+    from bergson_b200.query.faiss_index import HAVE_FAISS, FaissIndex
+
+    if HAVE_FAISS:
+        pytest.skip("the faiss package provides these factories")
+    x, q = _clustered(n=1200)
+    store = tmp_path / "store"
+    store.mkdir()
+    x.astype(np.float16).tofile(store / "gradients.bin")
+    (store / "info.json").write_text(json.dumps({"grad_sizes": {"w": x.shape[1]}, "num_grads": len(x), "base_dtype": "float16"}))
+    FaissIndex.create_index(store, tmp_path / "ann", FaissConfig(index_factory="IVF16,Flat", num_shards=2, nprobe=1), "cpu",
+                            unit_norm=False, h_inv={})
+    idx = FaissIndex(tmp_path / "ann")
+    assert idx.nprobe == 1 and all(s.nprobe == 1 for s in idx.shards)
+    _, truth = _exact(x.astype(np.float16).astype(np.float32), q, 10)
+    low = _recall(idx.search(q, 10)[1], truth)
+    idx.nprobe = 16
+    assert all(s.nprobe == 16 for s in idx.shards)
+    assert _recall(idx.search(q, 10)[1], truth) > max(low, 0.99)
