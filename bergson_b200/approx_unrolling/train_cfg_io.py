@@ -52,6 +52,10 @@ def infer_trainer_run(checkpoints: list[str]) -> str:
 
 
 def resolve(cfg: ApproxUnrollingConfig) -> ApproxUnrollingConfig:
+    from ..utils.trainer_export import ensure_exported
+
+    # Raw trainer checkpoints (step_<n>.ckpt) are exported to model directories on demand.
+    cfg.checkpoints = ensure_exported([str(c) for c in cfg.checkpoints])
     run = infer_trainer_run([str(c) for c in cfg.checkpoints])
     tcfg = None
     if run:

@@ -365,13 +365,28 @@ def adjust_lr(lr: float, mode: str | None, shape) -> float:
     return lr
 
 
-def muon(lr: Schedule | float, momentum: float = 0.95, adamw_betas=(0.9, 0.999), adamw_eps: float = 1e-8,
-         adamw_eps_root: float = 0.0, weight_decay: float = 0.0) -> GradientTransformation:
+def muon(lr: Schedule | float, momentum: float = 0.95, dampening: float = 0.0, weight_decay: float = 0.1,
+         adamw_betas: tuple[float | None, float] = (None, 0.999), adamw_eps: float = 1e-8, adamw_eps_root: float = 0.0, *,
+         moment_requires_grad: bool = False) -> GradientTransformation:
+    """Argument order and defaults of the reference (``bergson/magic/optim.py:27-37``): the first
+    AdamW beta defaults to ``momentum``; Nesterov momentum needs a positive ``momentum`` and no
+    dampening; ``moment_requires_grad`` makes the initial momentum buffers leaves of the graph."""
+    if not (callable(lr) or lr >= 0.0):
+        raise ValueError(f"Invalid learning rate: {lr}")
+    if not weight_decay >= 0.0:
+        raise ValueError(f"Invalid weight_decay value: {weight_decay}")
+    if momentum <= 0.0 or dampening != 0.0:
+        raise ValueError("Nesterov momentum requires a momentum and zero dampening")
     b1, b2 = adamw_betas
+    if b1 is None:
+        b1 = momentum
 
     def init(params: Params) -> OptState:
+        for p in params.values():
+            if p.ndim > 2:
+                raise ValueError(f"Muon does not support parameters with more than 2 dimensions, got shape {p.shape}")
         return {
-            "trace": {k: torch.zeros_like(p) for k, p in params.items() if p.ndim == 2},
+            "trace": {k: torch.zeros_like(p, requires_grad=moment_requires_grad) for k, p in params.items() if p.ndim == 2},
             "mu": {k: torch.zeros_like(p) for k, p in params.items() if p.ndim != 2},
             "nu": {k: torch.zeros_like(p) for k, p in params.items() if p.ndim != 2},
             "count": torch.zeros((), dtype=torch.long),

@@ -9,7 +9,7 @@ from pathlib import Path
 
 import torch
 
-from ..data import sorted_checkpoints
+EXPORT_DIRNAME = "exported"  # where export_checkpoints puts checkpoint-<i> by default
 
 
 def save_state_as_pretrained(trainer, state, out_dir: str, cfg=None) -> str:
@@ -58,19 +58,6 @@ def export_checkpoint(trainer, state, ckpt_path: str, out_dir: str, cfg=None) ->
     return out_dir
 
 
-def ensure_exported(trainer, state, run_path: str, cfg=None) -> list[tuple[int, str]]:
-    """Export every ``checkpoints/step_i.ckpt`` of a run to ``checkpoint-i/`` once."""
-    out = []
-    for step, path in sorted_checkpoints(os.path.join(run_path, "checkpoints")):
-        if not os.path.exists(os.path.join(path, ".metadata")):
-            continue
-        dst = os.path.join(run_path, f"checkpoint-{step}")
-        if not os.path.exists(os.path.join(dst, "config.json")):
-            export_checkpoint(trainer, state, path, dst, cfg)
-        out.append((step, dst))
-    return out
-
-
 def sorted_dcp_checkpoints(checkpoints_dir: str | Path) -> list[tuple[int, Path]]:
     """``(step, path)`` of every ``step_<i>[.ckpt]`` directory, ascending
     (reference ``bergson/utils/trainer_export.py:26-39``)."""
@@ -90,13 +77,13 @@ def export_checkpoints(run_path: str | Path, out_dir: str | Path | None = None, 
     """Export the trainer checkpoints of a finished run to ``checkpoint-<i>/`` directories (model
     in ``save_pretrained`` layout, ``optimizer.pt`` copied along), in step order, without a
     trainer in hand: model and state are rebuilt from the run's recorded config
-    (reference ``bergson/utils/trainer_export.py:42-113``).  ``out_dir`` defaults to the run
-    directory itself, where ``ensure_exported`` and the SOURCE pipeline look."""
+    (reference ``bergson/utils/trainer_export.py:42-113``).  ``out_dir`` defaults to
+    ``<run>/exported``, where ``ensure_exported`` and the SOURCE pipeline look."""
     from ..approx_unrolling.train_cfg_io import load_training_config
     from ..magic.trainer import prepare_trainer
 
     run_path = Path(run_path)
-    out_dir = Path(out_dir) if out_dir is not None else run_path
+    out_dir = Path(out_dir) if out_dir is not None else run_path / EXPORT_DIRNAME
     cfg = training_cfg if training_cfg is not None else load_training_config(run_path)
     available = [(s, p) for s, p in sorted_dcp_checkpoints(run_path / "checkpoints") if (p / ".metadata").exists()]
     if not available:
@@ -120,3 +107,26 @@ def export_checkpoints(run_path: str | Path, out_dir: str | Path | None = None, 
         export_checkpoint(trainer, state, str(ckpt), str(dst), cfg)
         exported.append(dst)
     return exported
+
+
+def ensure_exported(checkpoints: list[str]) -> list[str]:
+    """Checkpoint paths as model directories: a raw trainer checkpoint
+    ``<run>/checkpoints/step_<n>.ckpt`` becomes ``<run>/exported/checkpoint-<n>``, exported now
+    unless it already exists (one ``export_checkpoints`` call per run, so the model is rebuilt
+    once); every other path passes through (reference ``bergson/utils/trainer_export.py:116-143``)."""
+    resolved = [str(c) for c in checkpoints]
+    todo: dict[Path, set[int]] = {}
+    for i, c in enumerate(resolved):
+        p = Path(c)
+        stem = p.name.removesuffix(".ckpt").removeprefix("step_")
+        if not (p.name.endswith(".ckpt") and p.name.startswith("step_") and stem.isdigit()):
+            continue
+        run = p.parent.parent
+        dst = run / EXPORT_DIRNAME / f"checkpoint-{int(stem)}"
+        resolved[i] = str(dst)
+        if not dst.exists():
+            todo.setdefault(run, set()).add(int(stem))
+    for run, steps in todo.items():
+        print(f"Exporting trainer checkpoints {sorted(steps)} of {run}")
+        export_checkpoints(run, steps=sorted(steps), overwrite=False)
+    return resolved

@@ -25,7 +25,7 @@ def _setup(family="llama", opt="adamw", dtype=torch.float64, n=8, bs=2):
     sched = lambda s: 5e-3  # noqa: E731
     make = {"adamw": lambda: optim.adamw(sched, betas=(0.95, 0.975), eps_root=1e-8, weight_decay=0.01),
             "sgd": lambda: optim.sgd(sched, momentum=0.9, weight_decay=0.01),
-            "muon": lambda: optim.muon(sched, momentum=0.95, adamw_betas=(0.95, 0.975), adamw_eps_root=1e-8)}[opt]
+            "muon": lambda: optim.muon(sched, momentum=0.95, weight_decay=0.0, adamw_betas=(0.95, 0.975), adamw_eps_root=1e-8)}[opt]
     trainer, state = Trainer.initialize(model, make())
     return trainer, state, data, ds
 
@@ -137,7 +137,7 @@ def test_muon_matches_torch_optim():
     g = torch.randn(6, 4)
     ref_p = torch.nn.Parameter(w.clone())
     ref = torch.optim.Muon([ref_p], lr=0.1, momentum=0.95, weight_decay=0.0, adjust_lr_fn="match_rms_adamw")
-    ours = optim.muon(0.1, momentum=0.95)
+    ours = optim.muon(0.1, momentum=0.95, weight_decay=0.0)
     params = {"w": w.clone()}
     state = ours.init(params)
     for _ in range(3):
@@ -236,3 +236,16 @@ def test_state_activation_swaps_parameters_and_random_streams():
         partial.params.pop(next(iter(partial.params)))
         with partial.activate(model):
             pass
+
+
+def test_muon_argument_checks():
+    with pytest.raises(ValueError, match="Nesterov"):
+        optim.muon(0.1, momentum=0.0)
+    with pytest.raises(ValueError, match="Nesterov"):
+        optim.muon(0.1, dampening=0.1)
+    with pytest.raises(ValueError, match="weight_decay"):
+        optim.muon(0.1, weight_decay=-1.0)
+    with pytest.raises(ValueError, match="2 dimensions"):
+        optim.muon(0.1).init({"conv": torch.zeros(2, 3, 4)})
+    st = optim.muon(0.1, moment_requires_grad=True).init({"w": torch.zeros(3, 2), "b": torch.zeros(3)})
+    assert st["trace"]["w"].requires_grad and set(st["mu"]) == {"b"}

@@ -42,3 +42,33 @@ def test_export_of_a_train_run(tmp_path):
     (empty / "config.yaml").write_text((run / "config.yaml").read_text())
     with pytest.raises(FileNotFoundError, match="save_mode"):
         export_checkpoints(empty)
+
+
+def test_raw_checkpoints_are_exported_on_demand_for_source(tmp_path):
+    from bergson_b200.data import load_scores
+    from bergson_b200.utils.trainer_export import ensure_exported
+
+    run = tmp_path / "run"
+    main(["train", str(run), "--model", MODEL, "--data.dataset", "synthetic:zipf?n=16&len=12&vocab=256&seed=0&min_len=12",
+          "--batch_size", "4", "--lr", "1e-2", "--optimizer", "sgd", "--nproc_per_node", "1", "--save_mode", "all"])
+    found = sorted_dcp_checkpoints(run / "checkpoints")
+    raw = [str(p) for _, p in found[-4:]]
+    other = str(tmp_path / "some" / "checkpoint-7")
+    resolved = ensure_exported(raw[:2] + [other])
+    assert resolved[2] == other  # not a trainer checkpoint: passed through
+    assert all((run / "exported" / f"checkpoint-{s}" / "model.safetensors").exists() for s, _ in found[-4:-2])
+    stamp = (run / "exported" / f"checkpoint-{found[-4][0]}" / "model.safetensors").stat().st_mtime_ns
+    assert ensure_exported(raw[:2]) == resolved[:2]  # reused, not exported again
+    assert (run / "exported" / f"checkpoint-{found[-4][0]}" / "model.safetensors").stat().st_mtime_ns == stamp
+
+    out = tmp_path / "source"
+    main(["approxunrolling", str(out), "--model", MODEL, "--index_cfg.data.dataset", TRAIN,
+          "--approx_unrolling_cfg.query.dataset", "synthetic:zipf?n=3&len=12&vocab=256&seed=1&min_len=12",
+          "--checkpoints", *raw, "--segments", "2", "--nproc_per_node", "1", "--token_batch_size", "64",
+          "--ev_correction", "True", "--use_dataset_labels"])
+    assert all((run / "exported" / f"checkpoint-{s}").is_dir() for s, _ in found[-4:])
+    scores = load_scores(out / "scores") if (out / "scores").exists() else load_scores(out)
+    import numpy as np
+
+    s = np.asarray(scores[:], dtype=np.float64)
+    assert s.shape[0] == 12 and np.isfinite(s).all() and np.abs(s).sum() > 0
