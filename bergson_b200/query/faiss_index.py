@@ -182,7 +182,12 @@ class FaissIndex:
                 shard.nprobe = self._nprobe
 
     @staticmethod
-    def create_index(index_path: Path, faiss_path: Path, cfg: FaissConfig, device: str, unit_norm: bool, h_inv: dict):
+    def create_index(gradients_path: Path, faiss_path: Path, faiss_cfg: FaissConfig, device: str, unit_norm: bool,
+                     hessians: dict):
+        """Build the shards of ``faiss_cfg`` under ``faiss_path`` from the store (or the ``*shard*`` parts)
+        under ``gradients_path``; ``hessians`` maps module names to the matrices applied to their columns."""
+        index_path, cfg, h_inv = Path(gradients_path), faiss_cfg, hessians
+        faiss_path = Path(faiss_path)
         faiss_path.mkdir(parents=True, exist_ok=True)
         parts = list(gradients_loader(Path(index_path)))
         if not parts:

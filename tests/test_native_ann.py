@@ -120,7 +120,7 @@ def test_attributor_over_ivf_shards(tmp_path):
     with open(store / "info.json", "w") as f:
         json.dump({"grad_sizes": {"w": x.shape[1]}, "num_grads": len(x), "base_dtype": "float16"}, f)
     cfg = FaissConfig(index_factory="IVF8,SQfp16", num_shards=3, nprobe=8)
-    FaissIndex.create_index(store, tmp_path / "ann", cfg, "cpu", unit_norm=True, h_inv={})
+    FaissIndex.create_index(store, tmp_path / "ann", cfg, "cpu", unit_norm=True, hessians={})
     idx = FaissIndex(tmp_path / "ann")
     assert idx.ntotal == len(x) and idx.backend == "native"
     d, i = idx.search(q, 5)
@@ -200,7 +200,7 @@ def test_store_helpers_and_multi_part_stores(tmp_path):
     if HAVE_FAISS:
         return
     FaissIndex.create_index(root, tmp_path / "ann", FaissConfig(index_factory="IVF4,SQfp16", num_shards=2, nprobe=4), "cpu",
-                            unit_norm=False, h_inv={})
+                            unit_norm=False, hessians={})
     idx = FaissIndex(tmp_path / "ann")
     assert idx.ntotal == 900
     _, i = idx.search(q, 5)
@@ -224,7 +224,7 @@ def test_nprobe_can_be_changed_after_loading(tmp_path):
     x.astype(np.float16).tofile(store / "gradients.bin")
     (store / "info.json").write_text(json.dumps({"grad_sizes": {"w": x.shape[1]}, "num_grads": len(x), "base_dtype": "float16"}))
     FaissIndex.create_index(store, tmp_path / "ann", FaissConfig(index_factory="IVF16,Flat", num_shards=2, nprobe=1), "cpu",
-                            unit_norm=False, h_inv={})
+                            unit_norm=False, hessians={})
     idx = FaissIndex(tmp_path / "ann")
     assert idx.nprobe == 1 and all(s.nprobe == 1 for s in idx.shards)
     _, truth = _exact(x.astype(np.float16).astype(np.float32), q, 10)
