@@ -64,8 +64,12 @@ def _load_banked_model(run_cfg: ValidationConfig, out_dir: str, device) -> torch
 
 
 def per_doc_query_losses(forward: Callable, query_stream: DataStream, num_docs: int) -> torch.Tensor:
-    """Mean CE of each query document.  ``forward(input_ids)`` returns logits.  Token losses
-    are scattered by the document id of the *label* token and reduced over ranks."""
+    """Mean CE of each query document.  ``forward(input_ids)`` returns logits; a model (an
+    ``nn.Module`` whose output has ``.logits``) may be passed instead.  Token losses are
+    scattered by the document id of the *label* token and reduced over ranks."""
+    if isinstance(forward, torch.nn.Module):
+        module = forward
+        forward = lambda x: module(input_ids=x).logits  # noqa: E731
     device = query_stream.device
     sums = torch.zeros(num_docs, device=device)
     counts = torch.zeros(num_docs, device=device)

@@ -77,3 +77,30 @@ def test_bank_loss_cache_key_tracks_what_losses_depend_on():
     assert bank_loss_cache_key(a, False, 10) != bank_loss_cache_key(a, False, 11)
     b.batch_size = a.batch_size + 1
     assert bank_loss_cache_key(a, False, 10) != bank_loss_cache_key(b, False, 10)
+
+
+def test_per_doc_query_losses_accepts_a_model_and_matches_its_loss():
+    from datasets import Dataset
+
+    from bergson_b200.magic.data_stream import DataStream
+    from bergson_b200.validate import per_doc_query_losses
+
+    from .helpers import tiny_model
+
+    torch.manual_seed(0)
+    model = tiny_model("llama")
+    rows = [[1, 2, 3, 4, 5], [6, 7, 8], [9, 10, 11, 12], [13, 14]]
+    stream = DataStream(Dataset.from_dict({"input_ids": rows}), batch_size=2)
+    losses = per_doc_query_losses(model, stream, num_docs=4)
+    for i, r in enumerate(rows):  # one document per row: its loss when run alone, whatever it was padded with
+        x = torch.tensor([r])
+        torch.testing.assert_close(losses[i], model(x, labels=x).loss.detach().float(), rtol=1e-4, atol=1e-5)
+    # packed rows: a token's loss belongs to the document of its label token
+    packed = DataStream(Dataset.from_dict({"input_ids": [[1, 2, 3, 4, 5, 6]], "doc_ids": [[0, 0, 0, 1, 1, 1]]}), batch_size=1,
+                        weight_shape=(2,))
+    got = per_doc_query_losses(model, packed, num_docs=2)
+    x = torch.tensor([[1, 2, 3, 4, 5, 6]])
+    tok = torch.nn.functional.cross_entropy(model(x).logits[0, :-1].float(), x[0, 1:], reduction="none")
+    label_doc = torch.tensor([0, 0, 1, 1, 1])
+    for d in range(2):
+        torch.testing.assert_close(got[d], tok[label_doc == d].mean().detach(), rtol=1e-4, atol=1e-5)
