@@ -6,6 +6,7 @@ from __future__ import annotations
 
 import os
 import random
+import warnings
 from typing import Any, Type, TypeVar
 
 import ml_dtypes
@@ -112,6 +113,12 @@ def numpy_to_tensor(arr: np.ndarray) -> Tensor:
     """numpy -> tensor, bit-exact for ml_dtypes bfloat16 (and 2-byte void views)."""
     if arr.dtype == np_bfloat16 or arr.dtype.str == "|V2":
         return torch.from_numpy(arr.view(np.uint16).copy()).view(torch.bfloat16)
+    if not arr.flags.writeable:
+        # A read-only memory map: the tensor is only ever read, so torch's warning about writes
+        # through a non-writable array does not apply.
+        with warnings.catch_warnings():
+            warnings.filterwarnings("ignore", message="The given NumPy array is not writable")
+            return torch.from_numpy(arr)
     return torch.from_numpy(arr)
 
 
