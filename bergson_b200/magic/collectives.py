@@ -88,6 +88,40 @@ class _ReduceScatterRows(torch.autograd.Function):
         return _AllGatherRows.apply(g, ctx.group), None
 
 
+class _AllGatherRowsStarted(torch.autograd.Function):
+    """``all_gather_rows`` whose data movement was started earlier: the forward only hands out
+    the gathered tensor, the backward is the same reduce-scatter."""
+
+    @staticmethod
+    def forward(ctx, shard: Tensor, gathered: Tensor, group):
+        ctx.group = group
+        return gathered.view_as(gathered)
+
+    @staticmethod
+    def backward(ctx, g: Tensor):
+        return _ReduceScatterRows.apply(g, ctx.group), None, None
+
+
+def start_all_gather_rows(shard: Tensor, group=None):
+    """Begin ``all_gather_rows(shard)`` without waiting for it: returns a handle for
+    ``finish_all_gather_rows``.  The shard must not change until then."""
+    w = _world(group)
+    src = shard.detach().contiguous()
+    if _is_gloo(group):
+        parts = [torch.empty_like(src) for _ in range(w)]
+        return dist.all_gather(parts, src, group=group, async_op=True), parts, src
+    out = torch.empty((w * src.shape[0], *src.shape[1:]), dtype=src.dtype, device=src.device)
+    return dist.all_gather_into_tensor(out, src, group=group, async_op=True), out, src
+
+
+def finish_all_gather_rows(shard: Tensor, handle, group=None) -> Tensor:
+    """The gathered tensor of a started all-gather, attached to ``shard``'s autograd history."""
+    work, out, _src = handle
+    work.wait()
+    gathered = torch.cat(out, dim=0) if isinstance(out, list) else out
+    return _AllGatherRowsStarted.apply(shard, gathered, group)
+
+
 def all_reduce_sum(x: Tensor, group=None) -> Tensor:
     if not dist.is_initialized() or _world(group) == 1:
         return x

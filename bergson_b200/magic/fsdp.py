@@ -11,11 +11,13 @@ redistribute backward (``bergson/magic/fsdp.py:20-87``, ``dtensor_patch.py``).
 
 from __future__ import annotations
 
+import os
+
 import torch
 import torch.distributed as dist
 from torch import Tensor
 
-from .collectives import all_gather_rows
+from .collectives import all_gather_rows, finish_all_gather_rows, start_all_gather_rows
 
 
 def shallow_copy(tensors: dict[str, Tensor]) -> dict[str, Tensor]:
@@ -88,12 +90,22 @@ class LazyGather:
       shard (what a metagradient needs).  Peak memory is shards + one module's parameters +
       activations, at the price of a second all-gather per parameter in the backward pass.
 
+    * With ``prefetch`` (``BERGSON_B200_FSDP_PREFETCH=1``), while a module runs, the all-gather
+      of the module that ran after it in the previous forward pass is already under way; its
+      pre-hook then only waits for the data.  The call order is learnt during the first pass
+      and kept on the model.  Re-gathers of the backward pass are not prefetched.
+
     The reference gets the same effect from DTensor parametrisations
     (``bergson/magic/fsdp.py``); its full parameters are likewise gathered per module call.
     """
 
-    def __init__(self, model: torch.nn.Module, shards: dict[str, Tensor], shapes: dict[str, torch.Size]):
+    def __init__(self, model: torch.nn.Module, shards: dict[str, Tensor], shapes: dict[str, torch.Size],
+                 prefetch: bool | None = None):
         self.model, self.shards, self.shapes = model, shards, shapes
+        self.prefetch = os.environ.get("BERGSON_B200_FSDP_PREFETCH") == "1" if prefetch is None else prefetch
+        self.prefetch_hits = 0  # gathers whose data had been requested ahead of time
+        self._started: dict[str, tuple] = {}
+        self._seen: list[torch.nn.Module] = []
         self.gathers = 0  # forward gathers + re-gathers (read by the tests)
         self.packed = 0   # saved gathered parameters that were replaced by a marker
         key_of = {}
@@ -113,12 +125,38 @@ class LazyGather:
         self.gathers += 1
         return gather_param(self.shards[key], self.shapes[key])
 
+    def _gather_now_or_finish(self, key: str) -> Tensor:
+        handle = self._started.pop(key, None)
+        if handle is None:
+            return self._gather(key)
+        self.gathers += 1
+        self.prefetch_hits += 1
+        return finish_all_gather_rows(self.shards[key], handle)[: self.shapes[key][0]]
+
+    def _start_next(self, mod) -> None:
+        """Request the parameters of the module that followed ``mod`` in the last pass."""
+        order = getattr(self.model, "_lazy_gather_order", None)
+        if not order or not dist.is_initialized() or dist.get_world_size() == 1:
+            return
+        try:
+            nxt = order[order.index(mod) + 1]
+        except (ValueError, IndexError):
+            return
+        for _, key in self.slots.get(nxt, ()):
+            if key not in self._started and len(self.shapes[key]) > 0:
+                self._started[key] = start_all_gather_rows(self.shards[key])
+
     def _pre(self, mod, args):
+        if self.prefetch:
+            if mod not in self._seen:
+                self._seen.append(mod)
         for leaf, key in self.slots[mod]:
-            full = self._gather(key)
+            full = self._gather_now_or_finish(key) if self.prefetch else self._gather(key)
             self._live[id(full)] = key
             self._originals[(id(mod), leaf)] = mod._parameters.pop(leaf)
             setattr(mod, leaf, full)  # plain attribute: keeps the autograd history of the gather
+        if self.prefetch:
+            self._start_next(mod)
 
     def _post(self, mod, args, output):
         for leaf, _ in self.slots[mod]:
@@ -146,6 +184,11 @@ class LazyGather:
         return self
 
     def __exit__(self, *exc):
+        for handle in self._started.values():  # requested but never used (the call order changed)
+            handle[0].wait()
+        self._started.clear()
+        if self.prefetch and self._seen:
+            self.model._lazy_gather_order = list(self._seen)
         self._saved.__exit__(*exc)
         for h in self._handles:
             h.remove()

@@ -128,3 +128,57 @@ def test_fsdp2_build_two_ranks_equals_one(tmp_path):
     run("build", tmp_path / "fsdp", *opt, "--nproc_per_node", 2, "--fsdp", "true")
     a, b = np.asarray(load_gradients(tmp_path / "plain")), np.asarray(load_gradients(tmp_path / "fsdp"))
     np.testing.assert_allclose(a, b, rtol=1e-4, atol=1e-6)
+
+
+def _prefetch_worker(rank, local_rank, world, out_dir):
+    """Sharded parameters gathered per module, with and without requesting the next module's
+    parameters ahead of time: same loss, same sharded gradients, same second-order gradients."""
+    import torch.distributed as dist
+
+    from bergson_b200.distributed import init_dist
+    from bergson_b200.magic.fsdp import LazyGather, simple_fsdp
+
+    from .helpers import tiny_model
+
+    init_dist(rank, local_rank, world)
+    torch.manual_seed(0)  # the same full model on every rank
+    model = tiny_model("llama", dtype=torch.float64, num_hidden_layers=2)
+    model.eval()
+    full = {k: v.detach().clone() for k, v in model.named_parameters()}
+    shards, shapes = simple_fsdp(full)
+    shards = {k: v.requires_grad_(True) for k, v in shards.items()}
+    x = torch.randint(0, 128, (2, 9), generator=torch.Generator().manual_seed(rank))
+
+    def run(prefetch):
+        with LazyGather(model, shards, shapes, prefetch=prefetch) as lazy:
+            loss = model(input_ids=x, labels=x).loss
+        ps = list(shards.values())
+        g = torch.autograd.grad(loss, ps, create_graph=True, allow_unused=True)
+        inner = sum((t * t).sum() for t in g if t is not None)
+        gg = torch.autograd.grad(inner, ps, allow_unused=True)
+        return loss.detach(), g, gg, lazy
+
+    base = run(False)
+    first = run(True)   # learns the call order, nothing to request yet
+    second = run(True)  # requests each next module while the current one runs
+    assert first[3].prefetch_hits == 0 and second[3].prefetch_hits > 0
+    assert second[3].gathers == base[3].gathers
+    for got in (first, second):
+        torch.testing.assert_close(got[0], base[0], rtol=0, atol=0)
+        for a, b in zip(got[1] + got[2], base[1] + base[2]):
+            if b is None:
+                assert a is None
+            else:
+                torch.testing.assert_close(a, b, rtol=1e-12, atol=1e-14)
+    assert all(isinstance(p, torch.nn.Parameter) for p in model.parameters())
+    torch.save({"hits": second[3].prefetch_hits, "gathers": second[3].gathers}, f"{out_dir}/rank{rank}.pt")
+    dist.barrier()
+
+
+def test_lazy_gather_prefetch_two_ranks(tmp_path):
+    from bergson_b200.config import DistributedConfig
+    from bergson_b200.distributed import launch_distributed_run
+
+    launch_distributed_run("prefetch", _prefetch_worker, [str(tmp_path)], DistributedConfig(nproc_per_node=2))
+    got = [torch.load(tmp_path / f"rank{r}.pt") for r in range(2)]
+    assert got[0] == got[1] and got[0]["hits"] > 5
