@@ -104,3 +104,27 @@ def test_per_doc_query_losses_accepts_a_model_and_matches_its_loss():
     label_doc = torch.tensor([0, 0, 1, 1, 1])
     for d in range(2):
         torch.testing.assert_close(got[d], tok[label_doc == d].mean().detach(), rtol=1e-4, atol=1e-5)
+
+
+def test_stream_serves_per_token_weights_after_a_flat_reweight():
+    """Leave-out validation re-weights by flat index into the weights; with per-token weights
+    ``[docs, seq_len]`` a flat subset must hit exactly those tokens, a whole row of indices the
+    whole document, and per-document weights keep working."""
+    from datasets import Dataset
+
+    from bergson_b200.magic.data_stream import DataStream
+
+    data = Dataset.from_dict({"input_ids": [[1, 2, 3, 4], [5, 6, 7, 8]]})
+    stream = DataStream(data, batch_size=2, weight_shape=(2, 4))
+    stream.requires_grad = False
+    stream.weights.view(-1)[torch.tensor([0 * 4 + 2, 1 * 4 + 0])] = 0.0
+    want = torch.ones(2, 4)
+    want[0, 2] = want[1, 0] = 0.0
+    torch.testing.assert_close(stream[0]["example_weight"].cpu(), want)
+    stream.weights.data.fill_(1.0)
+    stream.weights.view(-1)[torch.arange(4, 8)] = 0.5  # every token of document 1
+    torch.testing.assert_close(stream[0]["example_weight"].cpu(), torch.tensor([[1.0] * 4, [0.5] * 4]))
+    per_doc = DataStream(data, batch_size=2)
+    per_doc.requires_grad = False
+    per_doc.weights.view(-1)[torch.tensor([1])] = 0.0
+    assert per_doc[0]["example_weight"].cpu().tolist() == [1.0, 0.0]
