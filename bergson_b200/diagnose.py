@@ -51,7 +51,7 @@ def _measure(model, short_ids, long_ids, device) -> tuple[float, float]:
             dot += float((a * b).sum())
             na += float((a * a).sum())
             nb += float((b * b).sum())
-    return dot / (na**0.5 * nb**0.5 + 1e-12), float((lm - la).abs())
+    return dot / (na**0.5 * nb**0.5 + 1e-12), float((lm.detach() - la.detach()).abs())
 
 
 def _trials(model, docs, n_trials: int, seed: int, device, vocab: int | None = None):
