@@ -111,3 +111,51 @@ def test_shard_bounds_tile_the_rows(dim, world):
         assert lo == end and hi - lo == base + (rem if rank == 0 else 0)  # the first rank takes the remainder
         end = hi
     assert end == dim
+
+
+def _two_batches(model, collector_cls, tmp_path, **kw):
+    from safetensors.torch import load_file
+
+    torch.manual_seed(3)
+    c = collector_cls(model=model, dtype=torch.float32, path=str(tmp_path), **kw)
+    xs = [torch.randn(2, 3, I), torch.randn(1, 4, I)]
+    masks = [torch.ones(2, 3, dtype=torch.bool), torch.ones(1, 4, dtype=torch.bool)]
+    masks[0][1, 2] = False
+    acts, grads = [], []
+    with c:
+        for x, m in zip(xs, masks):
+            with c.with_batch(m):
+                model.zero_grad()
+                model(x).sum().backward()
+            acts.append(x[m])
+            # d(sum of outputs)/d(biased output) is the same row at every position
+            grads.append(model.unbiased.weight.sum(0).expand(int(m.sum()), O))
+        c.teardown()
+    A = load_file(str(tmp_path / "activation_sharded" / "shard_0.safetensors"))
+    S = load_file(str(tmp_path / "gradient_sharded" / "shard_0.safetensors"))
+    return acts, grads, A["biased"], S["biased"]
+
+
+def test_trace_weighted_factors(tmp_path):
+    """TKFAC: each batch's activation Gram is weighted by the trace of its gradient Gram and the
+    other way round."""
+    from bergson_b200.hessians.tkfac import TraceCovarianceCollector
+
+    acts, grads, A, S = _two_batches(BiasModel(), TraceCovarianceCollector, tmp_path)
+    want_a = sum((g * g).sum() * (a.T @ a) for a, g in zip(acts, grads))
+    want_s = sum((a * a).sum() * (g.T @ g) for a, g in zip(acts, grads))
+    torch.testing.assert_close(A, want_a, rtol=1e-4, atol=1e-5)
+    torch.testing.assert_close(S, want_s, rtol=1e-4, atol=1e-5)
+
+
+def test_shampoo_factors_are_built_from_batch_gradients(tmp_path):
+    """Shampoo: M = g^T a per batch, A += M^T M, S += M M^T, and A is scaled to unit trace at the end."""
+    from bergson_b200.hessians.shampoo import ShampooCollector
+
+    acts, grads, A, S = _two_batches(BiasModel(), ShampooCollector, tmp_path)
+    ms = [g.T @ a for a, g in zip(acts, grads)]
+    want_a = sum(m.T @ m for m in ms)
+    want_s = sum(m @ m.T for m in ms)
+    torch.testing.assert_close(A, want_a / want_a.trace(), rtol=1e-4, atol=1e-6)
+    torch.testing.assert_close(S, want_s, rtol=1e-4, atol=1e-5)
+    assert float(A.trace()) == pytest.approx(1.0, rel=1e-5)
