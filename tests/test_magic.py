@@ -249,3 +249,49 @@ def test_muon_argument_checks():
         optim.muon(0.1).init({"conv": torch.zeros(2, 3, 4)})
     st = optim.muon(0.1, moment_requires_grad=True).init({"w": torch.zeros(3, 2), "b": torch.zeros(3)})
     assert st["trace"]["w"].requires_grad and set(st["mu"]) == {"b"}
+
+
+@pytest.mark.parametrize("weight_decay", [0.0, 0.1])
+@pytest.mark.parametrize("eps_root", [0.0, 1e-6])
+def test_muon_updates_vectors_like_adamw(weight_decay, eps_root):
+    """Muon orthogonalises matrices only; 1-D parameters take the AdamW step with the same
+    hyper-parameters (and torch's AdamW when eps_root is 0)."""
+    torch.manual_seed(0)
+    b0 = torch.randn(8)
+    X, Y = torch.randn(16, 8), torch.randn(16)
+    kw = dict(betas=(0.9, 0.999), eps=1e-8, eps_root=eps_root, weight_decay=weight_decay)
+    ref_opt = optim.adamw(0.01, **kw)
+    mu_opt = optim.muon(0.01, weight_decay=weight_decay, adamw_betas=(0.9, 0.999), adamw_eps=1e-8, adamw_eps_root=eps_root)
+    ref, mu = {"b": b0.clone()}, {"b": b0.clone()}
+    ref_state, mu_state = ref_opt.init(ref), mu_opt.init(mu)
+    torch_b = torch.nn.Parameter(b0.clone())
+    torch_opt = torch.optim.AdamW([torch_b], lr=0.01, betas=(0.9, 0.999), eps=1e-8, weight_decay=weight_decay)
+    for _ in range(10):
+        for params, opt, name in ((ref, ref_opt, "ref"), (mu, mu_opt, "mu")):
+            b = params["b"].detach().requires_grad_(True)
+            (X @ b - Y).pow(2).mean().backward()
+            state = ref_state if name == "ref" else mu_state
+            upd, state = opt.update({"b": b.grad}, state, params={"b": b})
+            params["b"] = optim.apply_updates({"b": b.detach()}, upd)["b"]
+            if name == "ref":
+                ref_state = state
+            else:
+                mu_state = state
+        torch_opt.zero_grad()
+        (X @ torch_b - Y).pow(2).mean().backward()
+        torch_opt.step()
+    torch.testing.assert_close(mu["b"], ref["b"], atol=1e-6, rtol=0)
+    if eps_root == 0.0:
+        torch.testing.assert_close(mu["b"], torch_b.data, atol=1e-5, rtol=0)
+
+
+def test_muon_mixed_shapes():
+    torch.manual_seed(1)
+    params = {"W": torch.randn(4, 4), "b": torch.randn(4)}
+    opt = optim.muon(0.01)
+    state = opt.init(params)
+    upd, state = opt.update({k: torch.randn_like(v) for k, v in params.items()}, state, params=params)
+    assert upd["W"].shape == (4, 4) and upd["b"].shape == (4,) and int(state["count"]) == 1
+    # the matrix update has (nearly) orthonormal direction: equal singular values
+    sv = torch.linalg.svdvals(upd["W"] + 0.01 * 0.1 * params["W"])  # take the weight-decay term back out
+    assert float(sv.max() / sv.min()) < 2.5
