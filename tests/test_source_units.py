@@ -114,3 +114,40 @@ def test_overwrite_recomputes_every_step(overwrite, tmp_path):
         with pytest.raises(_Stop):
             pl.approx_unrolling_pipeline(index_cfg, HessianConfig(method="ekfac", ev_correction=True), au)
     assert seen == {k: (not overwrite) for k in ("cov", "cov_sum", "lambda", "lambda_sum")}
+
+
+def _trainer_run(tmp_path, **training):
+    """A run directory as the trainer leaves it: config.yaml with one ``train`` step."""
+    import yaml
+
+    run = tmp_path / "trainer_run"
+    run.mkdir(parents=True, exist_ok=True)
+    body = dict(run_path=str(run), model=training.pop("model", "native:llama-tiny"), **training)
+    (run / "config.yaml").write_text(yaml.safe_dump({"steps": [{"train": body}]}))
+    return run
+
+
+def test_momentum_is_derived_from_the_trainer_that_made_the_checkpoints(tmp_path):
+    from bergson_b200.approx_unrolling.train_cfg_io import derive_momentum, resolve
+    from bergson_b200.config import TrainingConfig
+
+    # the trainer's SGD takes adam_beta1 as its heavy-ball momentum (0.95 unless set): 1 / (1 - 0.95) = 20 x lr * steps
+    assert derive_momentum(TrainingConfig(run_path="x", optimizer="sgd", adam_beta1=0.9)) == 0.9
+    assert 1.0 / (1.0 - derive_momentum(TrainingConfig(run_path="x", optimizer="sgd"))) == pytest.approx(20.0)
+    assert derive_momentum(TrainingConfig(run_path="x", optimizer="adamw", adam_beta1=0.95)) == 0.0  # its own preconditioner covers it
+    assert derive_momentum(TrainingConfig(run_path="x", optimizer="muon")) == 0.0
+
+    # checkpoints that belong to no trainer run: nothing derived, the unset momentum becomes 0
+    plain = resolve(ApproxUnrollingConfig(checkpoints=["a", "b"], model_path="gpt2"))
+    assert plain.checkpoints == ["a", "b"] and plain.model_path == "gpt2" and plain.momentum == 0.0
+
+    run = _trainer_run(tmp_path, optimizer="sgd", adam_beta1=0.9, model="native:llama-tiny?vocab_size=256")
+    for sub in ("exported/checkpoint-0", "checkpoint-5"):
+        (run / sub).mkdir(parents=True)
+        got = resolve(ApproxUnrollingConfig(checkpoints=[str(run / sub)]))
+        assert got.momentum == 0.9 and got.model_path == "native:llama-tiny?vocab_size=256"
+    # what the user sets wins, zero included
+    ck = str(run / "checkpoint-5")
+    assert resolve(ApproxUnrollingConfig(checkpoints=[ck], momentum=0.5)).momentum == 0.5
+    assert resolve(ApproxUnrollingConfig(checkpoints=[ck], momentum=0.0)).momentum == 0.0
+    assert resolve(ApproxUnrollingConfig(checkpoints=[ck], model_path="mine")).model_path == "mine"
