@@ -128,3 +128,17 @@ def test_stream_serves_per_token_weights_after_a_flat_reweight():
     per_doc.requires_grad = False
     per_doc.weights.view(-1)[torch.tensor([1])] = 0.0
     assert per_doc[0]["example_weight"].cpu().tolist() == [1.0, 0.0]
+
+
+def test_metasmoothness_over_several_epochs(tmp_path):
+    """Epochs are shuffled copies of the documents; a document keeps one data weight across all of
+    them, and gradient accumulation and clipping reach the three trainings."""
+    run("metasmoothness", tmp_path / "ms", "--model", MODEL, "--data.dataset", TRAIN, "--batch_size", "4", "--lr", "1e-3",
+        "--fd_step", "0.05", "--num_epochs", "2", "--grad_accum_steps", "2", "--max_grad_norm", "1.0", "--nproc_per_node", "1")
+    out = json.loads((tmp_path / "ms" / "metasmoothness.json").read_text())
+    assert -1.0 <= out["score"] <= 1.0 and out["total_movement_l1"] > 0
+    one = tmp_path / "one"
+    run("metasmoothness", one, "--model", MODEL, "--data.dataset", TRAIN, "--batch_size", "4", "--lr", "1e-3",
+        "--fd_step", "0.05", "--num_epochs", "1", "--nproc_per_node", "1")
+    single = json.loads((one / "metasmoothness.json").read_text())
+    assert out["total_movement_l1"] != single["total_movement_l1"]  # twice the steps, clipped: another trajectory
