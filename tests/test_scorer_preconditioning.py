@@ -69,3 +69,32 @@ def test_scores_sum_over_modules_and_land_in_the_offset_columns(tmp_path):
     out = w.scores.numpy()
     np.testing.assert_allclose(out[[2, 0], 3:], want[[2, 0]].numpy(), rtol=1e-5, atol=1e-5)
     assert np.abs(out[[1, 3]]).sum() == 0 and np.abs(out[:, :3]).sum() == 0
+
+
+import pytest  # noqa: E402
+
+
+@pytest.mark.parametrize("unit_normalize", [False, True])
+@pytest.mark.parametrize("slices", [[(0, 2), (2, 5)], [(0, 1), (1, 3), (3, 5)]])
+def test_scoring_the_queries_in_slices_equals_one_pass(slices, unit_normalize):
+    """Slicing the query set bounds memory; it must not change a single score, and unit
+    normalisation of the index rows must not be computed per slice."""
+    g = torch.Generator().manual_seed(0)
+    sizes = {"a": 6, "b": 4}
+    queries = {m: torch.randn(5, d, generator=g) for m, d in sizes.items()}
+    rows = {m: torch.randn(7, d, generator=g) for m, d in sizes.items()}
+
+    def run(parts):
+        w = InMemorySequenceScoreWriter(7, 5, dtype=torch.float32)
+        for lo, hi in parts:
+            s = Scorer({m: q[lo:hi] for m, q in queries.items()}, list(sizes), w, CPU, torch.float32,
+                       unit_normalize=unit_normalize, query_offset=lo)
+            s(list(range(7)), rows)
+        return w.scores
+
+    whole, sliced = run([(0, 5)]), run(slices)
+    torch.testing.assert_close(sliced, whole, rtol=0, atol=1e-6)
+    if unit_normalize:
+        flat = torch.cat([rows[m] for m in sizes], 1)
+        want = (flat / flat.norm(dim=1, keepdim=True)) @ torch.cat([queries[m] for m in sizes], 1).T
+        torch.testing.assert_close(whole, want, rtol=1e-5, atol=1e-6)
