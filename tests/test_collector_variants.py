@@ -159,3 +159,33 @@ def test_two_node_build_equals_single_node(tmp_path):
         assert p.returncode == 0, (tmp_path / f"node{node}.log").read_text()[-2000:]
     a, b = np.asarray(load_gradients(tmp_path / "one")), np.asarray(load_gradients(tmp_path / "two"))
     np.testing.assert_allclose(a, b, rtol=1e-4, atol=1e-6)
+
+
+def test_shapes_of_global_and_per_module_targets():
+    from bergson_b200 import GradientProcessor
+    from bergson_b200.collector.gradient_collectors import TraceCollector
+    from bergson_b200.config import AttentionConfig
+
+    from .helpers import TwoLayer
+
+    model = TwoLayer(i=5, h=6, o=2)
+    mk = lambda proc, **kw: TraceCollector(model=model, processor=proc, device="cpu", dtype=torch.float32, **kw)  # noqa: E731
+    assert dict(mk(GradientProcessor(projection_dim=64, projection_target="global")).shapes()) == {"gradients": torch.Size((64,))}
+    with pytest.raises(AssertionError):
+        mk(GradientProcessor(projection_dim=None, projection_target="global")).shapes()
+    per = mk(GradientProcessor(projection_dim=8)).shapes()
+    assert set(per) == {"fc1", "fc2"} and all(tuple(s) == (8, 8) for s in per.values())
+    full = mk(GradientProcessor(include_bias=True)).shapes()
+    assert tuple(full["fc1"]) == (6, 6) and tuple(full["fc2"]) == (2, 7)  # a bias adds one input column
+    heads = mk(GradientProcessor(), attention_cfgs={"fc1": AttentionConfig(num_heads=3, head_size=2, head_dim=2)}).shapes()
+    assert list(heads) == ["fc1.head_0", "fc1.head_1", "fc1.head_2", "fc2"] and tuple(heads["fc1.head_1"]) == (2, 5)
+
+
+def test_global_projection_is_a_sum_of_column_blocks():
+    """Projecting the concatenated gradient equals summing each module's projection by its own
+    column block: why one matrix per module, added up, is a global projection."""
+    torch.manual_seed(42)
+    g = [torch.randn(3, d) for d in (6, 10, 4)]
+    R = create_projection_matrix("test/single", 8, 20, torch.float32, torch.device("cpu"))
+    blocks = R.split([6, 10, 4], dim=1)
+    torch.testing.assert_close(torch.cat(g, 1) @ R.T, sum(x @ b.T for x, b in zip(g, blocks)))
