@@ -100,3 +100,17 @@ def test_approximate_indices_answer_the_same_calls(store, factory):
     # the index was written beside the store and is reused by the next Attributor
     again = Attributor(path, device="cpu", unit_norm=True, faiss_cfg=FaissConfig(index_factory=factory, nprobe=2))
     assert again.faiss_index.ntotal == len(ds)
+
+
+def test_memory_mapped_index_gives_the_same_neighbours(store):
+    """``mmap_index``: the shard's rows stay on disk and are read list by list."""
+    import numpy as np
+
+    model, ds, path = store
+    cfg = dict(index_factory="IVF2,Flat", nprobe=2, num_shards=2)
+    resident = Attributor(path, device="cpu", unit_norm=True, faiss_cfg=FaissConfig(**cfg))
+    mapped = Attributor(path, device="cpu", unit_norm=True, faiss_cfg=FaissConfig(**cfg, mmap_index=True))
+    assert isinstance(mapped.faiss_index.shards[0].vectors, np.memmap)
+    a, b = _trace(resident, model, ds, 2, 5), _trace(mapped, model, ds, 2, 5)
+    assert a.indices[0].tolist() == b.indices[0].tolist()
+    torch.testing.assert_close(a.scores, b.scores, atol=1e-6, rtol=0)
