@@ -39,7 +39,12 @@ def _acquire_slot(block: bool) -> Tensor | None:
     with _slot_lock:
         if _n_slots < _MAX_SLOTS:
             _n_slots += 1
-            return torch.empty(_CHUNK, dtype=torch.uint8, pin_memory=True)
+            try:
+                return torch.empty(_CHUNK, dtype=torch.uint8, pin_memory=True)
+            except RuntimeError:
+                # No page-locked memory to be had (locked-memory limit): a pageable buffer is
+                # slower but just as correct, the copy into it simply completes before it returns.
+                return torch.empty(_CHUNK, dtype=torch.uint8)
     # Every holder of a slot writes it out and returns it without waiting for another one, so a
     # blocking wait always ends.
     return _free_slots.get() if block else None
