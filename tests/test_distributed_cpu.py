@@ -182,3 +182,21 @@ def test_lazy_gather_prefetch_two_ranks(tmp_path):
     launch_distributed_run("prefetch", _prefetch_worker, [str(tmp_path)], DistributedConfig(nproc_per_node=2))
     got = [torch.load(tmp_path / f"rank{r}.pt") for r in range(2)]
     assert got[0] == got[1] and got[0]["hits"] > 5
+
+
+def test_optimizer_moments_are_saved_whole_under_sharding(tmp_path):
+    """With row-sharded parameters the second moments are sharded too; the exported
+    ``optimizer.pt`` must hold them at full shape, equal to the unsharded run's."""
+    common = ["--model", MODEL, "--data.dataset", "synthetic:zipf?n=16&len=12&vocab=256&seed=0&min_len=12", "--batch_size", "4",
+              "--lr", "1e-3", "--save_mode", "all", "--save_optimizer_state", "last"]
+    run("train", tmp_path / "one", *common, "--nproc_per_node", 1)
+    run("train", tmp_path / "two", *common, "--nproc_per_node", 2, "--fsdp", "true")
+    found = {}
+    for name in ("one", "two"):
+        found[name] = torch.load(tmp_path / name / "optimizer.pt", weights_only=False)  # the final state's moments
+    a, b = found["one"]["state"], found["two"]["state"]
+    assert a.keys() == b.keys() and len(a) > 0
+    for k in a:
+        assert a[k]["param_name"] == b[k]["param_name"]
+        assert a[k]["exp_avg_sq"].shape == b[k]["exp_avg_sq"].shape
+        torch.testing.assert_close(a[k]["exp_avg_sq"], b[k]["exp_avg_sq"], rtol=2e-3, atol=1e-10)
