@@ -71,3 +71,12 @@ def test_recall_command(tmp_path):
           "--data.seed", "0", "--data.data_dir", str(tmp_path / "data")])
     row = list(csv.DictReader(open(tmp_path / "out" / "summary.csv")))[0]
     assert float(row["MRR"]) == 1.0 and float(row["recall_at_3"]) == 1.0 and (tmp_path / "out" / "config.yaml").exists()
+
+
+def test_eigenvalue_correction_refuses_projected_gradients(tmp_path):
+    """The corrected eigenvalues live in the unprojected [O, I] basis of every layer."""
+    with pytest.raises(ValueError, match="does not support gradient projection"):
+        main(["hessian", str(tmp_path / "h"), "--model", MODEL, "--index_cfg.data.dataset",
+              "synthetic:zipf?n=4&len=10&vocab=256&seed=0&min_len=6", "--method", "kfac", "--ev_correction", "true",
+              "--projection_dim", "8", "--nproc_per_node", "1"])
+    assert not (tmp_path / "h").exists() or not any((tmp_path / "h").glob("*_sharded"))
