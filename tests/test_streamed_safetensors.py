@@ -74,3 +74,19 @@ def test_device_tensors_go_through_pinned_staging(tmp_path):
         for k, v in tensors.items():
             assert torch.equal(back[k], v.cpu()), k
     assert 0 < ss._n_slots <= ss._MAX_SLOTS and ss._free_slots.qsize() == ss._n_slots  # every slot was returned
+
+
+def test_an_exception_leaves_no_file_behind(tmp_path):
+    path = tmp_path / "z.safetensors"
+    with pytest.raises(KeyError):
+        with StreamedSafetensors(path, {"a": ((2,), torch.float32)}) as w:
+            w.write("a", torch.ones(2))
+            raise KeyError("the producer failed")
+    assert not path.exists() and not (tmp_path / "z.safetensors.partial").exists()
+    # an older complete file is only replaced by a complete new one
+    with StreamedSafetensors(path, {"a": ((2,), torch.float32)}) as w:
+        w.write("a", torch.ones(2))
+    with pytest.raises(RuntimeError):
+        with StreamedSafetensors(path, {"a": ((2,), torch.float32), "b": ((1,), torch.float32)}) as w:
+            w.write("a", torch.zeros(2))
+    assert torch.equal(load_file(str(path))["a"], torch.ones(2))
