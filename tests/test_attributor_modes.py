@@ -114,3 +114,27 @@ def test_memory_mapped_index_gives_the_same_neighbours(store):
     a, b = _trace(resident, model, ds, 2, 5), _trace(mapped, model, ds, 2, 5)
     assert a.indices[0].tolist() == b.indices[0].tolist()
     torch.testing.assert_close(a.scores, b.scores, atol=1e-6, rtol=0)
+
+
+def test_attributor_over_rows_in_memory_and_module_subsets():
+    """``from_rows``: no store on disk; ``modules=`` restricts the inner product to some blocks."""
+    g = torch.Generator().manual_seed(0)
+    sizes = {"a": 6, "b": 4, "c": 5}
+    rows = torch.randn(20, 15, generator=g)
+    attr = Attributor.from_rows(rows, sizes, unit_norm=False)
+    assert attr.N == 20 and attr.ordered_modules == ["a", "b", "c"] and attr.grads["b"].shape == (20, 4)
+    q = {"a": rows[3:5, :6].clone(), "b": rows[3:5, 6:10].clone(), "c": rows[3:5, 10:].clone()}
+    s, i = attr.search(q, k=3)
+    want = rows @ rows[3:5].T
+    assert i[:, 0].tolist() == [3, 4]
+    torch.testing.assert_close(s[:, 0], want[[3, 4], [0, 1]], rtol=1e-5, atol=1e-5)
+    s_ab, i_ab = attr.search(q, k=20, modules={"a", "b"})
+    part = rows[:, :10] @ rows[3:5, :10].T  # only the columns of a and b take part
+    order = part.T.argsort(dim=1, descending=True)
+    assert i_ab.tolist() == order.tolist()
+    torch.testing.assert_close(s_ab, part.T.gather(1, order), rtol=1e-5, atol=1e-5)
+    cos = Attributor.from_rows(rows, sizes, unit_norm=True)
+    s1, i1 = cos.search(q, k=1)
+    assert i1[:, 0].tolist() == [3, 4] and torch.allclose(s1[:, 0], torch.ones(2), atol=1e-5)
+    low, _ = cos.search(q, k=2, reverse=True)
+    assert (low[:, 0] <= low[:, 1]).all() and (low < s1).all()
