@@ -55,8 +55,22 @@ def _node_parent(node: int, nnode: int, port: int, partial, final):
     assert (final / "config.yaml").exists(), f"node {node}: result not visible after the barrier"
 
 
+def _port_whose_successor_is_free() -> int:
+    import socket
+
+    for _ in range(50):  # the parents' barrier listens on MASTER_PORT + 1
+        port = find_free_port()
+        with socket.socket(socket.AF_INET, socket.SOCK_STREAM) as s:
+            try:
+                s.bind(("127.0.0.1", port + 1))
+                return port
+            except OSError:
+                continue
+    raise RuntimeError("no pair of adjacent free ports found")
+
+
 def test_parents_wait_for_the_capped_build(tmp_path):
-    port = find_free_port()
+    port = _port_whose_successor_is_free()
     mp.spawn(_node_parent, args=(2, port, tmp_path / "run.part", tmp_path / "run"), nprocs=2, join=True)
     assert (tmp_path / "run" / "config.yaml").read_text() == "data"
 
