@@ -99,10 +99,14 @@ class FiniteDiff:
                     _xor_swap_(named[name].data, old)
 
     def derivative(self, fn) -> float:
+        def value() -> float:
+            v = fn()
+            return float(v.detach() if isinstance(v, torch.Tensor) else v)
+
         with self.perturbed(+1.0):
-            hi = float(fn())
+            hi = value()
         with self.perturbed(-1.0):
-            lo = float(fn())
+            lo = value()
         return (hi - lo) / (2 * self.eps)
 
 
